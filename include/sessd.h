@@ -1,0 +1,235 @@
+/*
+ * sessd.h - C ABI of the B200 (sm_100a) sparse 3D front end for SE-SSD.
+ *
+ * Every entry point replaces one piece of the reference's TensorRT plugin code; the
+ * reference location is cited at each declaration (paths are relative to the reference
+ * project root). Conventions shared by all entry points:
+ *
+ *   - plain C types only; device buffers are raw pointers, `stream` is a cudaStream_t passed
+ *     as void*; nothing is allocated or freed inside an *_enqueue call and nothing blocks
+ *     (the reference's enqueue() has the same contract, e.g. submConv3dlayer.cu:539-641);
+ *   - tensors use the reference's layouts (row-major, batch outermost):
+ *       points      f32 [B][max_points][4]      (x, y, z, intensity)   voxelGenerator.cu:361
+ *       points_size i32 [B]
+ *       features    f32|f16 [B][max_voxels][C]
+ *       coors       i32 [B][max_voxels][4]      (b, z, y, x)           voxelGenerator.cu:404
+ *       voxel_num   i32 [B]
+ *       dense       f32|f16 [B][C*D][H][W]                             sparse2Dense.cu:201-206
+ *     rows at index >= voxel_num[b] of an output are zero, as the reference leaves them;
+ *   - the reference runs batch 1 only (se-ssd-ai-trt.cpp:1125); B > 1 processes B independent
+ *     frames in one call, frame b using rows [b][...] of every tensor;
+ *   - return value: SESSD_OK (0) or a negative sessd_error. The reference aborts the process on
+ *     any CUDA error (voxelGenerator.cu:8-19); this library never aborts;
+ *   - conditions only the device can see (capacity overflows) are reported as bits OR-ed into
+ *     the int32 status word that occupies the first 4 bytes of the caller's workspace; it is
+ *     cleared at the start of every *_enqueue and may be read after the stream has been
+ *     synchronised (sessd_read_status does the copy).
+ */
+#ifndef SESSD_H_
+#define SESSD_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define SESSD_OK 0
+typedef enum sessd_error {
+    SESSD_ERR_NULL = -1,        /* a required pointer is null */
+    SESSD_ERR_PARAM = -2,       /* a parameter is out of its supported range */
+    SESSD_ERR_WORKSPACE = -3,   /* workspace_bytes is smaller than *_workspace_bytes() */
+    SESSD_ERR_CUDA = -4,        /* a CUDA runtime call failed; see sessd_last_cuda_error() */
+    SESSD_ERR_UNSUPPORTED = -5  /* channel count / dtype combination has no kernel */
+} sessd_error;
+
+/* Bits of the device status word. */
+#define SESSD_STATUS_VOXEL_OVERFLOW 1 /* more voxels / active outputs than max_voxels; extra ones dropped */
+#define SESSD_STATUS_HASH_FULL 2      /* a coordinate table ran out of probes; entry dropped */
+#define SESSD_STATUS_PAIR_OVERFLOW 4  /* a rulebook column exceeded max_voxels entries on export */
+#define SESSD_STATUS_BAD_COORD 8      /* an input coordinate lies outside the declared grid; row ignored */
+
+typedef enum sessd_dtype { SESSD_F32 = 0, SESSD_F16 = 1 } sessd_dtype;
+
+/* ------------------------------------------------------------------------------------------
+ * Voxel generator.  Replaces VoxelGeneratorPlugin (voxelGenerator.h:19-110).
+ * The struct is the plugin's serialized blob, field for field (voxelGenerator.cu:576-600).
+ * ---------------------------------------------------------------------------------------- */
+typedef struct sessd_voxel_params {
+    int32_t max_voxels;            /* voxelNum_   */
+    int32_t max_points_per_voxel;  /* pointNum_   (<= 8) */
+    int32_t voxel_feature_num;     /* featureNum_ (4)   */
+    float x_min, x_max, y_min, y_max, z_min, z_max;
+    float voxel_x, voxel_y, voxel_z;
+    int32_t point_feature_num;     /* 4 */
+    int32_t grid_x, grid_y, grid_z;
+} sessd_voxel_params;
+
+/* Fills grid_x/y/z = np_round((max - min) / voxel) in fp32.
+ * Replaces VoxelGeneratorPlugin::configurePlugin (voxelGenerator.cu:228-235) and np_round (:61-68). */
+int sessd_voxel_configure(sessd_voxel_params* p);
+
+/* Replaces VoxelGeneratorPlugin::getWorkspaceSize (voxelGenerator.cu:237-252). */
+size_t sessd_voxelize_workspace_bytes(const sessd_voxel_params* p, int batch, int max_points);
+
+/* Replaces VoxelGeneratorPlugin::enqueue (voxelGenerator.cu:480-542) with its two kernels
+ * generateVoxels_kernel (:348-451) and generateAverage_kernel (:255-321).
+ * inputs  = { points f32 [B][max_points][4], points_size i32 [B] }
+ * outputs = { voxels [B][max_voxels][4] (out_dtype), coors i32 [B][max_voxels][4], voxel_num i32 [B] }
+ * Voxel rows are numbered by their lowest point index; a voxel averages its
+ * max_points_per_voxel lowest-indexed points. */
+int sessd_voxelize_enqueue(const sessd_voxel_params* p, int batch, int max_points, int out_dtype,
+                           const void* const* inputs, void* const* outputs,
+                           void* workspace, size_t workspace_bytes, void* stream);
+
+/* Device pointer (inside `workspace`) to the clamped per-voxel point counts, i32 [B][max_voxels],
+ * valid after sessd_voxelize_enqueue. The reference keeps the same array in its workspace
+ * (num_points_per_voxel, voxelGenerator.cu:507-509). */
+void* sessd_voxelize_num_points(const sessd_voxel_params* p, int batch, int max_points, void* workspace);
+
+/* ------------------------------------------------------------------------------------------
+ * Sparse convolutions.  Replace SubmConv3dLayerPlugin (submConv3dlayer.h:19-121) and
+ * SparseConv3dLayerPlugin (sparseConv3dlayer.h:18-126). The struct holds the integer lists both
+ * plugins serialize (submConv3dlayer.cu:684-714, sparseConv3dlayer.cu:863-899); ksize/stride/padding
+ * are (z, y, x) triples = the reference's ksize0..2.
+ * ---------------------------------------------------------------------------------------- */
+typedef struct sessd_conv_params {
+    int32_t in_channel, out_channel, max_voxels, feature_num;
+    int32_t out_shape_x, out_shape_y, out_shape_z;
+    int32_t spatial_shape_x, spatial_shape_y, spatial_shape_z;
+    int32_t ksize[3], stride[3], padding[3];
+    int32_t dilation, out_padding;
+    int32_t subm; /* 1: submanifold (outputs = inputs); 0: strided, outputs = union of candidates */
+} sessd_conv_params;
+
+/* Device-resident weights of one layer, repacked for the kernels. */
+typedef struct sessd_conv_weights sessd_conv_weights;
+
+/* Uploads weights f32 [kvol][Cin][Cout] (host pointer, the layout of submConv3dlayer.cu:510).
+ * Replaces the cudaMalloc + cudaMemcpy in the plugin constructors (submConv3dlayer.cu:146-150,
+ * sparseConv3dlayer.cu:157-161). scale/shift (host f32 [Cout], may be null) and relu fold the
+ * BatchNorm1d + ReLU the reference inserts after every layer (se-ssd-ai-trt.cpp:808-856) into the
+ * kernel epilogue: y = max(0, x*scale + shift); with null/null/0 the layer is the bare plugin. */
+int sessd_conv_weights_create(const sessd_conv_params* p, const float* weights, const float* scale,
+                              const float* shift, int relu, int dtype, sessd_conv_weights** out);
+/* Replaces SubmConv3dLayerPlugin::terminate (submConv3dlayer.cu:671-677). */
+void sessd_conv_weights_destroy(sessd_conv_weights* w);
+
+/* Replaces getWorkspaceSize (submConv3dlayer.cu:247-267, sparseConv3dlayer.cu:286-306). */
+size_t sessd_conv_workspace_bytes(const sessd_conv_params* p, int batch);
+
+/* Replaces SubmConv3dLayerPlugin::enqueue (submConv3dlayer.cu:539-641): rulebook kernels
+ * prepareSubMGridKernel (:441-459), getValidOutPosKernel (:271-358), getSubMIndicePairsKernel
+ * (:376-424) and the 27 sparseGatherConvScatter launches (:479-518, :632-638).
+ * inputs = { features [B][max_voxels][Cin], coors, voxel_num }, outputs = { features [B][max_voxels][Cout] } */
+int sessd_subm_conv_enqueue(const sessd_conv_params* p, const sessd_conv_weights* w, int batch,
+                            const void* const* inputs, void* const* outputs,
+                            void* workspace, size_t workspace_bytes, void* stream);
+
+/* Replaces SparseConv3dLayerPlugin::enqueue (sparseConv3dlayer.cu:606-813): getValidOutPosKernel
+ * (:310-386), fillGridKernel1/2 (:475-541), getSparseIndicePairsKernel (:405-454) and the per-offset
+ * sparseGatherConvScatter launches (:557-589, :804-809).
+ * outputs = { features [B][max_voxels][Cout], coors i32 [B][max_voxels][4], voxel_num i32 [B] }.
+ * Output rows are numbered in the order a sequential pass over (input row, candidate) first meets
+ * them (the rule of the host loop kept in comments at sparseConv3dlayer.cu:738-757). */
+int sessd_sparse_conv_enqueue(const sessd_conv_params* p, const sessd_conv_weights* w, int batch,
+                              const void* const* inputs, void* const* outputs,
+                              void* workspace, size_t workspace_bytes, void* stream);
+
+/* Writes the rulebook of the last *_conv_enqueue that used `workspace`, for frame `frame`, in the
+ * reference's own layout: indice_pairs i32 [kvol][2][max_voxels] (input row, output row; -1 unused) and
+ * indice_num u32 [kvol] (submConv3dlayer.cu:254-255, :413-419). Both are device pointers, as is
+ * out_voxel_num (i32 [B]: the layer's output row counts, i.e. the input voxel_num for a submanifold
+ * layer and outputs[2] for a strided one). Within one offset, pairs are ordered by output row. Used by the parity tests; the kernels themselves work from
+ * an output-stationary neighbour map and never build this list. */
+int sessd_conv_rulebook_export(const sessd_conv_params* p, int batch, int frame, void* workspace,
+                               int32_t* indice_pairs, uint32_t* indice_num, void* stream,
+                               const void* out_voxel_num);
+
+/* ------------------------------------------------------------------------------------------
+ * Sparse -> dense BEV.  Replaces Sparse2DensePlugin (sparse2Dense.h:18-86); the struct is its
+ * serialized blob (sparse2Dense.cu:283-295).
+ * ---------------------------------------------------------------------------------------- */
+typedef struct sessd_s2d_params {
+    int32_t feature_map_size_x, feature_map_size_y, feature_map_size_z, feature_map_channel;
+} sessd_s2d_params;
+
+/* Replaces Sparse2DensePlugin::enqueue (sparse2Dense.cu:224-249) and sparse2dense_kernel (:182-207).
+ * inputs = { features [B][max_voxels][C], coors, voxel_num }, outputs = { dense [B][C*D][H][W] }.
+ * Needs no workspace beyond the 256-byte status block (workspace may be null: then no status). */
+int sessd_sparse2dense_enqueue(const sessd_s2d_params* p, int batch, int max_voxels, int dtype,
+                               const void* const* inputs, void* const* outputs,
+                               void* workspace, size_t workspace_bytes, void* stream);
+
+/* ------------------------------------------------------------------------------------------
+ * Whole front end: voxelise -> conv stack (BN + ReLU folded) -> dense BEV, the layer sequence
+ * wired at se-ssd-ai-trt.cpp:1138-1252, as one call. Coordinate tables and neighbour maps are built
+ * once per resolution and shared by the layers that use them (the reference rebuilds the rulebook
+ * inside every plugin call).
+ * ---------------------------------------------------------------------------------------- */
+typedef struct sessd_backbone sessd_backbone;
+
+/* weights[l] / scale[l] / shift[l]: host pointers per layer, as for sessd_conv_weights_create. */
+int sessd_backbone_create(const sessd_voxel_params* vp, const sessd_conv_params* layers, int nlayers,
+                          const float* const* weights, const float* const* scale, const float* const* shift,
+                          const sessd_s2d_params* s2d, int dtype, sessd_backbone** out);
+void sessd_backbone_destroy(sessd_backbone* bb);
+size_t sessd_backbone_workspace_bytes(const sessd_backbone* bb, int batch, int max_points);
+
+/* points f32 [B][max_points][4], points_size i32 [B] -> dense [B][C*D][H][W] (all device pointers).
+ * Replaces the sparse part of one IExecutionContext::enqueueV2 call (se-ssd-ai-trt.cpp:1868). */
+int sessd_backbone_enqueue(const sessd_backbone* bb, int batch, int max_points,
+                           const void* points, const void* points_size, void* dense,
+                           void* workspace, size_t workspace_bytes, void* stream);
+
+/* Device pointers (inside `workspace`) to what layer `layer` produced in the last enqueue:
+ * features [B][max_voxels][Cout], coors, voxel_num. layer = -1 selects the voxeliser's outputs. */
+int sessd_backbone_layer_view(const sessd_backbone* bb, int batch, int max_points, void* workspace, int layer,
+                              void** features, void** coors, void** voxel_num);
+
+/* Host-buffer variant used for end-to-end timing: copies `nframes` frames of points from (ideally
+ * pinned) host memory, runs them in groups of `batch` on `nstreams` streams and copies each frame's
+ * final voxel count and status word back to the host. Replaces the per-frame body of the reference's
+ * inference loop (se-ssd-ai-trt.cpp:1858-1894: H2D copy, enqueueV2, D2H copy, stream sync). The dense
+ * BEV map of the last group stays on the device (the reference also keeps it there for its 2D head).
+ * A pipeline owns its device buffers and streams; create/destroy allocate and free them. */
+typedef struct sessd_pipeline sessd_pipeline;
+int sessd_pipeline_create(const sessd_backbone* bb, int batch, int max_points, int nstreams, sessd_pipeline** out);
+void sessd_pipeline_destroy(sessd_pipeline* pl);
+/* host_points f32 [nframes][max_points][4], host_sizes i32 [nframes];
+ * host_voxel_num i32 [nframes], host_status i32 [nframes] (status of the group the frame ran in). */
+int sessd_pipeline_run_host(sessd_pipeline* pl, const float* host_points, const int32_t* host_sizes, int nframes,
+                            int32_t* host_voxel_num, int32_t* host_status, float* elapsed_ms);
+/* Same work with the points already on the device: points f32 [nframes][max_points][4], sizes i32 [nframes].
+ * Kernels are enqueued on the pipeline's streams; elapsed device time between the first and the last
+ * stream event is returned in *elapsed_ms when it is non-null. */
+int sessd_pipeline_run_device(sessd_pipeline* pl, const void* points, const void* sizes, int nframes,
+                              float* elapsed_ms);
+/* Dense BEV buffer / workspace of stream `s` (device pointers; dense is [batch][C*D][H][W]). */
+void* sessd_pipeline_dense(sessd_pipeline* pl, int s);
+void* sessd_pipeline_workspace(sessd_pipeline* pl, int s);
+/* Index of the last coordinate level of a backbone (number of strided layers). */
+int sessd_backbone_final_level(const sessd_backbone* bb);
+
+/* Per-launch timing for benchmarks (takes the place of the reference's unused Tn::Profiler,
+ * Utils.h:24-49). Between begin and end every kernel this library launches from the calling thread is
+ * bracketed by CUDA events on its own stream. end synchronises the device, writes the kernel names
+ * (newline separated) and their durations in milliseconds, and returns the number of launches. */
+int sessd_profile_begin(void);
+int sessd_profile_end(void* stream, char* names, size_t names_cap, float* ms, int cap);
+/* Number of kernel launches issued by this library since process start (for launch accounting). */
+uint64_t sessd_launch_count(void);
+
+/* Synchronises `stream`, copies the status word of `workspace` to the host and returns it (>= 0),
+ * or a negative sessd_error. */
+int sessd_read_status(const void* workspace, void* stream);
+/* Text of the last CUDA error seen by this thread inside the library ("" if none). */
+const char* sessd_last_cuda_error(void);
+/* Library version string. */
+const char* sessd_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* SESSD_H_ */

@@ -1,0 +1,412 @@
+"""B200 (sm_100a) sparse 3D front end for SE-SSD: Python view of the C ABI in include/sessd.h.
+
+The product is libsessd.so (hand-written CUDA behind a C ABI that mirrors the reference's TensorRT
+plugins). This module only binds it with ctypes and uses torch tensors as device buffers; there is no
+CPU fallback: importing works without a GPU (so that the build can be checked), every compute call
+needs the library and a CUDA device and raises otherwise.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+import numpy as np
+
+from . import schedule, synth  # noqa: F401
+from .build import LIB_PATH, build
+
+F32, F16 = 0, 1
+STATUS_VOXEL_OVERFLOW, STATUS_HASH_FULL, STATUS_PAIR_OVERFLOW, STATUS_BAD_COORD = 1, 2, 4, 8
+
+EXPORTS = (
+    "sessd_voxel_configure", "sessd_voxelize_workspace_bytes", "sessd_voxelize_enqueue", "sessd_voxelize_num_points",
+    "sessd_conv_weights_create", "sessd_conv_weights_destroy", "sessd_conv_workspace_bytes",
+    "sessd_subm_conv_enqueue", "sessd_sparse_conv_enqueue", "sessd_conv_rulebook_export",
+    "sessd_sparse2dense_enqueue", "sessd_backbone_create", "sessd_backbone_destroy",
+    "sessd_backbone_workspace_bytes", "sessd_backbone_enqueue", "sessd_backbone_layer_view",
+    "sessd_backbone_final_level", "sessd_pipeline_create", "sessd_pipeline_destroy", "sessd_pipeline_run_host",
+    "sessd_pipeline_run_device", "sessd_pipeline_dense", "sessd_pipeline_workspace", "sessd_launch_count",
+    "sessd_profile_begin", "sessd_profile_end", "sessd_read_status", "sessd_last_cuda_error", "sessd_version",
+)
+
+
+class SessdError(RuntimeError):
+    pass
+
+
+class VoxelParams(C.Structure):
+    _fields_ = [("max_voxels", C.c_int32), ("max_points_per_voxel", C.c_int32), ("voxel_feature_num", C.c_int32),
+                ("x_min", C.c_float), ("x_max", C.c_float), ("y_min", C.c_float), ("y_max", C.c_float),
+                ("z_min", C.c_float), ("z_max", C.c_float),
+                ("voxel_x", C.c_float), ("voxel_y", C.c_float), ("voxel_z", C.c_float),
+                ("point_feature_num", C.c_int32), ("grid_x", C.c_int32), ("grid_y", C.c_int32), ("grid_z", C.c_int32)]
+
+
+class ConvParams(C.Structure):
+    _fields_ = [("in_channel", C.c_int32), ("out_channel", C.c_int32), ("max_voxels", C.c_int32),
+                ("feature_num", C.c_int32),
+                ("out_shape_x", C.c_int32), ("out_shape_y", C.c_int32), ("out_shape_z", C.c_int32),
+                ("spatial_shape_x", C.c_int32), ("spatial_shape_y", C.c_int32), ("spatial_shape_z", C.c_int32),
+                ("ksize", C.c_int32 * 3), ("stride", C.c_int32 * 3), ("padding", C.c_int32 * 3),
+                ("dilation", C.c_int32), ("out_padding", C.c_int32), ("subm", C.c_int32)]
+
+
+class S2DParams(C.Structure):
+    _fields_ = [("feature_map_size_x", C.c_int32), ("feature_map_size_y", C.c_int32),
+                ("feature_map_size_z", C.c_int32), ("feature_map_channel", C.c_int32)]
+
+
+_lib = None
+
+
+def lib():
+    """The loaded CUDA library; raises if it has not been built."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise SessdError(f"{LIB_PATH} is missing: run build() (needs nvcc); there is no CPU fallback")
+        L = C.CDLL(LIB_PATH)
+        for name in ("sessd_voxelize_workspace_bytes", "sessd_conv_workspace_bytes", "sessd_backbone_workspace_bytes"):
+            getattr(L, name).restype = C.c_size_t
+        for name in ("sessd_voxelize_num_points", "sessd_pipeline_dense", "sessd_pipeline_workspace"):
+            getattr(L, name).restype = C.c_void_p
+        L.sessd_launch_count.restype = C.c_uint64
+        L.sessd_last_cuda_error.restype = C.c_char_p
+        L.sessd_version.restype = C.c_char_p
+        _lib = L
+    return _lib
+
+
+def _check(rc: int, what: str):
+    if rc != 0:
+        names = {-1: "null pointer", -2: "bad parameter", -3: "workspace too small", -4: "CUDA error",
+                 -5: "unsupported configuration"}
+        extra = lib().sessd_last_cuda_error().decode() if rc == -4 else ""
+        raise SessdError(f"{what} failed: {names.get(rc, rc)} {extra}")
+
+
+def _torch():
+    import torch
+
+    if not torch.cuda.is_available():
+        raise SessdError("a CUDA device is required (there is no CPU path in this package)")
+    return torch
+
+
+def _stream():
+    return C.c_void_p(_torch().cuda.current_stream().cuda_stream)
+
+
+def _vp(*tensors):
+    return (C.c_void_p * len(tensors))(*[C.c_void_p(t.data_ptr()) if t is not None else None for t in tensors])
+
+
+def _tdtype(dtype):
+    torch = _torch()
+    return torch.float32 if dtype == F32 else torch.float16
+
+
+def voxel_params(max_voxels, point_range=synth.POINT_RANGE, voxel_size=synth.VOXEL_SIZE, max_points_per_voxel=5):
+    """VoxelParams from (xmin, ymin, zmin, xmax, ymax, zmax) and (vx, vy, vz), grid filled like configurePlugin."""
+    xmin, ymin, zmin, xmax, ymax, zmax = point_range
+    p = VoxelParams(max_voxels, max_points_per_voxel, 4, xmin, xmax, ymin, ymax, zmin, zmax, *voxel_size, 4, 0, 0, 0)
+    _check(lib().sessd_voxel_configure(C.byref(p)), "sessd_voxel_configure")
+    return p
+
+
+def conv_params(layer: schedule.ConvLayer, max_voxels: int) -> ConvParams:
+    p = ConvParams()
+    p.in_channel, p.out_channel, p.max_voxels, p.feature_num = layer.cin, layer.cout, max_voxels, layer.cin
+    p.out_shape_z, p.out_shape_y, p.out_shape_x = layer.out_shape
+    p.spatial_shape_z, p.spatial_shape_y, p.spatial_shape_x = layer.in_shape
+    for j in range(3):
+        p.ksize[j], p.stride[j], p.padding[j] = layer.ksize[j], layer.stride[j], layer.padding[j]
+    p.dilation, p.out_padding, p.subm = 1, 0, int(layer.subm)
+    return p
+
+
+def read_status(workspace) -> int:
+    rc = lib().sessd_read_status(C.c_void_p(workspace.data_ptr()), _stream())
+    if rc < 0:
+        _check(rc, "sessd_read_status")
+    return rc
+
+
+def voxelize(points, points_size, params: VoxelParams, out_dtype=F32):
+    """points: cuda f32 [B, P, 4]; points_size: cuda i32 [B]. Returns dict of cuda tensors + status."""
+    torch = _torch()
+    B, P = points.shape[0], points.shape[1]
+    nbytes = lib().sessd_voxelize_workspace_bytes(C.byref(params), B, P)
+    if nbytes == 0:
+        raise SessdError("sessd_voxelize_workspace_bytes rejected the parameters")
+    ws = torch.empty(nbytes, dtype=torch.uint8, device=points.device)
+    V = params.max_voxels
+    voxels = torch.empty((B, V, 4), dtype=_tdtype(out_dtype), device=points.device)
+    coors = torch.empty((B, V, 4), dtype=torch.int32, device=points.device)
+    num = torch.empty((B,), dtype=torch.int32, device=points.device)
+    _check(lib().sessd_voxelize_enqueue(C.byref(params), B, P, out_dtype, _vp(points, points_size),
+                                        _vp(voxels, coors, num), C.c_void_p(ws.data_ptr()), C.c_size_t(nbytes),
+                                        _stream()), "sessd_voxelize_enqueue")
+    status = read_status(ws)
+    npv_ptr = lib().sessd_voxelize_num_points(C.byref(params), B, P, C.c_void_p(ws.data_ptr()))
+    off = (npv_ptr - ws.data_ptr())
+    npv = ws[off:off + B * V * 4].view(torch.int32).reshape(B, V).clone()
+    return dict(voxels=voxels, coors=coors, voxel_num=num, num_points=npv, status=status)
+
+
+class ConvWeights:
+    """Device weights of one sparse conv layer (+ optional folded scale/shift/ReLU epilogue)."""
+
+    def __init__(self, params: ConvParams, weights, scale=None, shift=None, relu=False, dtype=F32):
+        _torch()
+        w = np.ascontiguousarray(weights, dtype=np.float32)
+        self._keep = [w]
+        fp = C.POINTER(C.c_float)
+        sc = sh = None
+        if scale is not None:
+            s = np.ascontiguousarray(scale, dtype=np.float32)
+            self._keep.append(s)
+            sc = s.ctypes.data_as(fp)
+        if shift is not None:
+            s = np.ascontiguousarray(shift, dtype=np.float32)
+            self._keep.append(s)
+            sh = s.ctypes.data_as(fp)
+        self.handle = C.c_void_p()
+        self.dtype = dtype
+        _check(lib().sessd_conv_weights_create(C.byref(params), w.ctypes.data_as(fp), sc, sh, int(relu), dtype,
+                                               C.byref(self.handle)), "sessd_conv_weights_create")
+
+    def close(self):
+        if self.handle:
+            lib().sessd_conv_weights_destroy(self.handle)
+            self.handle = C.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+def _conv_workspace(params, B, device):
+    torch = _torch()
+    nbytes = lib().sessd_conv_workspace_bytes(C.byref(params), B)
+    if nbytes == 0:
+        raise SessdError("sessd_conv_workspace_bytes rejected the parameters")
+    return torch.empty(nbytes, dtype=torch.uint8, device=device), nbytes
+
+
+def subm_conv(feat, coors, voxel_num, params: ConvParams, weights: ConvWeights, keep_workspace=False):
+    torch = _torch()
+    B, V = feat.shape[0], params.max_voxels
+    ws, nbytes = _conv_workspace(params, B, feat.device)
+    out = torch.empty((B, V, params.out_channel), dtype=_tdtype(weights.dtype), device=feat.device)
+    _check(lib().sessd_subm_conv_enqueue(C.byref(params), weights.handle, B, _vp(feat, coors, voxel_num), _vp(out),
+                                         C.c_void_p(ws.data_ptr()), C.c_size_t(nbytes), _stream()),
+           "sessd_subm_conv_enqueue")
+    status = read_status(ws)
+    r = dict(features=out, status=status)
+    if keep_workspace:
+        r["workspace"] = ws
+    return r
+
+
+def sparse_conv(feat, coors, voxel_num, params: ConvParams, weights: ConvWeights, keep_workspace=False):
+    torch = _torch()
+    B, V = feat.shape[0], params.max_voxels
+    ws, nbytes = _conv_workspace(params, B, feat.device)
+    out = torch.empty((B, V, params.out_channel), dtype=_tdtype(weights.dtype), device=feat.device)
+    ocoors = torch.empty((B, V, 4), dtype=torch.int32, device=feat.device)
+    onum = torch.empty((B,), dtype=torch.int32, device=feat.device)
+    _check(lib().sessd_sparse_conv_enqueue(C.byref(params), weights.handle, B, _vp(feat, coors, voxel_num),
+                                           _vp(out, ocoors, onum), C.c_void_p(ws.data_ptr()), C.c_size_t(nbytes),
+                                           _stream()), "sessd_sparse_conv_enqueue")
+    status = read_status(ws)
+    r = dict(features=out, coors=ocoors, voxel_num=onum, status=status)
+    if keep_workspace:
+        r["workspace"] = ws
+    return r
+
+
+def rulebook_export(params: ConvParams, B, frame, workspace, out_voxel_num):
+    """Reference-layout rulebook of the last conv call that used `workspace` (cuda tensors)."""
+    torch = _torch()
+    kvol = params.ksize[0] * params.ksize[1] * params.ksize[2]
+    pairs = torch.empty((kvol, 2, params.max_voxels), dtype=torch.int32, device=workspace.device)
+    num = torch.zeros((kvol,), dtype=torch.int32, device=workspace.device)
+    _check(lib().sessd_conv_rulebook_export(C.byref(params), B, frame, C.c_void_p(workspace.data_ptr()),
+                                            C.c_void_p(pairs.data_ptr()), C.c_void_p(num.data_ptr()), _stream(),
+                                            C.c_void_p(out_voxel_num.data_ptr())), "sessd_conv_rulebook_export")
+    torch.cuda.current_stream().synchronize()
+    return pairs, num
+
+
+def sparse2dense(feat, coors, voxel_num, params: S2DParams, dtype=F32):
+    torch = _torch()
+    B, V = feat.shape[0], feat.shape[1]
+    dense = torch.empty((B, params.feature_map_channel * params.feature_map_size_z, params.feature_map_size_y,
+                         params.feature_map_size_x), dtype=_tdtype(dtype), device=feat.device)
+    _check(lib().sessd_sparse2dense_enqueue(C.byref(params), B, V, dtype, _vp(feat, coors, voxel_num), _vp(dense),
+                                            None, C.c_size_t(0), _stream()), "sessd_sparse2dense_enqueue")
+    return dense
+
+
+class Backbone:
+    """voxelise -> conv stack (BN + ReLU folded) -> dense BEV, one C call per batch of frames."""
+
+    def __init__(self, max_voxels, weights, scale=None, shift=None, dtype=F16, layers=schedule.LAYERS,
+                 point_range=synth.POINT_RANGE, voxel_size=synth.VOXEL_SIZE, with_dense=True):
+        _torch()
+        self.layers, self.dtype, self.max_voxels = tuple(layers), dtype, max_voxels
+        self.vp = voxel_params(max_voxels, point_range, voxel_size)
+        n = len(self.layers)
+        cps = (ConvParams * n)(*[conv_params(l, max_voxels) for l in self.layers])
+        fp = C.POINTER(C.c_float)
+        self._keep = [np.ascontiguousarray(w, dtype=np.float32) for w in weights]
+        wptr = (fp * n)(*[w.ctypes.data_as(fp) for w in self._keep])
+        scptr = shptr = None
+        if scale is not None:
+            sc = [np.ascontiguousarray(s, dtype=np.float32) for s in scale]
+            sh = [np.ascontiguousarray(s, dtype=np.float32) for s in shift]
+            self._keep += sc + sh
+            scptr = (fp * n)(*[s.ctypes.data_as(fp) for s in sc])
+            shptr = (fp * n)(*[s.ctypes.data_as(fp) for s in sh])
+        last = self.layers[-1]
+        self.s2d = S2DParams(last.out_shape[2], last.out_shape[1], last.out_shape[0], last.cout) if with_dense else None
+        self.handle = C.c_void_p()
+        _check(lib().sessd_backbone_create(C.byref(self.vp), cps, n, wptr, scptr, shptr,
+                                           C.byref(self.s2d) if with_dense else None, dtype, C.byref(self.handle)),
+               "sessd_backbone_create")
+
+    def workspace_bytes(self, batch, max_points) -> int:
+        n = lib().sessd_backbone_workspace_bytes(self.handle, batch, max_points)
+        if n == 0:
+            raise SessdError("sessd_backbone_workspace_bytes rejected the parameters")
+        return n
+
+    def dense_shape(self, batch):
+        return (batch, self.s2d.feature_map_channel * self.s2d.feature_map_size_z, self.s2d.feature_map_size_y,
+                self.s2d.feature_map_size_x)
+
+    def run(self, points, points_size, workspace=None, dense=None):
+        """points cuda f32 [B, P, 4], points_size cuda i32 [B] -> (dense, workspace)."""
+        torch = _torch()
+        B, P = points.shape[0], points.shape[1]
+        nbytes = self.workspace_bytes(B, P)
+        if workspace is None:
+            workspace = torch.empty(nbytes, dtype=torch.uint8, device=points.device)
+        if dense is None and self.s2d is not None:
+            dense = torch.empty(self.dense_shape(B), dtype=_tdtype(self.dtype), device=points.device)
+        _check(lib().sessd_backbone_enqueue(self.handle, B, P, C.c_void_p(points.data_ptr()),
+                                            C.c_void_p(points_size.data_ptr()),
+                                            C.c_void_p(dense.data_ptr()) if dense is not None else None,
+                                            C.c_void_p(workspace.data_ptr()), C.c_size_t(workspace.numel()), _stream()),
+               "sessd_backbone_enqueue")
+        return dense, workspace
+
+    def layer_view(self, workspace, batch, max_points, layer):
+        """(features, coors, voxel_num) cuda tensors of conv layer `layer` (-1: voxeliser output)."""
+        torch = _torch()
+        f, c, n = C.c_void_p(), C.c_void_p(), C.c_void_p()
+        _check(lib().sessd_backbone_layer_view(self.handle, batch, max_points, C.c_void_p(workspace.data_ptr()), layer,
+                                               C.byref(f), C.byref(c), C.byref(n)), "sessd_backbone_layer_view")
+        ch = 4 if layer < 0 else self.layers[layer].cout
+        es = 4 if self.dtype == F32 else 2
+        V = self.max_voxels
+        base = workspace.data_ptr()
+
+        def view(ptr, nbytes, dt, shape):
+            off = ptr.value - base
+            return workspace[off:off + nbytes].view(dt).reshape(shape)
+
+        return (view(f, batch * V * ch * es, _tdtype(self.dtype), (batch, V, ch)),
+                view(c, batch * V * 16, torch.int32, (batch, V, 4)),
+                view(n, batch * 4, torch.int32, (batch,)))
+
+    def close(self):
+        if self.handle:
+            lib().sessd_backbone_destroy(self.handle)
+            self.handle = C.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+class Pipeline:
+    """Streams + device buffers that push frames through a Backbone `batch` at a time."""
+
+    def __init__(self, backbone: Backbone, batch, max_points, nstreams=2):
+        self.backbone, self.batch, self.max_points, self.nstreams = backbone, batch, max_points, nstreams
+        self.handle = C.c_void_p()
+        _check(lib().sessd_pipeline_create(backbone.handle, batch, max_points, nstreams, C.byref(self.handle)),
+               "sessd_pipeline_create")
+
+    def run_device(self, points, sizes) -> float:
+        """points cuda f32 [F, P, 4], sizes cuda i32 [F]; returns device milliseconds."""
+        ms = C.c_float(0)
+        _check(lib().sessd_pipeline_run_device(self.handle, C.c_void_p(points.data_ptr()), C.c_void_p(sizes.data_ptr()),
+                                               points.shape[0], C.byref(ms)), "sessd_pipeline_run_device")
+        return float(ms.value)
+
+    def run_host(self, points, sizes, voxel_num, status) -> float:
+        """points pinned f32 [F, P, 4], sizes/voxel_num/status pinned i32 [F] (CPU tensors)."""
+        ms = C.c_float(0)
+        _check(lib().sessd_pipeline_run_host(self.handle, C.c_void_p(points.data_ptr()), C.c_void_p(sizes.data_ptr()),
+                                             points.shape[0], C.c_void_p(voxel_num.data_ptr()),
+                                             C.c_void_p(status.data_ptr()), C.byref(ms)), "sessd_pipeline_run_host")
+        return float(ms.value)
+
+    def close(self):
+        if self.handle:
+            lib().sessd_pipeline_destroy(self.handle)
+            self.handle = C.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+def profile(fn):
+    """Runs fn() with per-launch timing; returns [(kernel name, ms), ...] in launch order."""
+    _check(lib().sessd_profile_begin(), "sessd_profile_begin")
+    try:
+        fn()
+    finally:
+        cap = 4096
+        names = C.create_string_buffer(1 << 18)
+        ms = (C.c_float * cap)()
+        n = lib().sessd_profile_end(_stream(), names, C.c_size_t(len(names)), ms, cap)
+    if n < 0:
+        _check(n, "sessd_profile_end")
+    nm = names.value.decode().split("\n")[:n]
+    return [(nm[i], float(ms[i])) for i in range(min(n, cap))]
+
+
+def launch_count() -> int:
+    return int(lib().sessd_launch_count())
+
+
+def random_weights(seed=0x5E55D000 + 3, layers=schedule.LAYERS, std=0.02, with_bn=True):
+    """Seeded N(0, std) weights per layer and a seeded BatchNorm folded to (scale, shift)."""
+    ws, scs, shs = [], [], []
+    for i, l in enumerate(layers):
+        ws.append(synth.normal_f32(seed + 17 * i, (l.kvol, l.cin, l.cout), std))
+        if with_bn:
+            s = synth.Stream(seed + 17 * i + 7)
+            gamma = 1.0 + 0.1 * s.normal(l.cout)
+            beta = 0.05 * s.normal(l.cout)
+            mean = 0.02 * s.normal(l.cout)
+            var = 0.5 + s.uniform(l.cout) * 0.02
+            # weights this small give conv outputs ~1e-2; scale them back to O(1) like a trained BN would
+            var = var * (std * std * l.kvol * l.cin / 4.0)
+            g32, b32, m32, v32 = [t.astype(np.float32) for t in (gamma, beta, mean, var)]
+            sc = (g32 / np.sqrt(v32 + np.float32(schedule.BN_EPS))).astype(np.float32)
+            sh = (b32 - m32 * g32 / np.sqrt(v32 + np.float32(schedule.BN_EPS))).astype(np.float32)
+            scs.append(sc)
+            shs.append(sh)
+    return ws, (scs if with_bn else None), (shs if with_bn else None)

@@ -1,0 +1,266 @@
+// Shared host/device helpers of the sparse front end library (sm_100a only).
+#pragma once
+
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include <atomic>
+#include <vector>
+
+#include "sessd.h"
+
+namespace sessd {
+
+constexpr uint32_t kEmpty = 0xFFFFFFFFu;   // empty key / unset rank in a coordinate table
+constexpr size_t kAlign = 256;             // sub-buffer alignment inside a workspace
+constexpr int kChunk = 1024;               // entries per compaction chunk (256 threads x 4)
+constexpr int kThreads = 256;
+constexpr int kMaxBatch = 4096;
+
+// ---- host side ---------------------------------------------------------------------------
+
+extern std::atomic<uint64_t> g_launches;
+void set_cuda_error(cudaError_t e, const char* what);
+
+// Optional per-launch timing: while a recorder is installed on the calling thread, every launch
+// made through SESSD_LAUNCH is bracketed by two events on its stream.
+struct StageRecorder {
+    std::vector<cudaEvent_t> events;   // 2 per launch
+    std::vector<const char*> names;
+    void before(cudaStream_t s);
+    void after(const char* name, cudaStream_t s);
+};
+extern thread_local StageRecorder* g_recorder;
+
+#define SESSD_CUDA(call)                                   \
+    do {                                                   \
+        cudaError_t e__ = (call);                          \
+        if (e__ != cudaSuccess) {                          \
+            ::sessd::set_cuda_error(e__, #call);           \
+            return SESSD_ERR_CUDA;                         \
+        }                                                  \
+    } while (0)
+
+// Launches `kernel` and accounts for it; evaluates to the launch error.
+#define SESSD_LAUNCH(kernel, grid, block, smem, stream, ...)                 \
+    do {                                                                     \
+        if (::sessd::g_recorder) ::sessd::g_recorder->before(stream);        \
+        kernel<<<(grid), (block), (smem), (stream)>>>(__VA_ARGS__);          \
+        ::sessd::g_launches.fetch_add(1, std::memory_order_relaxed);         \
+        if (::sessd::g_recorder) ::sessd::g_recorder->after(#kernel, stream);\
+        SESSD_CUDA(cudaGetLastError());                                      \
+    } while (0)
+
+// Number of SMs of the current device (cached per device).
+int sm_count();
+// Grid for a persistent grid-stride kernel: `per_sm` blocks on every SM.
+inline int persistent_grid(int per_sm) { return sm_count() * per_sm; }
+
+// Two-pass workspace layout: with base == nullptr it only measures.
+struct Bump {
+    char* base;
+    size_t off;
+    explicit Bump(void* b) : base(static_cast<char*>(b)), off(0) {}
+    template <typename T>
+    T* take(size_t count) {
+        off = (off + kAlign - 1) / kAlign * kAlign;
+        T* p = base ? reinterpret_cast<T*>(base + off) : nullptr;
+        off += count * sizeof(T);
+        return p;
+    }
+    size_t total() const { return (off + kAlign - 1) / kAlign * kAlign; }
+};
+
+inline uint32_t pow2_at_least(uint64_t v) {
+    uint32_t c = 64;
+    while (c < v) c <<= 1;
+    return c;
+}
+inline int ilog2(uint32_t v) {
+    int l = 0;
+    while ((1u << l) < v) ++l;
+    return l;
+}
+
+// One open-addressing coordinate table per frame: frame b owns slots [b*cap, (b+1)*cap).
+// keys: linear cell index inside the frame's grid, kEmpty when free.
+// rank: smallest producer index seen for the key (drives deterministic numbering); stride
+//       `rank_stride` between consecutive slots so that the voxeliser's per-slot point lists
+//       (whose first element is that minimum) can serve as the rank array.
+// vals: row index of the key, -1 when the key has no row.
+struct Table {
+    uint32_t* keys;
+    uint32_t* rank;
+    int32_t* vals;
+    uint32_t cap;       // power of two
+    int shift;          // 32 - log2(cap)
+    int rank_stride;
+};
+
+// Geometry of one sparse convolution (z, y, x order everywhere).
+struct ConvGeom {
+    int K[3], S[3], P[3];
+    int dil;
+    int in_shape[3];
+    int out_shape[3];
+    int kvol;
+    int span_max[3];  // most candidate outputs one input can have per axis
+    int ncand;        // product of span_max
+};
+
+// ---- device side -------------------------------------------------------------------------
+
+__device__ __forceinline__ uint32_t hash_slot(uint32_t key, int shift) {
+    return (key * 0x9E3779B1u) >> shift;
+}
+
+// Finds or claims the slot of `key`. Returns the slot index inside the frame's table or -1
+// when `cap` probes found neither the key nor a free slot.
+__device__ __forceinline__ int table_insert(uint32_t* keys, uint32_t cap, int shift, uint32_t key) {
+    uint32_t h = hash_slot(key, shift);
+    for (uint32_t probe = 0; probe < cap; ++probe) {
+        uint32_t cur = keys[h];
+        if (cur == key) return (int)h;
+        if (cur == kEmpty) {
+            uint32_t old = atomicCAS(&keys[h], kEmpty, key);
+            if (old == kEmpty || old == key) return (int)h;
+        }
+        h = (h + 1) & (cap - 1);
+    }
+    return -1;
+}
+
+__device__ __forceinline__ int table_find(const uint32_t* __restrict__ keys, uint32_t cap, int shift, uint32_t key) {
+    uint32_t h = hash_slot(key, shift);
+    for (uint32_t probe = 0; probe < cap; ++probe) {
+        uint32_t cur = __ldg(&keys[h]);
+        if (cur == key) return (int)h;
+        if (cur == kEmpty) return -1;
+        h = (h + 1) & (cap - 1);
+    }
+    return -1;
+}
+
+// Exclusive prefix sum of `v` over the block (blockDim.x == kThreads); *total gets the block sum.
+__device__ __forceinline__ int block_exclusive_scan(int v, int* total) {
+    __shared__ int warp_sums[kThreads / 32];
+    const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+    int incl = v;
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) {
+        int t = __shfl_up_sync(0xFFFFFFFFu, incl, d);
+        if (lane >= d) incl += t;
+    }
+    __syncthreads();  // protects warp_sums against a previous call
+    if (lane == 31) warp_sums[wid] = incl;
+    __syncthreads();
+    int base = 0, sum = 0;
+#pragma unroll
+    for (int w = 0; w < kThreads / 32; ++w) {
+        int s = warp_sums[w];
+        if (w < wid) base += s;
+        sum += s;
+    }
+    *total = sum;
+    return base + incl - v;
+}
+
+__device__ __forceinline__ int block_sum(int v) {
+    int total;
+    block_exclusive_scan(v, &total);
+    return total;
+}
+
+// ---- pieces shared between translation units --------------------------------------------
+
+// Ordered-unique numbering. Entry e of frame b (e < entries(b)) points at table slot
+// slot_of[b][e] (or -1). The entry whose index equals the slot's rank owns the slot; owners are
+// numbered 0,1,2,... in entry order. count pass + emit pass, no block waits on another block.
+struct NumberingArgs {
+    const int32_t* slot_of;     // [B][entry_stride]
+    int64_t entry_stride;
+    const int32_t* entry_count; // [B] device counts (points_size or voxel_num)
+    int entry_mul;              // entries(b) = min(entry_count[b], entry_limit) * entry_mul
+    int entry_limit;
+    int32_t* chunk_counts;      // [B][chunks_per_frame]
+    int chunks_per_frame;
+    int batch;
+};
+
+int launch_count_owners(const NumberingArgs& a, const Table& t, cudaStream_t stream);
+
+// Zeroes rows [voxel_num[b], max_voxels) of a [B][max_voxels][row_bytes] tensor (row_bytes % 4 == 0).
+int launch_zero_tail(void* tensor, int row_bytes, const int32_t* voxel_num, int batch, int max_voxels,
+                     cudaStream_t stream);
+int launch_fill_zero(void* ptr, size_t bytes, cudaStream_t stream);  // bytes % 16 == 0, ptr 16-byte aligned
+int launch_fill_ones(void* ptr, size_t bytes, cudaStream_t stream);  // every byte 0xFF; same constraints
+
+// rulebook.cu
+int conv_geom_from_params(const sessd_conv_params* p, ConvGeom* g);
+int launch_table_build(const int32_t* coors, const int32_t* voxel_num, int batch, int max_voxels, const int shape[3],
+                       const Table& t, int32_t* status, cudaStream_t stream);
+int launch_nbr_build(const int32_t* out_coors, const int32_t* out_num, int batch, int max_voxels, const ConvGeom& g,
+                     const Table& in_table, int32_t* nbr, cudaStream_t stream);
+int launch_spconv_outputs(const int32_t* in_coors, const int32_t* in_num, int batch, int max_voxels, const ConvGeom& g,
+                          const Table& out_table, int32_t* slot_of, int32_t* chunk_counts, int chunks_per_frame,
+                          int32_t* out_coors, int32_t* out_num, int32_t* status, cudaStream_t stream);
+inline int spconv_chunks_per_frame(int max_voxels, const ConvGeom& g) {
+    return (int)(((int64_t)max_voxels * g.ncand + kChunk - 1) / kChunk);
+}
+
+// conv_simt.cu
+struct ConvLaunch {
+    const void* in;        // [B][max_voxels][Cin]
+    void* out;             // [B][max_voxels][Cout]
+    const int32_t* nbr;    // [B][kvol][max_voxels]
+    const int32_t* out_num;// [B]
+    const void* weights;   // [kvol][Cin][Cout] in the feature dtype
+    const void* umma_weights; // fp16 weights pre-tiled for the tensor-core kernel, or null
+    const float* scale;    // [Cout] or null
+    const float* shift;    // [Cout] or null
+    int relu;
+    int batch, max_voxels, kvol, cin, cout, dtype;
+    // Optional fused BEV scatter (last layer): when dense != null the result row is also written to
+    // dense[b][c*D + z][y][x] using out_coors.
+    void* dense;
+    const int32_t* out_coors;
+    int D, H, W;
+};
+int launch_conv_simt(const ConvLaunch& c, cudaStream_t stream);
+bool conv_simt_supported(int cin, int cout);
+
+// conv_umma.cu (tcgen05 implicit GEMM, fp16 storage)
+bool conv_umma_supported(int cin, int cout);
+int conv_umma_pack_weights(const float* weights, int kvol, int cin, int cout, void** device_out);
+int launch_conv_umma(const ConvLaunch& c, cudaStream_t stream);
+
+// sparse2dense.cu
+int launch_sparse2dense(const void* feat, const int32_t* coors, const int32_t* voxel_num, int batch, int max_voxels,
+                        int C, int D, int H, int W, int dtype, void* dense, cudaStream_t stream);
+
+// voxelize.cu
+struct VoxelWorkspace {
+    int32_t* status;
+    Table table;          // rank = per-slot sorted point list [cap][max_pts]
+    int32_t* pt_slot;     // [B][max_points]
+    int32_t* chunk_counts;// [B][chunks]
+    int32_t* num_points;  // [B][max_voxels]
+    int chunks;
+    size_t table_bytes;   // bytes to set to 0xFF before a call (keys + point lists)
+    void* table_base;
+};
+void voxel_workspace_layout(Bump& bump, const sessd_voxel_params* p, int batch, int max_points, VoxelWorkspace* w);
+int voxelize_run(const sessd_voxel_params* p, int batch, int max_points, int out_dtype, const float* points,
+                 const int32_t* points_size, void* voxels, int32_t* coors, int32_t* voxel_num, const VoxelWorkspace& w,
+                 bool zero_tail, cudaStream_t stream);
+
+struct sessd_conv_weights_impl {
+    void* w;        // device, [kvol][Cin][Cout] in dtype
+    void* umma_w;   // device, tensor-core tiling of the same weights (fp16) or null
+    float* scale;   // device or null
+    float* shift;   // device or null
+    int relu, dtype, kvol, cin, cout;
+};
+
+}  // namespace sessd

@@ -1,0 +1,186 @@
+// Output-stationary sparse convolution on CUDA cores (fp32 and fp16 storage, fp32 accumulate).
+//
+// Replaces the reference's per-offset gather / multiply / atomicAdd kernel, launched kvol times per
+// layer with one thread per rulebook pair and Cout global atomics per pair
+// (submConv3dlayer.cu:479-518, :632-638). Here one launch covers the layer: a thread owns CO_T
+// output channels of one output row, walks the row's kvol neighbour slots, and for each present
+// neighbour accumulates s = sum_ci in[ci]*W[k][ci][co] as one fused-multiply-add chain (ci ascending),
+// then acc += s with k ascending. That is the arithmetic of the reference kernel with the order of
+// the atomic additions fixed, so fp32 results are reproducible bit for bit. BatchNorm scale/shift and
+// ReLU (a separate TensorRT scale + activation layer in the reference, se-ssd-ai-trt.cpp:808-856)
+// run in the epilogue, and the last layer can scatter straight into the dense BEV map.
+//
+// This path serves the memory-bound small-channel layers (4->16, 16->16, 16->32) and every fp32 layer.
+#include "common.cuh"
+
+namespace sessd {
+
+namespace {
+
+template <typename T, int N>
+struct RowLoader;
+
+template <int N>
+struct RowLoader<float, N> {
+    static __device__ __forceinline__ void load(const float* __restrict__ p, float (&x)[N]) {
+        static_assert(N % 4 == 0, "row length must be a multiple of 4");
+        const float4* v = reinterpret_cast<const float4*>(p);
+#pragma unroll
+        for (int i = 0; i < N / 4; ++i) {
+            const float4 t = __ldg(v + i);
+            x[4 * i + 0] = t.x; x[4 * i + 1] = t.y; x[4 * i + 2] = t.z; x[4 * i + 3] = t.w;
+        }
+    }
+};
+
+template <int N>
+struct RowLoader<__half, N> {
+    static __device__ __forceinline__ void load(const __half* __restrict__ p, float (&x)[N]) {
+        static_assert(N % 4 == 0, "row length must be a multiple of 4");
+        if constexpr (N % 8 == 0) {
+            const uint4* v = reinterpret_cast<const uint4*>(p);
+#pragma unroll
+            for (int i = 0; i < N / 8; ++i) {
+                const uint4 t = __ldg(v + i);
+                const __half2* h = reinterpret_cast<const __half2*>(&t);
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const float2 f = __half22float2(h[j]);
+                    x[8 * i + 2 * j] = f.x; x[8 * i + 2 * j + 1] = f.y;
+                }
+            }
+        } else {
+            const uint2* v = reinterpret_cast<const uint2*>(p);
+#pragma unroll
+            for (int i = 0; i < N / 4; ++i) {
+                const uint2 t = __ldg(v + i);
+                const __half2* h = reinterpret_cast<const __half2*>(&t);
+                const float2 a = __half22float2(h[0]), b = __half22float2(h[1]);
+                x[4 * i] = a.x; x[4 * i + 1] = a.y; x[4 * i + 2] = b.x; x[4 * i + 3] = b.y;
+            }
+        }
+    }
+};
+
+template <typename T, int N>
+__device__ __forceinline__ void store_row(T* __restrict__ p, const float (&y)[N]) {
+    if constexpr (sizeof(T) == 4) {
+        float4* v = reinterpret_cast<float4*>(p);
+#pragma unroll
+        for (int i = 0; i < N / 4; ++i) v[i] = make_float4(y[4 * i], y[4 * i + 1], y[4 * i + 2], y[4 * i + 3]);
+    } else {
+        uint4* v = reinterpret_cast<uint4*>(p);
+#pragma unroll
+        for (int i = 0; i < N / 8; ++i) {
+            uint4 t;
+            __half2* h = reinterpret_cast<__half2*>(&t);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) h[j] = __floats2half2_rn(y[8 * i + 2 * j], y[8 * i + 2 * j + 1]);
+            v[i] = t;
+        }
+    }
+}
+
+template <typename T>
+__device__ __forceinline__ T from_float(float v);
+template <>
+__device__ __forceinline__ float from_float<float>(float v) { return v; }
+template <>
+__device__ __forceinline__ __half from_float<__half>(float v) { return __float2half_rn(v); }
+
+constexpr int CO_T = 16;  // output channels per thread
+
+template <typename T, int CIN, int COUT>
+__global__ void __launch_bounds__(kThreads)
+conv_simt_kernel(const T* __restrict__ in, T* __restrict__ out, const int32_t* __restrict__ nbr,
+                 const int32_t* __restrict__ out_num, const T* __restrict__ weights, const float* __restrict__ scale,
+                 const float* __restrict__ shift, int relu, int batch, int max_voxels, int kvol,
+                 T* __restrict__ dense, const int4* __restrict__ out_coors, int D, int H, int W) {
+    constexpr int TPR = COUT / CO_T;          // threads per output row
+    constexpr int ROWS = kThreads / TPR;      // rows per block iteration
+    const int chunks = (max_voxels + ROWS - 1) / ROWS;
+    const int items = batch * chunks;
+    const int cg = threadIdx.x % TPR;
+    for (int it = blockIdx.x; it < items; it += gridDim.x) {
+        const int b = it / chunks;
+        const int o = (it - b * chunks) * ROWS + threadIdx.x / TPR;
+        int n = out_num[b];
+        n = n > max_voxels ? max_voxels : n;
+        if (o >= n) continue;
+        float acc[CO_T];
+#pragma unroll
+        for (int c = 0; c < CO_T; ++c) acc[c] = 0.f;
+        const int32_t* nb = nbr + (size_t)b * kvol * max_voxels + o;
+        const T* in_b = in + (size_t)b * max_voxels * CIN;
+        for (int k = 0; k < kvol; ++k) {
+            const int idx = __ldg(nb + (size_t)k * max_voxels);
+            if (idx < 0) continue;
+            float x[CIN];
+            RowLoader<T, CIN>::load(in_b + (size_t)idx * CIN, x);
+            float s[CO_T];
+#pragma unroll
+            for (int c = 0; c < CO_T; ++c) s[c] = 0.f;
+            const T* wk = weights + (size_t)k * CIN * COUT + cg * CO_T;
+#pragma unroll
+            for (int ci = 0; ci < CIN; ++ci) {
+                float w[CO_T];
+                RowLoader<T, CO_T>::load(wk + ci * COUT, w);
+#pragma unroll
+                for (int c = 0; c < CO_T; ++c) s[c] = fmaf(x[ci], w[c], s[c]);
+            }
+#pragma unroll
+            for (int c = 0; c < CO_T; ++c) acc[c] = __fadd_rn(acc[c], s[c]);
+        }
+#pragma unroll
+        for (int c = 0; c < CO_T; ++c) {
+            float v = acc[c];
+            if (scale) v = fmaf(v, __ldg(scale + cg * CO_T + c), shift ? __ldg(shift + cg * CO_T + c) : 0.f);
+            if (relu) v = v > 0.f ? v : 0.f;
+            acc[c] = v;
+        }
+        store_row<T, CO_T>(out + ((size_t)b * max_voxels + o) * COUT + cg * CO_T, acc);
+        if (dense) {
+            // Fused BEV scatter (sparse2Dense.cu:201-206): channel c*D + z, pixel (y, x).
+            const int4 c4 = __ldg(&out_coors[(size_t)b * max_voxels + o]);
+            T* d = dense + (size_t)b * COUT * D * H * W + ((size_t)c4.y * H + c4.z) * W + c4.w;
+#pragma unroll
+            for (int c = 0; c < CO_T; ++c) d[(size_t)(cg * CO_T + c) * D * H * W] = from_float<T>(acc[c]);
+        }
+    }
+}
+
+template <typename T, int CIN, int COUT>
+int launch_one(const ConvLaunch& c, cudaStream_t stream) {
+    SESSD_LAUNCH((conv_simt_kernel<T, CIN, COUT>), persistent_grid(4), kThreads, 0, stream,
+                 static_cast<const T*>(c.in), static_cast<T*>(c.out), c.nbr, c.out_num,
+                 static_cast<const T*>(c.weights), c.scale, c.shift, c.relu, c.batch, c.max_voxels, c.kvol,
+                 static_cast<T*>(c.dense), reinterpret_cast<const int4*>(c.out_coors), c.D, c.H, c.W);
+    return SESSD_OK;
+}
+
+template <typename T>
+int dispatch(const ConvLaunch& c, cudaStream_t stream) {
+#define SESSD_CASE(CI, CO) \
+    if (c.cin == CI && c.cout == CO) return launch_one<T, CI, CO>(c, stream);
+    SESSD_CASE(4, 16)
+    SESSD_CASE(16, 16)
+    SESSD_CASE(16, 32)
+    SESSD_CASE(32, 32)
+    SESSD_CASE(32, 64)
+    SESSD_CASE(64, 64)
+#undef SESSD_CASE
+    return SESSD_ERR_UNSUPPORTED;
+}
+
+}  // namespace
+
+bool conv_simt_supported(int cin, int cout) {
+    return (cin == 4 && cout == 16) || (cin == 16 && (cout == 16 || cout == 32)) || (cin == 32 && (cout == 32 || cout == 64)) ||
+           (cin == 64 && cout == 64);
+}
+
+int launch_conv_simt(const ConvLaunch& c, cudaStream_t stream) {
+    return c.dtype == SESSD_F32 ? dispatch<float>(c, stream) : dispatch<__half>(c, stream);
+}
+
+}  // namespace sessd

@@ -1,0 +1,245 @@
+// Rulebook construction for submanifold and strided sparse convolutions.
+//
+// The reference builds, in every plugin call, a dense index grid (up to 369 MB, reset with
+// cudaMemset), a candidate list per voxel and an input-stationary pair list per kernel offset
+// (submConv3dlayer.cu:271-459, sparseConv3dlayer.cu:310-555). Here the active coordinates of a
+// frame live in an open-addressing table (a few hundred KB), and the rulebook is kept in
+// output-stationary form: nbr[b][k][o] = input row that feeds output row o through kernel offset k,
+// or -1. Pair (k, i, o) of the reference exists exactly when nbr[b][k][o] == i, because
+// k = in - out*stride + pad per axis (submConv3dlayer.cu:328-329) and input rows are unique.
+#include "numbering.cuh"
+
+namespace sessd {
+
+namespace {
+
+__global__ void __launch_bounds__(kThreads)
+table_build_kernel(const int4* __restrict__ coors, const int32_t* __restrict__ voxel_num, int batch, int max_voxels,
+                   int Z, int Y, int X, Table t, int32_t* status) {
+    const int chunks = (max_voxels + kThreads - 1) / kThreads;
+    const int items = batch * chunks;
+    for (int it = blockIdx.x; it < items; it += gridDim.x) {
+        const int b = it / chunks;
+        const int i = (it - b * chunks) * kThreads + threadIdx.x;
+        int n = voxel_num[b];
+        n = n > max_voxels ? max_voxels : n;
+        if (i >= n) continue;
+        const int4 c = __ldg(&coors[(size_t)b * max_voxels + i]);  // (b, z, y, x)
+        if (c.y < 0 || c.y >= Z || c.z < 0 || c.z >= Y || c.w < 0 || c.w >= X) {
+            atomicOr(status, SESSD_STATUS_BAD_COORD);
+            continue;
+        }
+        const uint32_t key = ((uint32_t)c.y * Y + c.z) * X + c.w;
+        const int slot = table_insert(t.keys + (size_t)b * t.cap, t.cap, t.shift, key);
+        if (slot < 0) {
+            atomicOr(status, SESSD_STATUS_HASH_FULL);
+            continue;
+        }
+        // Duplicate coordinates (the reference's grid keeps whichever write lands last,
+        // submConv3dlayer.cu:457) resolve to the highest row here.
+        atomicMax(&t.vals[(size_t)b * t.cap + slot], i);
+    }
+}
+
+// One thread per (offset k, output row o); threads of a warp share k and walk consecutive rows, so
+// the writes to nbr[b][k][*] are coalesced.
+__global__ void __launch_bounds__(kThreads)
+nbr_build_kernel(const int4* __restrict__ out_coors, const int32_t* __restrict__ out_num, int batch, int max_voxels,
+                 ConvGeom g, Table in_table, int32_t* __restrict__ nbr) {
+    const int chunks = (max_voxels + kThreads - 1) / kThreads;
+    const int items = batch * g.kvol * chunks;
+    const int k12 = g.K[1] * g.K[2];
+    for (int it = blockIdx.x; it < items; it += gridDim.x) {
+        const int b = it / (g.kvol * chunks);
+        const int r = it - b * (g.kvol * chunks);
+        const int k = r / chunks;
+        const int o = (r - k * chunks) * kThreads + threadIdx.x;
+        int n = out_num[b];
+        n = n > max_voxels ? max_voxels : n;
+        if (o >= n) continue;
+        const int4 c = __ldg(&out_coors[(size_t)b * max_voxels + o]);
+        const int kz = k / k12, ky = (k - kz * k12) / g.K[2], kx = k - kz * k12 - ky * g.K[2];
+        // in = out*stride - pad + k*dilation (inverse of the offset formula at submConv3dlayer.cu:328)
+        const int iz = c.y * g.S[0] - g.P[0] + kz * g.dil;
+        const int iy = c.z * g.S[1] - g.P[1] + ky * g.dil;
+        const int ix = c.w * g.S[2] - g.P[2] + kx * g.dil;
+        int row = -1;
+        if (iz >= 0 && iz < g.in_shape[0] && iy >= 0 && iy < g.in_shape[1] && ix >= 0 && ix < g.in_shape[2]) {
+            const uint32_t key = ((uint32_t)iz * g.in_shape[1] + iy) * g.in_shape[2] + ix;
+            const int slot = table_find(in_table.keys + (size_t)b * in_table.cap, in_table.cap, in_table.shift, key);
+            if (slot >= 0) row = in_table.vals[(size_t)b * in_table.cap + slot];
+        }
+        nbr[((size_t)b * g.kvol + k) * max_voxels + o] = row;
+    }
+}
+
+// Candidate outputs of every input row of a strided convolution. Entry t = i*ncand + e, where e
+// counts this row's candidates in the reference's enumeration order (from the upper corner
+// downward, x fastest: sparseConv3dlayer.cu:351-383). Each in-bounds candidate claims its cell in
+// the output table and lowers the cell's rank to t.
+__global__ void __launch_bounds__(kThreads)
+spconv_candidates_kernel(const int4* __restrict__ in_coors, const int32_t* __restrict__ in_num, int batch,
+                         int max_voxels, ConvGeom g, Table out_table, int32_t* __restrict__ slot_of,
+                         int32_t* status) {
+    const int64_t per_frame = (int64_t)max_voxels * g.ncand;
+    const int chunks = (int)((per_frame + kThreads - 1) / kThreads);
+    const int items = batch * chunks;
+    for (int it = blockIdx.x; it < items; it += gridDim.x) {
+        const int b = it / chunks;
+        const int t = (it - b * chunks) * kThreads + threadIdx.x;
+        int n = in_num[b];
+        n = n > max_voxels ? max_voxels : n;
+        if (t >= n * g.ncand) continue;
+        const int i = t / g.ncand, e = t - i * g.ncand;
+        const int4 c4 = __ldg(&in_coors[(size_t)b * max_voxels + i]);
+        const int c[3] = {c4.y, c4.z, c4.w};
+        int hi[3], span[3];
+#pragma unroll
+        for (int j = 0; j < 3; ++j) {
+            // C integer division, as in the reference (sparseConv3dlayer.cu:339-348).
+            const int lo = (c[j] - (g.K[j] - 1) * g.dil - 1 + g.S[j] + g.P[j]) / g.S[j];
+            hi[j] = (c[j] + g.P[j]) / g.S[j];
+            span[j] = (hi[j] - lo) / g.dil + 1;
+        }
+        int slot = -1;
+        if (e < span[0] * span[1] * span[2]) {
+            const int cx = e % span[2], cy = (e / span[2]) % span[1], cz = e / (span[2] * span[1]);
+            const int oz = hi[0] - cz * g.dil, oy = hi[1] - cy * g.dil, ox = hi[2] - cx * g.dil;
+            if (oz >= 0 && oz < g.out_shape[0] && oy >= 0 && oy < g.out_shape[1] && ox >= 0 && ox < g.out_shape[2]) {
+                const uint32_t key = ((uint32_t)oz * g.out_shape[1] + oy) * g.out_shape[2] + ox;
+                slot = table_insert(out_table.keys + (size_t)b * out_table.cap, out_table.cap, out_table.shift, key);
+                if (slot < 0)
+                    atomicOr(status, SESSD_STATUS_HASH_FULL);
+                else
+                    atomicMin(&out_table.rank[(size_t)b * out_table.cap + slot], (uint32_t)t);
+            }
+        }
+        slot_of[(size_t)b * per_frame + t] = slot;
+    }
+}
+
+struct OutputEmit {
+    Table t;
+    int Yo, Xo, max_voxels;
+    int32_t* out_coors;
+    int32_t* out_num;
+    int32_t* status;
+    __device__ void frame_total(int b, int total) const {
+        out_num[b] = total > max_voxels ? max_voxels : total;
+        if (total > max_voxels) atomicOr(status, SESSD_STATUS_VOXEL_OVERFLOW);
+    }
+    __device__ void operator()(int b, int /*e*/, int slot, int id) const {
+        const size_t gslot = (size_t)b * t.cap + (uint32_t)slot;
+        if (id >= max_voxels) {
+            t.vals[gslot] = -1;
+            return;
+        }
+        t.vals[gslot] = id;
+        const uint32_t key = t.keys[gslot];
+        const int plane = Yo * Xo;
+        const int z = key / plane, rem = key - z * plane;
+        const int y = rem / Xo, x = rem - y * Xo;
+        reinterpret_cast<int4*>(out_coors)[(size_t)b * max_voxels + id] = make_int4(b, z, y, x);
+    }
+};
+
+// One block per kernel offset: compacts nbr[frame][k][*] into the reference's pair columns.
+__global__ void __launch_bounds__(kThreads)
+rulebook_export_kernel(const int32_t* __restrict__ nbr, const int32_t* __restrict__ out_num, int frame, int kvol,
+                       int max_voxels, int32_t* __restrict__ pairs, uint32_t* __restrict__ pair_num) {
+    const int k = blockIdx.x;
+    int n = out_num[frame];
+    n = n > max_voxels ? max_voxels : n;
+    const int32_t* col = nbr + ((size_t)frame * kvol + k) * max_voxels;
+    int32_t* pin = pairs + ((size_t)k * 2 + 0) * max_voxels;
+    int32_t* pout = pairs + ((size_t)k * 2 + 1) * max_voxels;
+    int base = 0;
+    for (int o0 = 0; o0 < n; o0 += kThreads) {
+        const int o = o0 + threadIdx.x;
+        const int v = o < n ? col[o] : -1;
+        int total;
+        const int pos = base + block_exclusive_scan(v >= 0 ? 1 : 0, &total);
+        if (v >= 0) {
+            pin[pos] = v;
+            pout[pos] = o;
+        }
+        base += total;
+    }
+    if (threadIdx.x == 0) pair_num[k] = (uint32_t)base;
+}
+
+}  // namespace
+
+int conv_geom_from_params(const sessd_conv_params* p, ConvGeom* g) {
+    for (int j = 0; j < 3; ++j) {
+        g->K[j] = p->ksize[j];
+        g->S[j] = p->subm ? 1 : p->stride[j];
+        g->P[j] = p->padding[j];
+        if (g->K[j] < 1 || g->K[j] > 3 || g->S[j] < 1 || g->S[j] > 3 || g->P[j] < 0 || g->P[j] > 2) return SESSD_ERR_PARAM;
+    }
+    g->dil = p->dilation < 1 ? 1 : p->dilation;
+    if (g->dil != 1) return SESSD_ERR_UNSUPPORTED;  // the reference only ever passes 1 (se-ssd-ai-trt.cpp:704)
+    g->out_shape[0] = p->out_shape_z; g->out_shape[1] = p->out_shape_y; g->out_shape[2] = p->out_shape_x;
+    if (p->subm) {
+        // SubM layers carry only out_shape in the reference (submConv3dlayer.cu:596-603).
+        for (int j = 0; j < 3; ++j) g->in_shape[j] = g->out_shape[j];
+    } else {
+        g->in_shape[0] = p->spatial_shape_z; g->in_shape[1] = p->spatial_shape_y; g->in_shape[2] = p->spatial_shape_x;
+    }
+    g->kvol = g->K[0] * g->K[1] * g->K[2];
+    g->ncand = 1;
+    for (int j = 0; j < 3; ++j) {
+        if (g->in_shape[j] < 1 || g->out_shape[j] < 1) return SESSD_ERR_PARAM;
+        g->span_max[j] = (g->K[j] - 1) / g->S[j] + 1;
+        g->ncand *= g->span_max[j];
+    }
+    const uint64_t vin = (uint64_t)g->in_shape[0] * g->in_shape[1] * g->in_shape[2];
+    const uint64_t vout = (uint64_t)g->out_shape[0] * g->out_shape[1] * g->out_shape[2];
+    if (vin >= 0xFFFFFFFFull || vout >= 0xFFFFFFFFull) return SESSD_ERR_PARAM;  // keys are 32-bit cell indices
+    return SESSD_OK;
+}
+
+int launch_table_build(const int32_t* coors, const int32_t* voxel_num, int batch, int max_voxels, const int shape[3],
+                       const Table& t, int32_t* status, cudaStream_t stream) {
+    SESSD_LAUNCH(table_build_kernel, persistent_grid(8), kThreads, 0, stream, reinterpret_cast<const int4*>(coors),
+                 voxel_num, batch, max_voxels, shape[0], shape[1], shape[2], t, status);
+    return SESSD_OK;
+}
+
+int launch_nbr_build(const int32_t* out_coors, const int32_t* out_num, int batch, int max_voxels, const ConvGeom& g,
+                     const Table& in_table, int32_t* nbr, cudaStream_t stream) {
+    SESSD_LAUNCH(nbr_build_kernel, persistent_grid(8), kThreads, 0, stream, reinterpret_cast<const int4*>(out_coors),
+                 out_num, batch, max_voxels, g, in_table, nbr);
+    return SESSD_OK;
+}
+
+int launch_spconv_outputs(const int32_t* in_coors, const int32_t* in_num, int batch, int max_voxels, const ConvGeom& g,
+                          const Table& out_table, int32_t* slot_of, int32_t* chunk_counts, int chunks_per_frame,
+                          int32_t* out_coors, int32_t* out_num, int32_t* status, cudaStream_t stream) {
+    SESSD_LAUNCH(spconv_candidates_kernel, persistent_grid(8), kThreads, 0, stream,
+                 reinterpret_cast<const int4*>(in_coors), in_num, batch, max_voxels, g, out_table, slot_of, status);
+    NumberingArgs a{};
+    a.slot_of = slot_of;
+    a.entry_stride = (int64_t)max_voxels * g.ncand;
+    a.entry_count = in_num;
+    a.entry_mul = g.ncand;
+    a.entry_limit = max_voxels;
+    a.chunk_counts = chunk_counts;
+    a.chunks_per_frame = chunks_per_frame;
+    a.batch = batch;
+    int rc = launch_count_owners(a, out_table, stream);
+    if (rc) return rc;
+    OutputEmit e{out_table, g.out_shape[1], g.out_shape[2], max_voxels, out_coors, out_num, status};
+    SESSD_LAUNCH(emit_owners_kernel<OutputEmit>, persistent_grid(8), kThreads, 0, stream, a, out_table, e);
+    return SESSD_OK;
+}
+
+int launch_rulebook_export(const int32_t* nbr, const int32_t* out_num, int frame, int kvol, int max_voxels,
+                           int32_t* pairs, uint32_t* pair_num, cudaStream_t stream) {
+    SESSD_CUDA(cudaMemsetAsync(pairs, 0xFF, sizeof(int32_t) * 2 * (size_t)kvol * max_voxels, stream));
+    SESSD_LAUNCH(rulebook_export_kernel, kvol, kThreads, 0, stream, nbr, out_num, frame, kvol, max_voxels, pairs,
+                 pair_num);
+    return SESSD_OK;
+}
+
+}  // namespace sessd

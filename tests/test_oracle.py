@@ -1,0 +1,180 @@
+"""CPU tests of the oracle itself: known answers, an independent dense brute force, golden vectors."""
+import os
+
+import numpy as np
+import pytest
+
+from conftest import canonical_rulebook
+
+KITTI0 = "/root/reference/data/kitti_training_velodyne_reduced/000000.bin"
+GOLDEN = os.path.join(os.path.dirname(__file__), "golden")
+
+
+def test_np_round_matches_numpy_rule(oracle):
+    # half-way cases go to even (voxelGenerator.cu:61-68); others round to nearest
+    for x, want in [(0.5, 0), (1.5, 2), (2.5, 2), (3.5, 4), (40.0, 40), (39.6, 40), (1407.9999, 1408), (0.49, 0)]:
+        assert oracle.np_round(x) == want
+
+
+def test_grid_size_of_reference_geometry(oracle, pkg):
+    # (70.4-0)/0.05, (40+40)/0.05, (1+3)/0.1 in fp32 -> 1408 x 1600 x 40; the conv stack then uses Z = 41
+    assert oracle.grid_size(pkg.synth.POINT_RANGE, pkg.synth.VOXEL_SIZE) == (1408, 1600, 40)
+
+
+@pytest.mark.skipif(not os.path.exists(KITTI0), reason="reference lidar frame not reachable")
+def test_known_voxel_count_of_first_reference_frame(oracle, pkg):
+    # 16825 is the only known-answer value in the reference tree (submConv3dlayer.cu:254, :618)
+    pts = np.fromfile(KITTI0, dtype=np.float32).reshape(-1, 4)
+    _, _, _, n, st = oracle.voxelize(pts, pkg.synth.POINT_RANGE, pkg.synth.VOXEL_SIZE, 60000)
+    assert (n, st) == (16825, 0)
+
+
+def test_voxelize_hand_case(oracle):
+    rng, vs = (0.0, 0.0, 0.0, 4.0, 4.0, 2.0), (1.0, 1.0, 1.0)
+    pts = np.array([
+        [0.5, 0.5, 0.5, 1.0],    # voxel (z0,y0,x0)  row 0
+        [3.5, 0.5, 1.5, 2.0],    # voxel (1,0,3)     row 1
+        [0.25, 0.75, 0.1, 3.0],  # row 0 again
+        [4.0, 0.5, 0.5, 9.0],    # x == max: dropped
+        [-0.1, 0.5, 0.5, 9.0],   # x < min: dropped
+        [0.9, 0.9, 0.9, 5.0],    # row 0
+        [0.1, 0.1, 0.1, 7.0], [0.2, 0.2, 0.2, 7.0], [0.3, 0.3, 0.3, 7.0],  # row 0: points 4,5,6 of the voxel
+        [0.4, 0.4, 0.4, 100.0],  # 7th point of row 0: beyond max 5, ignored
+    ], np.float32)
+    vox, coors, npv, n, st = oracle.voxelize(pts, rng, vs, max_voxels=8, max_pts=5)
+    assert n == 2 and st == 0
+    assert coors[:2].tolist() == [[0, 0, 0, 0], [0, 1, 0, 3]]
+    assert npv[:2].tolist() == [5, 1]
+    kept = pts[[0, 2, 5, 6, 7]]
+    want = kept[0].copy()
+    for r in kept[1:]:
+        want = want + r
+    np.testing.assert_array_equal(vox[0], want / np.float32(5))
+    np.testing.assert_array_equal(vox[1], pts[1])
+    assert not vox[2:].any() and not coors[2:].any()
+
+
+def test_voxelize_overflow_keeps_first_voxels(oracle):
+    rng, vs = (0.0, 0.0, 0.0, 8.0, 1.0, 1.0), (1.0, 1.0, 1.0)
+    pts = np.array([[x + 0.5, 0.5, 0.5, float(x)] for x in [5, 1, 7, 3, 1, 0]], np.float32)
+    vox, coors, npv, n, st = oracle.voxelize(pts, rng, vs, max_voxels=3)
+    assert n == 3 and st == oracle.VOXEL_OVERFLOW
+    assert coors[:3, 3].tolist() == [5, 1, 7] and npv[:3].tolist() == [1, 2, 1]
+
+
+def _dense_conv_bruteforce(coors, feat, W, K, S, P, in_shape, out_shape, subm):
+    """Definition-level dense evaluation: out[o] = sum_k in[o*s - p + k] W[k]; active set per the plugin rules."""
+    Cin, Cout = W.shape[1], W.shape[2]
+    dense = np.zeros(tuple(in_shape) + (Cin,), np.float64)
+    act = np.zeros(tuple(in_shape), bool)
+    for c, f in zip(coors, feat):
+        dense[c[1], c[2], c[3]] = f
+        act[c[1], c[2], c[3]] = True
+    out = {}
+    trip = []
+    for oz in range(out_shape[0]):
+        for oy in range(out_shape[1]):
+            for ox in range(out_shape[2]):
+                if subm and not act[oz, oy, ox]:
+                    continue
+                acc = np.zeros(Cout)
+                hit = False
+                for kz in range(K[0]):
+                    for ky in range(K[1]):
+                        for kx in range(K[2]):
+                            iz, iy, ix = oz * S[0] - P[0] + kz, oy * S[1] - P[1] + ky, ox * S[2] - P[2] + kx
+                            if 0 <= iz < in_shape[0] and 0 <= iy < in_shape[1] and 0 <= ix < in_shape[2] and act[iz, iy, ix]:
+                                k = (kz * K[1] + ky) * K[2] + kx
+                                acc += dense[iz, iy, ix] @ W[k].astype(np.float64)
+                                hit = True
+                                trip.append((k, (iz * in_shape[1] + iy) * in_shape[2] + ix,
+                                             (oz * out_shape[1] + oy) * out_shape[2] + ox))
+                if hit:
+                    out[(oz, oy, ox)] = acc
+    trip = np.array(sorted(trip), np.int64).reshape(-1, 3)
+    return out, trip
+
+
+CASES = [
+    # subm, K, S, P, in_shape
+    (True, (3, 3, 3), (1, 1, 1), (1, 1, 1), (4, 6, 5)),
+    (False, (3, 3, 3), (2, 2, 2), (1, 1, 1), (5, 8, 6)),
+    (False, (3, 3, 3), (2, 2, 2), (0, 1, 1), (11, 8, 6)),
+    (False, (3, 1, 1), (2, 1, 1), (0, 0, 0), (5, 6, 7)),
+]
+
+
+@pytest.mark.parametrize("subm,K,S,P,in_shape", CASES)
+def test_rulebook_and_conv_against_dense_bruteforce(oracle, subm, K, S, P, in_shape):
+    rs = np.random.RandomState(7)
+    out_shape = in_shape if subm else tuple((in_shape[j] + 2 * P[j] - K[j]) // S[j] + 1 for j in range(3))
+    vol = int(np.prod(in_shape))
+    n = vol // 3
+    cells = rs.permutation(vol)[:n]
+    coors = np.zeros((n, 4), np.int32)
+    coors[:, 1], coors[:, 2], coors[:, 3] = cells // (in_shape[1] * in_shape[2]), (cells // in_shape[2]) % in_shape[1], cells % in_shape[2]
+    Cin, Cout, maxV = 4, 16, 256
+    feat = rs.randn(n, Cin).astype(np.float32)
+    W = rs.randn(int(np.prod(K)), Cin, Cout).astype(np.float32)
+    if subm:
+        pairs, num, st = oracle.subm_rulebook(coors, n, in_shape, maxV)
+        ocoors, on = coors, n
+    else:
+        ocoors, on, pairs, num, st = oracle.spconv_rulebook(coors, n, K, S, P, out_shape, maxV)
+    assert st == 0
+    want, want_trip = _dense_conv_bruteforce(coors, feat, W, K, S, P, in_shape, out_shape, subm)
+    got_trip = canonical_rulebook(pairs, num, coors, ocoors[:on], in_shape, out_shape)
+    np.testing.assert_array_equal(got_trip, want_trip)
+    assert on == len(want)
+    out = oracle.conv_apply(feat, pairs, num, W, on)
+    out64 = oracle.conv_apply_f64(feat, pairs, num, W, on)
+    for r in range(on):
+        key = tuple(int(v) for v in ocoors[r, 1:])
+        np.testing.assert_allclose(out64[r], want[key], rtol=1e-12, atol=1e-12)
+        np.testing.assert_allclose(out[r], want[key], rtol=2e-5, atol=2e-5)
+
+
+def test_spconv_output_numbering_is_first_seen_order(oracle):
+    coors = np.array([[0, 4, 4, 4], [0, 0, 0, 0], [0, 4, 4, 5]], np.int32)
+    oc, on, pairs, num, st = oracle.spconv_rulebook(coors, 3, (3, 3, 3), (2, 2, 2), (1, 1, 1), (3, 4, 4), 64)
+    # input (4,4,4) (even coords, pad 1) has the single candidate (2,2,2); (0,0,0) -> (0,0,0); (4,4,5) -> x in {3,2}
+    assert on == 3 and st == 0
+    assert oc[0].tolist() == [0, 2, 2, 2] and oc[1].tolist() == [0, 0, 0, 0] and oc[2].tolist() == [0, 2, 2, 3]
+
+
+def test_scale_shift_relu_and_fold(oracle):
+    g, b, m, v = [np.array(t, np.float32) for t in ([1.5, 0.5], [0.1, -0.2], [0.3, 0.4], [0.25, 4.0])]
+    sc, sh = oracle.fold_bn(g, b, m, v, 1e-5)
+    np.testing.assert_allclose(sc, g / np.sqrt(v + 1e-5), rtol=1e-6)
+    np.testing.assert_allclose(sh, b - m * g / np.sqrt(v + 1e-5), rtol=1e-6)
+    x = np.array([[1.0, -3.0], [-1.0, 2.0]], np.float32)
+    y = oracle.scale_shift_relu(x, sc, sh)
+    np.testing.assert_allclose(y, np.maximum(0, x * sc + sh), rtol=1e-6)
+
+
+def test_sparse2dense_layout(oracle):
+    feat = np.arange(2 * 3, dtype=np.float32).reshape(2, 3) + 1
+    coors = np.array([[0, 1, 2, 3], [0, 0, 0, 1]], np.int32)
+    d = oracle.sparse2dense(feat, coors, 2, 3, 2, 4, 5)
+    assert d.shape == (1, 6, 4, 5)
+    for c in range(3):
+        assert d[0, c * 2 + 1, 2, 3] == feat[0, c] and d[0, c * 2 + 0, 0, 1] == feat[1, c]
+    assert np.count_nonzero(d) == 6
+
+
+def test_golden_vectors(oracle, pkg):
+    """The committed fixtures (tests/golden/make_golden.py) pin the oracle against silent drift."""
+    g = np.load(os.path.join(GOLDEN, "front_end_small.npz"))
+    import make_golden_inputs as mk
+
+    case = mk.small_case(pkg)
+    r = oracle.front_end(case["points"], case["range"], case["voxel"], case["max_voxels"], case["layers"],
+                         np.concatenate([w.ravel() for w in case["weights"]]), np.concatenate(case["scale"]),
+                         np.concatenate(case["shift"]), fp16=False, bev=case["bev"])
+    np.testing.assert_array_equal(r["layer_rows"], g["layer_rows"])
+    np.testing.assert_array_equal(r["layer_pairs"], g["layer_pairs"])
+    np.testing.assert_array_equal(r["coors"], g["coors"])
+    np.testing.assert_array_equal(r["feat"], g["feat"])
+    nz = np.flatnonzero(r["dense"])
+    np.testing.assert_array_equal(nz, g["dense_nz"])
+    np.testing.assert_array_equal(r["dense"].ravel()[nz], g["dense_val"])
