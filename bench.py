@@ -1,0 +1,362 @@
+#!/usr/bin/env python
+"""Benchmark of the sparse 3D front end (voxelise -> 14 sparse conv layers -> dense BEV, fp16).
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload sweep|single]
+
+One process per GPU (torchrun sets RANK / LOCAL_RANK / WORLD_SIZE for N > 1). A step is one pass over
+the rank's shard of frames (default: 512 synthetic 120,000-point frames per GPU, the throughput-sweep
+configuration). Frames are independent, so ranks exchange nothing on the data path; the process group
+only carries the barrier and the max-over-ranks of the device time. Rank 0 prints one JSON line.
+
+--impl reference times the CPU restatement of the reference plugins (oracle/, all host threads) on a
+bounded sample of the same frames: the reference itself has no CPU implementation and cannot be built
+without TensorRT.
+"""
+from __future__ import annotations
+
+import argparse
+import importlib.util
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+METRIC = "frames/sec (voxelize + sparse 3D backbone + dense BEV, fp16)"
+
+
+def load_package():
+    name = "se_ssd_ai_trt_b200"
+    if name in sys.modules:
+        return sys.modules[name]
+    path = os.path.join(ROOT, "se-ssd-ai-trt_b200", "__init__.py")
+    spec = importlib.util.spec_from_file_location(name, path, submodule_search_locations=[os.path.dirname(path)])
+    mod = importlib.util.module_from_spec(spec)
+    sys.modules[name] = mod
+    spec.loader.exec_module(mod)
+    return mod
+
+
+WORKLOADS = {
+    # name: (points per frame, object clusters, frames per GPU per step, max_voxels, frames per launch group)
+    "sweep": dict(points=120000, boxes=40, frames=512, max_voxels=200000, batch=16,
+                  desc="throughput sweep: 512 frames x 120,000 points per GPU"),
+    "single": dict(points=20000, boxes=15, frames=2048, max_voxels=60000, batch=32,
+                   desc="20,000-point frames (single-frame backbone case), 2048 per GPU"),
+}
+
+
+def make_frames(pkg, wl, nframes, first_index, threads=8):
+    """Seeded synthetic frames [nframes, P, 4] (+ sizes); stands in for the reference's KITTI loop."""
+    P = wl["points"]
+    out = np.empty((nframes, P, 4), np.float32)
+
+    def work(lo, hi):
+        for f in range(lo, hi):
+            seed = pkg.sharding.frame_seed(first_index + f)
+            out[f] = pkg.synth.lidar_frame(seed, n_points=P, n_boxes=wl["boxes"])
+
+    step = (nframes + threads - 1) // threads
+    ts = [threading.Thread(target=work, args=(i, min(nframes, i + step))) for i in range(0, nframes, step)]
+    [t.start() for t in ts]
+    [t.join() for t in ts]
+    return out, np.full(nframes, P, np.int32)
+
+
+class ClockSampler:
+    """Samples nvidia-smi clocks / throttle reasons of one GPU while the timed region runs."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index, self.proc, self.lines = index, None, []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}",
+                                          "--format=csv,noheader,nounits", "-lms", "200"], stdout=subprocess.PIPE,
+                                         stderr=subprocess.DEVNULL, text=True)
+            self.t = threading.Thread(target=self._read, daemon=True)
+            self.t.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if not self.proc:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        for ln in self.lines:
+            p = [t.strip() for t in ln.split(",")]
+            if len(p) < 8:
+                continue
+            try:
+                sm.append(float(p[0]))
+                mx.append(float(p[1]))
+            except ValueError:
+                continue
+            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), p[4:8]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            p = json.load(f)
+        return dict(hbm=float(p["hbm_gbs"]), tensor=float(p["bf16_tflops"]),
+                    tensor_sustained=float(p.get("bf16_tflops_sustained", p["bf16_tflops"])), source="measured")
+    return dict(hbm=6650.0, tensor=1590.0, tensor_sustained=1400.0, source="fallback")
+
+
+def layer_costs(pkg, rows_in, rows_out, pairs, esize=2):
+    """Algorithmic bytes and flops per conv layer for one frame set ('Roofline arithmetic')."""
+    out = []
+    for l, ni, no, p in zip(pkg.schedule.LAYERS, rows_in, rows_out, pairs):
+        b = ni * l.cin * esize + no * l.cout * esize + l.kvol * l.cin * l.cout * esize + 16 * ni
+        if not l.subm:
+            b += 16 * no + 4
+        out.append(dict(name=l.name, bytes=float(b), flops=2.0 * p * l.cin * l.cout))
+    return out
+
+
+def cpu_baseline(pkg, wl, frames, sizes, seconds_hint=20.0):
+    """Times the CPU oracle (all host threads) on a bounded sample of the same frames."""
+    sys.path.insert(0, ROOT)
+    from oracle import binding as oracle
+
+    threads = oracle.hardware_threads() or os.cpu_count() or 1
+    per_frame = 5.5 * wl["points"] / 120000.0      # single-thread seconds per frame, measured once offline
+    n = int(max(threads, min(len(frames), round(seconds_hint / per_frame * threads))))
+    n = min(n, len(frames))
+    w, sc, sh = pkg.random_weights()
+    sec, status = oracle.front_end_frames(frames[:n], sizes[:n], pkg.synth.POINT_RANGE, pkg.synth.VOXEL_SIZE,
+                                          wl["max_voxels"], pkg.schedule.LAYERS,
+                                          np.concatenate([t.ravel() for t in w]), np.concatenate(sc),
+                                          np.concatenate(sh), fp16=True, nthreads=threads, with_dense=True)
+    return dict(value=n / sec, unit="frames/s", cores=threads, kind="port",
+                sample=f"{n} of the step's frames, {threads} host threads, fp16-storage emulation, {sec:.1f} s",
+                status=status), n, sec
+
+
+def run_reference(args, pkg, wl, rank, world):
+    """--impl reference: the CPU restatement of the reference plugins, timed on the host cores."""
+    if rank != 0:
+        return
+    threads = os.cpu_count() or 1
+    per_step = max(threads, 8)
+    frames, sizes = make_frames(pkg, wl, min(wl["frames"], per_step), 0)
+    total_s, total_f, info = 0.0, 0, None
+    for step in range(args.warmup + args.steps):
+        info, n, sec = cpu_baseline(pkg, wl, frames, sizes, seconds_hint=1e-9)
+        if step >= args.warmup:
+            total_s += sec
+            total_f += n
+        if step == 0 and sec * (args.warmup + args.steps) > 240:   # keep the whole run within minutes
+            args.steps = max(1, int(240 / sec) - args.warmup)
+            if step >= args.warmup + args.steps:
+                break
+    value = total_f / total_s if total_s > 0 else info["value"]
+    info["value"] = value
+    line = dict(impl="reference", metric=METRIC, value=value, unit="frames/s", n_gpus=args.gpus, steps=args.steps,
+                warmup=args.warmup, ms_per_step=1000.0 * total_s / max(args.steps, 1), higher_is_better=True,
+                scaling="weak", vs_baseline=None, dtype="f16", data="synthetic",
+                config=dict(workload=args.workload, description=wl["desc"], points_per_frame=wl["points"],
+                            frames_per_step=total_f // max(args.steps, 1)),
+                cpu_baseline=info,
+                e2e=dict(value=value, unit="frames/s", h2d_bytes_per_step=0, d2h_bytes_per_step=0))
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=3)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="sweep", choices=sorted(WORKLOADS))
+    ap.add_argument("--frames", type=int, default=0, help="frames per GPU per step (default: the workload's)")
+    ap.add_argument("--batch", type=int, default=0, help="frames per launch group")
+    ap.add_argument("--streams", type=int, default=2)
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 0)
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    pkg = load_package()
+    wl = dict(WORKLOADS[args.workload])
+    if args.frames:
+        wl["frames"] = args.frames
+    if args.batch:
+        wl["batch"] = args.batch
+
+    if args.impl == "reference":
+        run_reference(args, pkg, wl, rank, world)
+        return
+
+    import torch
+    import torch.distributed as dist
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the library has no CPU path")
+    torch.cuda.set_device(local)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    pkg.lib()
+
+    F, P, B = wl["frames"], wl["points"], wl["batch"]
+    frames, sizes = make_frames(pkg, wl, F, pkg.sharding.first_frame(rank, F))
+    h_pts = torch.from_numpy(frames).pin_memory()
+    h_sizes = torch.from_numpy(sizes).pin_memory()
+    h_num = torch.zeros(F, dtype=torch.int32).pin_memory()
+    h_status = torch.zeros(F, dtype=torch.int32).pin_memory()
+    d_pts = h_pts.cuda()
+    d_sizes = h_sizes.cuda()
+
+    w, sc, sh = pkg.random_weights()
+    bb = pkg.Backbone(wl["max_voxels"], w, sc, sh, dtype=pkg.F16)
+    pipe = pkg.Pipeline(bb, B, P, nstreams=args.streams)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(max(args.warmup, 3)):
+        pipe.run_device(d_pts, d_sizes)
+    barrier()
+    sampler = ClockSampler(local)
+    sampler.start()
+    launches0 = pkg.launch_count()
+    t0 = time.perf_counter()
+    dev_ms = 0.0
+    for _ in range(args.steps):
+        dev_ms += pipe.run_device(d_pts, d_sizes)      # CUDA events on the pipeline's own streams
+    barrier()
+    wall_ms = (time.perf_counter() - t0) * 1e3
+    launches = pkg.launch_count() - launches0
+    clocks = sampler.stop()
+
+    # end to end through the host-buffer entry point: H2D of the points and D2H of counts + status inside
+    for _ in range(2):
+        pipe.run_host(h_pts, h_sizes, h_num, h_status)
+    barrier()
+    e2e_ms = 0.0
+    for _ in range(args.steps):
+        e2e_ms += pipe.run_host(h_pts, h_sizes, h_num, h_status)
+    barrier()
+    status_bits = int(np.bitwise_or.reduce(h_status.numpy()))
+
+    t = torch.tensor([dev_ms, e2e_ms, wall_ms], dtype=torch.float64, device="cuda")
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    dev_ms, e2e_ms, wall_ms = [float(v) for v in t.cpu()]
+    total_frames = F * args.steps * world
+    value = total_frames / (dev_ms / 1e3)
+    e2e = total_frames / (e2e_ms / 1e3)
+
+    line = None
+    if rank == 0:
+        # per-kernel device times of one launch group, measured with events around every launch
+        grp_pts, grp_sizes = d_pts[:B].contiguous(), d_sizes[:B].contiguous()
+        ws = torch.empty(bb.workspace_bytes(B, P), dtype=torch.uint8, device="cuda")
+        dense = torch.empty(bb.dense_shape(B), dtype=torch.float16, device="cuda")
+        bb.run(grp_pts, grp_sizes, ws, dense)
+        torch.cuda.synchronize()
+        stages = pkg.profile(lambda: bb.run(grp_pts, grp_sizes, ws, dense))
+        per_kernel = {}
+        for name, ms in stages:
+            k = per_kernel.setdefault(name.strip("()"), [0, 0.0])
+            k[0] += 1
+            k[1] += ms
+        group_ms = sum(v[1] for v in per_kernel.values())
+        # algorithmic work of that group: rows per layer from the device, pairs from the neighbour maps
+        rows_in, rows_out, pairs = [], [], pkg.pair_counts(bb, grp_pts, grp_sizes, ws, dense)
+        prev = int(bb.layer_view(ws, B, P, -1)[2].sum())
+        for i in range(len(bb.layers)):
+            n = int(bb.layer_view(ws, B, P, i)[2].sum())
+            rows_in.append(prev)
+            rows_out.append(n)
+            prev = n
+        costs = layer_costs(pkg, rows_in, rows_out, pairs)
+        pk = peaks()
+        conv_names = [n for n in per_kernel if "conv_" in n]
+        top = max(per_kernel, key=lambda n: per_kernel[n][1])
+        # every conv kernel instance is attributed the layers it ran (same order as the schedule)
+        conv_launch_order = [n.strip("()") for n, _ in stages if "conv_" in n]
+        conv_ms = [ms for n, ms in stages if "conv_" in n]
+        if "conv_" in top:
+            idx = [i for i, n in enumerate(conv_launch_order) if n == top]
+            flops = sum(costs[i]["flops"] for i in idx)
+            byts = sum(costs[i]["bytes"] for i in idx)
+            ms = sum(conv_ms[i] for i in idx)
+            tens = any(pkg.schedule.LAYERS[i].cin >= 32 for i in idx)
+            if tens:
+                ach = flops / (ms / 1e3) / 1e12
+                roof = dict(bound="tensor", achieved=ach, peak=pk["tensor_sustained"], unit="TFLOP/s",
+                            frac=ach / pk["tensor_sustained"], traffic=None)
+            else:
+                ach = byts / (ms / 1e3) / 1e9
+                roof = dict(bound="hbm", achieved=ach, peak=pk["hbm"], unit="GB/s", frac=ach / pk["hbm"], traffic=None)
+            roof.update(kernel=top, launches=len(idx), avg_launch_ms=ms / len(idx), peak_source=pk["source"])
+        else:
+            vox_rows = int(bb.layer_view(ws, B, P, -1)[2].sum())
+            byts = 16.0 * float(grp_sizes.sum()) + vox_rows * (16 + 8 + 4) + 4 * B
+            ms = per_kernel[top][1]
+            ach = byts / (ms / 1e3) / 1e9
+            roof = dict(bound="hbm", achieved=ach, peak=pk["hbm"], unit="GB/s", frac=ach / pk["hbm"], traffic=None,
+                        kernel=top, launches=per_kernel[top][0], avg_launch_ms=ms / per_kernel[top][0],
+                        peak_source=pk["source"])
+        total_flops = sum(c["flops"] for c in costs)
+        line = dict(metric=METRIC, value=value, unit="frames/s", n_gpus=world, steps=args.steps,
+                    warmup=max(args.warmup, 3), ms_per_step=dev_ms / args.steps, higher_is_better=True,
+                    scaling="weak", vs_baseline=None, dtype="f16", data="synthetic",
+                    config=dict(workload=args.workload, description=wl["desc"], points_per_frame=P,
+                                frames_per_gpu_per_step=F, frames_per_launch_group=B, streams=args.streams,
+                                max_voxels=wl["max_voxels"], layers=len(bb.layers),
+                                l2="inputs larger than L2 (points of one step: %.0f MB)" % (F * P * 16 / 1e6),
+                                parallelism=f"frames sharded over {world} GPU(s), no collective"),
+                    e2e=dict(value=e2e, unit="frames/s", h2d_bytes_per_step=F * P * 16 + F * 4,
+                             d2h_bytes_per_step=F * 4 + (F + B - 1) // B * 4),
+                    gpu_launches=int(launches), clocks=clocks, roofline=roof,
+                    wall_ms_per_step=wall_ms / args.steps, status_bits=status_bits,
+                    group_profile=dict(frames=B, total_ms=group_ms,
+                                       gflop_per_frame=total_flops / B / 1e9,
+                                       kernels={n: dict(launches=v[0], ms=round(v[1], 4)) for n, v in
+                                                sorted(per_kernel.items(), key=lambda kv: -kv[1][1])}))
+        if world == 1 and not args.no_cpu_baseline:
+            info, _, _ = cpu_baseline(pkg, wl, frames, sizes)
+            line["cpu_baseline"] = info
+        else:
+            line["cpu_baseline"] = None
+    pipe.close()
+    bb.close()
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+    if rank == 0:
+        print(json.dumps(line), flush=True)
+
+
+if __name__ == "__main__":
+    main()

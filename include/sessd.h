@@ -21,7 +21,8 @@
  *   - return value: SESSD_OK (0) or a negative sessd_error. The reference aborts the process on
  *     any CUDA error (voxelGenerator.cu:8-19); this library never aborts;
  *   - conditions only the device can see (capacity overflows) are reported as bits OR-ed into
- *     the int32 status word that occupies the first 4 bytes of the caller's workspace; it is
+ *     the int32 status word that occupies the first 4 bytes of the caller's workspace (the first
+ *     1024 bytes of every workspace are reserved for it and for counters); it is
  *     cleared at the start of every *_enqueue and may be read after the stream has been
  *     synchronised (sessd_read_status does the copy).
  */
@@ -182,6 +183,13 @@ size_t sessd_backbone_workspace_bytes(const sessd_backbone* bb, int batch, int m
 int sessd_backbone_enqueue(const sessd_backbone* bb, int batch, int max_points,
                            const void* points, const void* points_size, void* dense,
                            void* workspace, size_t workspace_bytes, void* stream);
+
+/* Same work as sessd_backbone_enqueue, plus a count of the rulebook pairs of every layer (the P of the
+ * flop count 2*P*Cin*Cout), copied to host_counts[nlayers] after synchronising the stream. For benchmarks
+ * and tests; the reference exposes the same numbers as indice_num (submConv3dlayer.cu:413). */
+int sessd_backbone_pair_counts(const sessd_backbone* bb, int batch, int max_points,
+                               const void* points, const void* points_size, void* dense,
+                               void* workspace, size_t workspace_bytes, void* stream, int64_t* host_counts);
 
 /* Device pointers (inside `workspace`) to what layer `layer` produced in the last enqueue:
  * features [B][max_voxels][Cout], coors, voxel_num. layer = -1 selects the voxeliser's outputs. */

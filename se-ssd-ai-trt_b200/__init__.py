@@ -12,7 +12,7 @@ import os
 
 import numpy as np
 
-from . import schedule, synth  # noqa: F401
+from . import schedule, sharding, synth  # noqa: F401
 from .build import LIB_PATH, build
 
 F32, F16 = 0, 1
@@ -23,7 +23,8 @@ EXPORTS = (
     "sessd_conv_weights_create", "sessd_conv_weights_destroy", "sessd_conv_workspace_bytes",
     "sessd_subm_conv_enqueue", "sessd_sparse_conv_enqueue", "sessd_conv_rulebook_export",
     "sessd_sparse2dense_enqueue", "sessd_backbone_create", "sessd_backbone_destroy",
-    "sessd_backbone_workspace_bytes", "sessd_backbone_enqueue", "sessd_backbone_layer_view",
+    "sessd_backbone_workspace_bytes", "sessd_backbone_enqueue", "sessd_backbone_pair_counts",
+    "sessd_backbone_layer_view",
     "sessd_backbone_final_level", "sessd_pipeline_create", "sessd_pipeline_destroy", "sessd_pipeline_run_host",
     "sessd_pipeline_run_device", "sessd_pipeline_dense", "sessd_pipeline_workspace", "sessd_launch_count",
     "sessd_profile_begin", "sessd_profile_end", "sessd_read_status", "sessd_last_cuda_error", "sessd_version",
@@ -385,6 +386,18 @@ def profile(fn):
         _check(n, "sessd_profile_end")
     nm = names.value.decode().split("\n")[:n]
     return [(nm[i], float(ms[i])) for i in range(min(n, cap))]
+
+
+def pair_counts(backbone: Backbone, points, points_size, workspace, dense):
+    """Runs the backbone once more and returns the number of rulebook pairs of every layer (list of int)."""
+    B, P = points.shape[0], points.shape[1]
+    out = (C.c_int64 * len(backbone.layers))()
+    _check(lib().sessd_backbone_pair_counts(backbone.handle, B, P, C.c_void_p(points.data_ptr()),
+                                            C.c_void_p(points_size.data_ptr()),
+                                            C.c_void_p(dense.data_ptr()) if dense is not None else None,
+                                            C.c_void_p(workspace.data_ptr()), C.c_size_t(workspace.numel()), _stream(),
+                                            out), "sessd_backbone_pair_counts")
+    return [int(v) for v in out]
 
 
 def launch_count() -> int:

@@ -46,10 +46,12 @@ void StageRecorder::after(const char* name, cudaStream_t s) {
 
 int launch_rulebook_export(const int32_t* nbr, const int32_t* out_num, int frame, int kvol, int max_voxels,
                            int32_t* pairs, uint32_t* pair_num, cudaStream_t stream);
+int launch_count_pairs(const int32_t* nbr, const int32_t* out_num, int batch, int max_voxels, int kvol,
+                       unsigned long long* total, cudaStream_t stream);
 
 namespace {
 
-constexpr int kStatusInts = 64;  // the status block is 256 bytes; word 0 is the status
+constexpr int kStatusInts = 256;  // status block: 1 KB; word 0 is the status, bytes 256.. hold 64 pair counters
 
 // np.round as the reference mimics it (voxelGenerator.cu:61-68).
 int np_round_f32(float x) {
@@ -564,9 +566,9 @@ size_t sessd_backbone_workspace_bytes(const sessd_backbone* bb, int batch, int m
     return bump.total();
 }
 
-int sessd_backbone_enqueue(const sessd_backbone* bb, int batch, int max_points, const void* points,
-                           const void* points_size, void* dense, void* workspace, size_t workspace_bytes,
-                           void* stream_) {
+static int backbone_enqueue_impl(const sessd_backbone* bb, int batch, int max_points, const void* points,
+                                const void* points_size, void* dense, void* workspace, size_t workspace_bytes,
+                                void* stream_, bool count_pairs) {
     if (!bb || !points || !points_size || !workspace) return SESSD_ERR_NULL;
     if (bb->has_s2d && !dense) return SESSD_ERR_NULL;
     if (!voxel_params_ok(&bb->vp, batch, max_points)) return SESSD_ERR_PARAM;
@@ -616,6 +618,11 @@ int sessd_backbone_enqueue(const sessd_backbone* bb, int batch, int max_points, 
             if (rc) return rc;
             nbr = w.nbr_strided;
         }
+        if (count_pairs) {
+            auto* counters = reinterpret_cast<unsigned long long*>(reinterpret_cast<char*>(w.status) + 256);
+            rc = launch_count_pairs(nbr, w.num[L.level_out], batch, maxV, L.g.kvol, counters + i, stream);
+            if (rc) return rc;
+        }
         ConvLaunch c{};
         c.in = cur;
         c.out = w.feat[i];
@@ -643,6 +650,26 @@ int sessd_backbone_enqueue(const sessd_backbone* bb, int batch, int max_points, 
         if (rc) return rc;
         cur = w.feat[i];
     }
+    return SESSD_OK;
+}
+
+int sessd_backbone_enqueue(const sessd_backbone* bb, int batch, int max_points, const void* points,
+                           const void* points_size, void* dense, void* workspace, size_t workspace_bytes,
+                           void* stream) {
+    return backbone_enqueue_impl(bb, batch, max_points, points, points_size, dense, workspace, workspace_bytes, stream,
+                                 false);
+}
+
+int sessd_backbone_pair_counts(const sessd_backbone* bb, int batch, int max_points, const void* points,
+                               const void* points_size, void* dense, void* workspace, size_t workspace_bytes,
+                               void* stream, int64_t* host_counts) {
+    if (!host_counts) return SESSD_ERR_NULL;
+    int rc = backbone_enqueue_impl(bb, batch, max_points, points, points_size, dense, workspace, workspace_bytes,
+                                   stream, true);
+    if (rc) return rc;
+    SESSD_CUDA(cudaStreamSynchronize(static_cast<cudaStream_t>(stream)));
+    SESSD_CUDA(cudaMemcpy(host_counts, static_cast<char*>(workspace) + 256, sizeof(int64_t) * bb->layers.size(),
+                          cudaMemcpyDeviceToHost));
     return SESSD_OK;
 }
 

@@ -168,7 +168,34 @@ rulebook_export_kernel(const int32_t* __restrict__ nbr, const int32_t* __restric
     if (threadIdx.x == 0) pair_num[k] = (uint32_t)base;
 }
 
+// Number of present neighbours (= rulebook pairs) of one layer, added to *total.
+__global__ void __launch_bounds__(kThreads)
+count_pairs_kernel(const int32_t* __restrict__ nbr, const int32_t* __restrict__ out_num, int batch, int max_voxels,
+                   int kvol, unsigned long long* total) {
+    const int chunks = (max_voxels + kThreads - 1) / kThreads;
+    const int items = batch * kvol * chunks;
+    int local = 0;
+    for (int it = blockIdx.x; it < items; it += gridDim.x) {
+        const int b = it / (kvol * chunks);
+        const int r = it - b * (kvol * chunks);
+        const int k = r / chunks;
+        const int o = (r - k * chunks) * kThreads + threadIdx.x;
+        int n = out_num[b];
+        n = n > max_voxels ? max_voxels : n;
+        if (o < n && nbr[((size_t)b * kvol + k) * max_voxels + o] >= 0) ++local;
+    }
+    const int sum = block_sum(local);
+    if (threadIdx.x == 0 && sum) atomicAdd(total, (unsigned long long)sum);
+}
+
 }  // namespace
+
+int launch_count_pairs(const int32_t* nbr, const int32_t* out_num, int batch, int max_voxels, int kvol,
+                       unsigned long long* total, cudaStream_t stream) {
+    SESSD_LAUNCH(count_pairs_kernel, persistent_grid(8), kThreads, 0, stream, nbr, out_num, batch, max_voxels, kvol,
+                 total);
+    return SESSD_OK;
+}
 
 int conv_geom_from_params(const sessd_conv_params* p, ConvGeom* g) {
     for (int j = 0; j < 3; ++j) {

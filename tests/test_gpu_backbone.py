@@ -1,0 +1,170 @@
+"""GPU parity of the fused front end (voxelise -> 14 conv layers -> dense BEV) and of Sparse2Dense."""
+import os
+
+import numpy as np
+import pytest
+
+import make_golden_inputs as mk
+from conftest import rel_err
+
+pytestmark = pytest.mark.gpu
+GOLDEN = os.path.join(os.path.dirname(__file__), "golden")
+
+
+def _oracle_layers(oracle, case, fp16):
+    """Runs the oracle layer by layer, returning (coors, n, features) after every layer."""
+    vox, coors, npv, n, st = oracle.voxelize(case["points"], case["range"], case["voxel"], case["max_voxels"])
+    feat = vox[:n]
+    if fp16:
+        feat = feat.astype(np.float16).astype(np.float32)
+    outs = [(coors[:n].copy(), n, feat)]
+    maxV = case["max_voxels"]
+    for l, W, sc, sh in zip(case["layers"], case["weights"], case["scale"], case["shift"]):
+        c, n, f = outs[-1]
+        if l.subm:
+            pairs, pnum, st = oracle.subm_rulebook(c, n, l.out_shape, maxV)
+            oc, on = c, n
+        else:
+            oc, on, pairs, pnum, st = oracle.spconv_rulebook(c, n, l.ksize, l.stride, l.padding, l.out_shape, maxV)
+            oc = oc[:on].copy()
+        y = oracle.conv_apply(f, pairs, pnum, W, on, half_inputs=fp16)
+        y = oracle.scale_shift_relu(y, sc, sh, True, half_out=fp16)
+        outs.append((oc, on, y))
+    return outs
+
+
+def _gpu_run(gpu, case, dtype, frames=None):
+    import torch
+
+    frames = frames or [case["points"]]
+    P = max(len(f) for f in frames)
+    pts = np.zeros((len(frames), P, 4), np.float32)
+    sizes = np.zeros(len(frames), np.int32)
+    for b, f in enumerate(frames):
+        pts[b, :len(f)], sizes[b] = f, len(f)
+    bb = gpu.Backbone(case["max_voxels"], case["weights"], case["scale"], case["shift"], dtype=dtype,
+                      layers=case["layers"], point_range=case["range"], voxel_size=case["voxel"])
+    dense, ws = bb.run(torch.from_numpy(pts).cuda(), torch.from_numpy(sizes).cuda())
+    torch.cuda.synchronize()
+    assert gpu.read_status(ws) == 0
+    views = [bb.layer_view(ws, len(frames), P, i) for i in range(-1, len(case["layers"]))]
+    views = [(f.float().cpu().numpy(), c.cpu().numpy(), n.cpu().numpy()) for f, c, n in views]
+    d = dense.float().cpu().numpy()
+    bb.close()
+    return d, views
+
+
+@pytest.mark.parametrize("dtype,tol", [(0, 1e-5), (1, 1e-2)])
+def test_small_backbone_every_layer(gpu, oracle, dtype, tol):
+    case = mk.small_case(gpu)
+    want = _oracle_layers(oracle, case, fp16=bool(dtype))
+    dense, views = _gpu_run(gpu, case, dtype)
+    for i, ((wc, wn, wf), (gf, gc, gn)) in enumerate(zip(want, views)):
+        assert int(gn[0]) == wn, f"layer {i - 1}"
+        np.testing.assert_array_equal(gc[0, :wn], wc)
+        err = rel_err(gf[0, :wn], wf)
+        assert err <= tol, f"layer {i - 1}: rel err {err}"
+        if dtype == 0:
+            np.testing.assert_array_equal(gf[0, :wn], wf)
+    c, n, f = want[-1]
+    Cc, D, H, W = case["bev"]
+    want_dense = oracle.sparse2dense(f, c, n, Cc, D, H, W)
+    assert rel_err(dense, want_dense) <= tol
+    assert np.count_nonzero(dense) <= np.count_nonzero(want_dense)
+
+
+def test_small_backbone_matches_committed_golden(gpu):
+    g = np.load(os.path.join(GOLDEN, "front_end_small.npz"))
+    case = mk.small_case(gpu)
+    dense, views = _gpu_run(gpu, case, 0)
+    gf, gc, gn = views[-1]
+    n = int(gn[0])
+    np.testing.assert_array_equal([int(v[2][0]) for v in views[1:]], g["layer_rows"])
+    np.testing.assert_array_equal(gc[0, :n], g["coors"])
+    np.testing.assert_allclose(gf[0, :n], g["feat"], rtol=1e-5, atol=1e-7)
+    nz = np.flatnonzero(dense)
+    np.testing.assert_array_equal(nz, g["dense_nz"])
+    np.testing.assert_allclose(dense.ravel()[nz], g["dense_val"], rtol=1e-5, atol=1e-7)
+
+
+def test_batched_frames_equal_single_frame_runs(gpu):
+    """Frames in one batch must not influence each other (they are sharded across GPUs as units)."""
+    case = mk.small_case(gpu)
+    other = mk.small_case(gpu, n_points=900, seed=123)["points"]
+    d_b, v_b = _gpu_run(gpu, case, 1, frames=[other, case["points"], np.zeros((0, 4), np.float32)])
+    d_1, v_1 = _gpu_run(gpu, case, 1)
+    np.testing.assert_array_equal(d_b[1], d_1[0])
+    assert not d_b[2].any()
+    for (fb, cb, nb), (f1, c1, n1) in zip(v_b, v_1):
+        n = int(n1[0])
+        assert int(nb[1]) == n and int(nb[2]) == 0
+        np.testing.assert_array_equal(fb[1, :n], f1[0, :n])
+        c1 = c1[0, :n].copy()
+        c1[:, 0] = 1
+        np.testing.assert_array_equal(cb[1, :n], c1)
+
+
+def test_full_size_backbone_fp16_20k_points(gpu, oracle):
+    """The single-frame backbone case at the reference's full grid, fp16, per-layer 1e-2."""
+    S = gpu.synth
+    w, sc, sh = gpu.random_weights()
+    case = dict(points=S.single_frame(), range=S.POINT_RANGE, voxel=S.VOXEL_SIZE, max_voxels=60000,
+                layers=gpu.schedule.LAYERS, weights=w, scale=sc, shift=sh, bev=(64, 2, 200, 176))
+    want = _oracle_layers(oracle, case, fp16=True)
+    dense, views = _gpu_run(gpu, case, 1)
+    for i, ((wc, wn, wf), (gf, gc, gn)) in enumerate(zip(want, views)):
+        assert int(gn[0]) == wn
+        np.testing.assert_array_equal(gc[0, :wn], wc)
+        err = rel_err(gf[0, :wn], wf)
+        assert err <= 1e-2, f"layer {i - 1}: rel err {err}"
+    c, n, f = want[-1]
+    assert rel_err(dense, oracle.sparse2dense(f, c, n, 64, 2, 200, 176)) <= 1e-2
+
+
+def test_round_trip_dense_to_sparse_at_sweep_size(gpu):
+    """Size-independent property at the 120k-point size: every active output row reappears in the BEV map
+    at channel c*D+z, pixel (y,x), and nothing else is non-zero."""
+    import torch
+
+    S = gpu.synth
+    w, sc, sh = gpu.random_weights()
+    bb = gpu.Backbone(200000, w, sc, sh, dtype=1)
+    f = S.sweep_frame(3)
+    pts = torch.from_numpy(f[None]).cuda()
+    sizes = torch.tensor([len(f)], dtype=torch.int32, device="cuda")
+    dense, ws = bb.run(pts, sizes)
+    torch.cuda.synchronize()
+    assert gpu.read_status(ws) == 0
+    feat, coors, num = bb.layer_view(ws, 1, len(f), len(bb.layers) - 1)
+    n = int(num[0])
+    c = coors[0, :n].long()
+    d = dense[0].reshape(64, 2, 200, 176)
+    got = d[:, c[:, 1], c[:, 2], c[:, 3]].T
+    assert torch.equal(got, feat[0, :n])
+    assert int((dense != 0).sum()) == int((feat[0, :n] != 0).sum())
+    # the rows are unique cells
+    key = (c[:, 1] * 200 + c[:, 2]) * 176 + c[:, 3]
+    assert key.unique().numel() == n
+    bb.close()
+
+
+@pytest.mark.parametrize("dtype", [0, 1])
+def test_sparse2dense_plugin_entry(gpu, oracle, dtype):
+    import torch
+
+    rs = np.random.RandomState(4)
+    B, V, Cc, D, H, W = 2, 512, 64, 2, 20, 16
+    feat = np.zeros((B, V, Cc), np.float32)
+    coors = np.zeros((B, V, 4), np.int32)
+    num = np.array([300, 0], np.int32)
+    cells = rs.permutation(D * H * W)[:300]
+    coors[0, :300, 1], coors[0, :300, 2], coors[0, :300, 3] = cells // (H * W), (cells // W) % H, cells % W
+    feat[0, :300] = rs.randn(300, Cc)
+    tdt = torch.float32 if dtype == 0 else torch.float16
+    p = gpu.S2DParams(W, H, D, Cc)
+    dense = gpu.sparse2dense(torch.from_numpy(feat).cuda().to(tdt), torch.from_numpy(coors).cuda(),
+                             torch.from_numpy(num).cuda(), p, dtype)
+    src = feat[0, :300].astype(np.float16).astype(np.float32) if dtype else feat[0, :300]
+    want = oracle.sparse2dense(src, coors[0], 300, Cc, D, H, W, batch=1)
+    np.testing.assert_array_equal(dense[0].float().cpu().numpy(), want[0])
+    assert not dense[1].any()
