@@ -300,12 +300,12 @@ def main():
             prev = n
         costs = layer_costs(pkg, rows_in, rows_out, pairs)
         pk = peaks()
-        conv_names = [n for n in per_kernel if "conv_" in n]
+        is_conv = lambda n: n.startswith("conv_simt") or n.startswith("conv_umma")  # noqa: E731
         top = max(per_kernel, key=lambda n: per_kernel[n][1])
         # every conv kernel instance is attributed the layers it ran (same order as the schedule)
-        conv_launch_order = [n.strip("()") for n, _ in stages if "conv_" in n]
-        conv_ms = [ms for n, ms in stages if "conv_" in n]
-        if "conv_" in top:
+        conv_launch_order = [n.strip("()") for n, _ in stages if is_conv(n)]
+        conv_ms = [ms for n, ms in stages if is_conv(n)]
+        if is_conv(top):
             idx = [i for i, n in enumerate(conv_launch_order) if n == top]
             flops = sum(costs[i]["flops"] for i in idx)
             byts = sum(costs[i]["bytes"] for i in idx)

@@ -42,15 +42,17 @@ extern thread_local StageRecorder* g_recorder;
         }                                                  \
     } while (0)
 
-// Launches `kernel` and accounts for it; evaluates to the launch error.
-#define SESSD_LAUNCH(kernel, grid, block, smem, stream, ...)                 \
+// Launches `kernel` and accounts for it under `name`; returns from the caller on a launch error.
+#define SESSD_LAUNCH_NAMED(name, kernel, grid, block, smem, stream, ...)      \
     do {                                                                     \
         if (::sessd::g_recorder) ::sessd::g_recorder->before(stream);        \
         kernel<<<(grid), (block), (smem), (stream)>>>(__VA_ARGS__);          \
         ::sessd::g_launches.fetch_add(1, std::memory_order_relaxed);         \
-        if (::sessd::g_recorder) ::sessd::g_recorder->after(#kernel, stream);\
+        if (::sessd::g_recorder) ::sessd::g_recorder->after(name, stream);   \
         SESSD_CUDA(cudaGetLastError());                                      \
     } while (0)
+#define SESSD_LAUNCH(kernel, grid, block, smem, stream, ...) \
+    SESSD_LAUNCH_NAMED(#kernel, kernel, grid, block, smem, stream, __VA_ARGS__)
 
 // Number of SMs of the current device (cached per device).
 int sm_count();

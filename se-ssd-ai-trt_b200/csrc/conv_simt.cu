@@ -11,6 +11,8 @@
 // run in the epilogue, and the last layer can scatter straight into the dense BEV map.
 //
 // This path serves the memory-bound small-channel layers (4->16, 16->16, 16->32) and every fp32 layer.
+#include <string>
+
 #include "common.cuh"
 
 namespace sessd {
@@ -151,7 +153,9 @@ conv_simt_kernel(const T* __restrict__ in, T* __restrict__ out, const int32_t* _
 
 template <typename T, int CIN, int COUT>
 int launch_one(const ConvLaunch& c, cudaStream_t stream) {
-    SESSD_LAUNCH((conv_simt_kernel<T, CIN, COUT>), persistent_grid(4), kThreads, 0, stream,
+    static const std::string name = std::string("conv_simt<") + (sizeof(T) == 4 ? "f32," : "f16,") +
+                                    std::to_string(CIN) + "," + std::to_string(COUT) + ">";
+    SESSD_LAUNCH_NAMED(name.c_str(), (conv_simt_kernel<T, CIN, COUT>), persistent_grid(4), kThreads, 0, stream,
                  static_cast<const T*>(c.in), static_cast<T*>(c.out), c.nbr, c.out_num,
                  static_cast<const T*>(c.weights), c.scale, c.shift, c.relu, c.batch, c.max_voxels, c.kvol,
                  static_cast<T*>(c.dense), reinterpret_cast<const int4*>(c.out_coors), c.D, c.H, c.W);
