@@ -50,6 +50,7 @@ typedef enum sessd_error {
 #define SESSD_STATUS_HASH_FULL 2      /* a coordinate table ran out of probes; entry dropped */
 #define SESSD_STATUS_PAIR_OVERFLOW 4  /* a rulebook column exceeded max_voxels entries on export */
 #define SESSD_STATUS_BAD_COORD 8      /* an input coordinate lies outside the declared grid; row ignored */
+#define SESSD_STATUS_TIMEOUT 16       /* a bounded wait inside a kernel gave up; the call's outputs are invalid */
 
 typedef enum sessd_dtype { SESSD_F32 = 0, SESSD_F16 = 1 } sessd_dtype;
 

@@ -16,7 +16,7 @@ from . import schedule, sharding, synth  # noqa: F401
 from .build import LIB_PATH, build
 
 F32, F16 = 0, 1
-STATUS_VOXEL_OVERFLOW, STATUS_HASH_FULL, STATUS_PAIR_OVERFLOW, STATUS_BAD_COORD = 1, 2, 4, 8
+STATUS_VOXEL_OVERFLOW, STATUS_HASH_FULL, STATUS_PAIR_OVERFLOW, STATUS_BAD_COORD, STATUS_TIMEOUT = 1, 2, 4, 8, 16
 
 EXPORTS = (
     "sessd_voxel_configure", "sessd_voxelize_workspace_bytes", "sessd_voxelize_enqueue", "sessd_voxelize_num_points",

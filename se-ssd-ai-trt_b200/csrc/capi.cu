@@ -428,6 +428,7 @@ static int conv_enqueue_common(const sessd_conv_params* p, const sessd_conv_weig
     c.cin = p->in_channel;
     c.cout = p->out_channel;
     c.dtype = w->impl.dtype;
+    c.status = ws.status;
     rc = choose_conv(c, stream);
     if (rc) return rc;
     // Rows past the active count are zero in the reference (outputs are memset, submConv3dlayer.cu:594).
@@ -639,6 +640,7 @@ static int backbone_enqueue_impl(const sessd_backbone* bb, int batch, int max_po
         c.cin = L.p.in_channel;
         c.cout = L.p.out_channel;
         c.dtype = bb->dtype;
+        c.status = w.status;
         if (bb->has_s2d && i + 1 == bb->layers.size()) {
             c.dense = dense;
             c.out_coors = w.coors[L.level_out];

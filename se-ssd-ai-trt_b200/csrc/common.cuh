@@ -228,6 +228,7 @@ struct ConvLaunch {
     void* dense;
     const int32_t* out_coors;
     int D, H, W;
+    int32_t* status;       // device status word (tensor-core path reports wait timeouts there)
 };
 int launch_conv_simt(const ConvLaunch& c, cudaStream_t stream);
 bool conv_simt_supported(int cin, int cout);

@@ -1,13 +1,443 @@
-// Tensor-core (tcgen05 / TMEM) implicit-GEMM sparse convolution: placeholder until the kernel lands.
+// Sparse convolution as an implicit GEMM on the 5th-generation tensor cores (tcgen05 + TMEM).
+//
+// Replaces, for fp16 features and 16/32/64 channels, the reference's per-offset scalar kernel
+// (submConv3dlayer.cu:479-518, launched kvol times per layer, :632-638). One CTA owns a tile of 128
+// output rows. For every group of kernel offsets it gathers the 128 neighbour rows into shared
+// memory as a K-major, 128-byte-swizzled A operand (one 128-byte row per output row: 64/Cin offsets
+// side by side, missing neighbours zero-filled), streams the matching pre-tiled weight block as the B
+// operand with a bulk asynchronous copy, and issues tcgen05.mma (M=128, N=Cout, K=16 x 4) into one
+// fp32 accumulator in tensor memory that stays resident across all offsets. The epilogue reads the
+// accumulator with tcgen05.ld, applies the folded BatchNorm scale/shift and ReLU, and stores fp16
+// rows (and, for the last layer, scatters them into the dense BEV map).
+//
+// Warp roles (192 threads): warps 0-3 gather A tiles with 16-byte cp.async and later run the
+// epilogue; warp 4 owns tensor memory and issues the MMAs from one thread; warp 5 streams the weight
+// blocks. Stages hand over through mbarriers; every wait is bounded by a clock limit, after which the
+// CTA raises SESSD_STATUS_TIMEOUT, stops issuing work, frees its tensor memory and returns.
+#include <string>
+#include <vector>
+
 #include "common.cuh"
 
 namespace sessd {
 
-bool conv_umma_supported(int, int) { return false; }
-int conv_umma_pack_weights(const float*, int, int, int, void** device_out) {
-    *device_out = nullptr;
+namespace {
+
+constexpr int TILE_M = 128;
+constexpr int STAGES = 4;
+constexpr int LAG = 2;                       // gather groups kept in flight before a stage is published
+constexpr int ROW_BYTES = 128;               // 64 halves per A/B row
+constexpr int A_BYTES = TILE_M * ROW_BYTES;  // 16 KB
+constexpr int UMMA_THREADS = 192;
+constexpr int KVOL_MAX = 27;
+constexpr long long WAIT_LIMIT_CYCLES = 4000000000LL;  // about two seconds
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+// Bounded wait: false when the phase did not complete within the clock limit or the CTA is aborting.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const long long t0 = clock64();
+    for (;;) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if (*abort_flag) return false;
+        if (clock64() - t0 > WAIT_LIMIT_CYCLES) {
+            *abort_flag = 1;
+            return false;
+        }
+    }
+}
+
+__device__ __forceinline__ void cp_async_16(uint32_t dst, const void* src, uint32_t src_bytes) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {
+    asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+__device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+__device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
+                 "l"(src), "r"(bytes), "r"(bar)
+                 : "memory");
+}
+
+// Shared-memory matrix descriptor, K-major, 128-byte swizzle: rows of 128 bytes, groups of 8 rows 1024
+// bytes apart (stride byte offset), leading byte offset unused by swizzled K-major layouts (set to 1),
+// descriptor version 1, layout type 2 (SWIZZLE_128B).
+__device__ __forceinline__ uint64_t umma_desc(uint32_t saddr) {
+    uint64_t d = 0;
+    d |= (uint64_t)((saddr & 0x3FFFFu) >> 4);
+    d |= (uint64_t)1 << 16;
+    d |= (uint64_t)(1024 >> 4) << 32;
+    d |= (uint64_t)1 << 46;
+    d |= (uint64_t)2 << 61;
+    return d;
+}
+
+// Instruction descriptor, kind::f16: fp32 accumulate, fp16 A and B, both K-major, M = 128, N = n.
+__host__ __device__ constexpr uint32_t umma_idesc(int n) {
+    return (1u << 4) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(TILE_M >> 4) << 24);
+}
+
+__device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t acc) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(tmem_d),
+        "l"(adesc), "l"(bdesc), "r"(idesc), "r"(acc)
+        : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+struct SharedCtl {
+    unsigned long long full[STAGES];
+    unsigned long long empty[STAGES];
+    unsigned long long acc_full;
+    uint32_t tmem_base;
+    uint32_t stage_mask;
+    int abort_flag;
+    int pad;
+};
+
+template <int COUT>
+constexpr int umma_smem_bytes() {
+    return 1024 /*alignment slack*/ + STAGES * (A_BYTES + COUT * ROW_BYTES) + KVOL_MAX * TILE_M * 4 + 2 * COUT * 4 +
+           (int)sizeof(SharedCtl);
+}
+
+template <int CIN, int COUT>
+__global__ void __launch_bounds__(UMMA_THREADS, 2)
+conv_umma_kernel(const __half* __restrict__ in, __half* __restrict__ out, const int32_t* __restrict__ nbr,
+                 const int32_t* __restrict__ out_num, const uint8_t* __restrict__ wtiles,
+                 const float* __restrict__ scale, const float* __restrict__ shift, int relu, int batch,
+                 int max_voxels, int kvol, __half* __restrict__ dense, const int4* __restrict__ out_coors, int D, int H,
+                 int W, int32_t* status) {
+    constexpr int KG = 64 / CIN;            // kernel offsets sharing one 128-byte A row
+    constexpr int CPO = CIN / 8;            // 16-byte chunks per offset
+    constexpr int B_BYTES = COUT * ROW_BYTES;
+    constexpr int TMEM_COLS = COUT < 32 ? 32 : COUT;
+    constexpr uint32_t IDESC = umma_idesc(COUT);
+
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint8_t* sA = smem;
+    uint8_t* sB = sA + STAGES * A_BYTES;
+    int32_t* s_nbr = reinterpret_cast<int32_t*>(sB + STAGES * B_BYTES);
+    float* s_scale = reinterpret_cast<float*>(s_nbr + KVOL_MAX * TILE_M);
+    float* s_shift = s_scale + COUT;
+    SharedCtl* ctl = reinterpret_cast<SharedCtl*>(s_shift + COUT);
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int nstages = (kvol + KG - 1) / KG;
+
+    if (tid == 0) {
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(smem_u32(&ctl->full[s]), TILE_M + 1);
+            mbar_init(smem_u32(&ctl->empty[s]), 1);
+        }
+        mbar_init(smem_u32(&ctl->acc_full), 1);
+        ctl->stage_mask = 0;
+        ctl->abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    for (int c = tid; c < COUT; c += UMMA_THREADS) {
+        s_scale[c] = scale ? scale[c] : 1.f;
+        s_shift[c] = (scale && shift) ? shift[c] : 0.f;
+    }
+    if (warp == 4) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&ctl->tmem_base)),
+                     "r"(TMEM_COLS)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = ctl->tmem_base;
+    volatile int* abort_flag = &ctl->abort_flag;
+
+    const int tiles_per_frame = (max_voxels + TILE_M - 1) / TILE_M;
+    const int items = batch * tiles_per_frame;
+    uint32_t it = 0;        // stages consumed so far by this CTA (same value in every role)
+    uint32_t tile_iter = 0; // tiles with at least one active stage processed so far
+
+    for (int item = blockIdx.x; item < items; item += gridDim.x) {
+        const int b = item / tiles_per_frame;
+        const int row0 = (item - b * tiles_per_frame) * TILE_M;
+        int n = out_num[b];
+        n = n > max_voxels ? max_voxels : n;
+        if (row0 >= n) continue;  // uniform over the CTA
+
+        tc_fence_before();
+        __syncthreads();  // previous tile completely finished: s_nbr and the accumulator are free
+        if (*abort_flag) break;
+        if (tid == 0) ctl->stage_mask = 0;
+        __syncthreads();
+        {
+            uint32_t m = 0;
+            const int32_t* src = nbr + (size_t)b * kvol * max_voxels + row0;
+            for (int e = tid; e < kvol * TILE_M; e += UMMA_THREADS) {
+                const int k = e / TILE_M, r = e - k * TILE_M;
+                const int v = (row0 + r < n) ? __ldg(src + (size_t)k * max_voxels + r) : -1;
+                s_nbr[e] = v;
+                if (v >= 0) m |= 1u << (k / KG);
+            }
+            m = __reduce_or_sync(0xFFFFFFFFu, m);
+            if (lane == 0 && m) atomicOr(&ctl->stage_mask, m);
+        }
+        __syncthreads();
+        tc_fence_after();
+        const uint32_t mask = ctl->stage_mask;
+        const int nactive = __popc(mask);
+
+        if (warp < 4) {
+            // ---------------- gather producers ----------------
+            const int c = tid & 7;                 // 16-byte chunk of the 128-byte row
+            const int koff = c / CPO;              // which offset of the stage's group this chunk belongs to
+            const int csub = (c % CPO) * 8;        // first channel of the chunk
+            const __half* in_b = in + (size_t)b * max_voxels * CIN;
+            uint32_t pending[LAG + 1];
+            int npending = 0;
+            uint32_t my_it = it;
+            bool ok = true;
+            for (int g = 0; g < nstages && ok; ++g) {
+                if (!((mask >> g) & 1u)) continue;
+                const uint32_t s = my_it % STAGES;
+                ok = mbar_wait(smem_u32(&ctl->empty[s]), ((my_it / STAGES) & 1u) ^ 1u, abort_flag);
+                if (!ok) break;
+                const int k = g * KG + koff;
+                const uint32_t a_base = smem_u32(sA + s * A_BYTES);
+#pragma unroll
+                for (int p = 0; p < TILE_M / 16; ++p) {
+                    const int r = (tid >> 3) + 16 * p;
+                    const int idx = (k < kvol) ? s_nbr[k * TILE_M + r] : -1;
+                    const __half* src = in_b + (size_t)(idx < 0 ? 0 : idx) * CIN + csub;
+                    const uint32_t dst = a_base + r * ROW_BYTES + ((c ^ (r & 7)) << 4);
+                    cp_async_16(dst, src, idx < 0 ? 0u : 16u);
+                }
+                cp_async_commit();
+                pending[npending++] = s;
+                ++my_it;
+                if (npending > LAG) {
+                    cp_async_wait<LAG>();
+                    fence_proxy_async();
+                    mbar_arrive(smem_u32(&ctl->full[pending[0]]));
+#pragma unroll
+                    for (int q = 0; q < LAG; ++q) pending[q] = pending[q + 1];
+                    --npending;
+                }
+            }
+            cp_async_wait<0>();
+            fence_proxy_async();
+            for (int q = 0; q < npending; ++q) mbar_arrive(smem_u32(&ctl->full[pending[q]]));
+
+            // ---------------- epilogue ----------------
+            const int row = row0 + tid;
+            float acc[COUT];
+            bool have = false;
+            if (nactive > 0) {
+                bool got = ok && mbar_wait(smem_u32(&ctl->acc_full), tile_iter & 1u, abort_flag);
+                got = __all_sync(0xFFFFFFFFu, got);
+                if (got) {
+                    tc_fence_after();
+#pragma unroll
+                    for (int c0 = 0; c0 < COUT; c0 += 16) {
+                        uint32_t r16[16];
+                        tmem_ld16(tmem + ((uint32_t)(warp * 32) << 16) + c0, r16);
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) acc[c0 + j] = __uint_as_float(r16[j]);
+                    }
+                    tmem_ld_wait();
+                    have = true;
+                }
+            } else {
+#pragma unroll
+                for (int j = 0; j < COUT; ++j) acc[j] = 0.f;
+                have = true;
+            }
+            if (have && row < n) {
+                __half* dst = out + ((size_t)b * max_voxels + row) * COUT;
+#pragma unroll
+                for (int c0 = 0; c0 < COUT; c0 += 8) {
+                    uint4 pk;
+                    __half2* h = reinterpret_cast<__half2*>(&pk);
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        float v0 = fmaf(acc[c0 + 2 * j], s_scale[c0 + 2 * j], s_shift[c0 + 2 * j]);
+                        float v1 = fmaf(acc[c0 + 2 * j + 1], s_scale[c0 + 2 * j + 1], s_shift[c0 + 2 * j + 1]);
+                        if (relu) {
+                            v0 = v0 > 0.f ? v0 : 0.f;
+                            v1 = v1 > 0.f ? v1 : 0.f;
+                        }
+                        acc[c0 + 2 * j] = v0;
+                        acc[c0 + 2 * j + 1] = v1;
+                        h[j] = __floats2half2_rn(v0, v1);
+                    }
+                    *reinterpret_cast<uint4*>(dst + c0) = pk;
+                }
+                if (dense) {
+                    // fused BEV scatter (sparse2Dense.cu:201-206): channel c*D + z, pixel (y, x)
+                    const int4 c4 = __ldg(&out_coors[(size_t)b * max_voxels + row]);
+                    __half* d = dense + (size_t)b * COUT * D * H * W + ((size_t)c4.y * H + c4.z) * W + c4.w;
+#pragma unroll
+                    for (int j = 0; j < COUT; ++j) d[(size_t)j * D * H * W] = __float2half_rn(acc[j]);
+                }
+            }
+        } else if (warp == 4) {
+            // ---------------- MMA issuer ----------------
+            if (lane == 0) {
+                uint32_t my_it = it;
+                bool first = true, ok = true;
+                for (int g = 0; g < nstages && ok; ++g) {
+                    if (!((mask >> g) & 1u)) continue;
+                    const uint32_t s = my_it % STAGES;
+                    ok = mbar_wait(smem_u32(&ctl->full[s]), (my_it / STAGES) & 1u, abort_flag);
+                    if (!ok) break;
+                    tc_fence_after();
+                    const uint32_t a_addr = smem_u32(sA + s * A_BYTES), b_addr = smem_u32(sB + s * B_BYTES);
+#pragma unroll
+                    for (int kk = 0; kk < 4; ++kk) {
+                        umma_f16(tmem, umma_desc(a_addr + kk * 32), umma_desc(b_addr + kk * 32), IDESC,
+                                 (first && kk == 0) ? 0u : 1u);
+                    }
+                    first = false;
+                    umma_commit(smem_u32(&ctl->empty[s]));  // frees the stage once these MMAs have read it
+                    ++my_it;
+                }
+                if (ok && nactive > 0) umma_commit(smem_u32(&ctl->acc_full));
+            }
+            __syncwarp();
+        } else {
+            // ---------------- weight streamer ----------------
+            if (lane == 0) {
+                uint32_t my_it = it;
+                bool ok = true;
+                for (int g = 0; g < nstages && ok; ++g) {
+                    if (!((mask >> g) & 1u)) continue;
+                    const uint32_t s = my_it % STAGES;
+                    ok = mbar_wait(smem_u32(&ctl->empty[s]), ((my_it / STAGES) & 1u) ^ 1u, abort_flag);
+                    if (!ok) break;
+                    const uint32_t bar = smem_u32(&ctl->full[s]);
+                    mbar_arrive_expect_tx(bar, B_BYTES);
+                    bulk_load(smem_u32(sB + s * B_BYTES), wtiles + (size_t)g * B_BYTES, B_BYTES, bar);
+                    ++my_it;
+                }
+            }
+            __syncwarp();
+        }
+        it += nactive;
+        if (nactive > 0) ++tile_iter;
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (tid == 0 && *abort_flag) atomicOr(status, SESSD_STATUS_TIMEOUT);
+    if (warp == 4) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(TMEM_COLS) : "memory");
+    }
+}
+
+template <int CIN, int COUT>
+int launch_one(const ConvLaunch& c, cudaStream_t stream) {
+    static const std::string name = "conv_umma<f16," + std::to_string(CIN) + "," + std::to_string(COUT) + ">";
+    constexpr int smem = umma_smem_bytes<COUT>();
+    static bool configured = false;
+    if (!configured) {
+        SESSD_CUDA(cudaFuncSetAttribute(conv_umma_kernel<CIN, COUT>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+        configured = true;
+    }
+    SESSD_LAUNCH_NAMED(name.c_str(), (conv_umma_kernel<CIN, COUT>), persistent_grid(2), UMMA_THREADS, smem, stream,
+                       static_cast<const __half*>(c.in), static_cast<__half*>(c.out), c.nbr, c.out_num,
+                       static_cast<const uint8_t*>(c.umma_weights), c.scale, c.shift, c.relu, c.batch, c.max_voxels,
+                       c.kvol, static_cast<__half*>(c.dense), reinterpret_cast<const int4*>(c.out_coors), c.D, c.H, c.W,
+                       c.status);
     return SESSD_OK;
 }
-int launch_conv_umma(const ConvLaunch&, cudaStream_t) { return SESSD_ERR_UNSUPPORTED; }
+
+}  // namespace
+
+bool conv_umma_supported(int cin, int cout) {
+    return (cin == 16 || cin == 32 || cin == 64) && (cout == 16 || cout == 32 || cout == 64);
+}
+
+// Weight tiles in the order the kernel consumes them: for stage g (a group of 64/Cin kernel offsets) a
+// block of Cout rows x 128 bytes, row n holding K index kk = j*Cin + ci -> W[g*KG + j][ci][n], stored
+// K-major with the 128-byte swizzle (16-byte chunk index XOR row index mod 8), zero beyond kvol.
+int conv_umma_pack_weights(const float* weights, int kvol, int cin, int cout, void** device_out) {
+    *device_out = nullptr;
+    if (!conv_umma_supported(cin, cout)) return SESSD_OK;
+    const int kg = 64 / cin, nstages = (kvol + kg - 1) / kg;
+    std::vector<__half> img((size_t)nstages * cout * 64, __float2half_rn(0.f));
+    for (int g = 0; g < nstages; ++g)
+        for (int n = 0; n < cout; ++n)
+            for (int kk = 0; kk < 64; ++kk) {
+                const int k = g * kg + kk / cin, ci = kk % cin;
+                if (k >= kvol) continue;
+                const int chunk = kk / 8;
+                const size_t pos = ((size_t)g * cout + n) * 64 + (size_t)((chunk ^ (n & 7)) * 8) + (kk % 8);
+                img[pos] = __float2half_rn(weights[((size_t)k * cin + ci) * cout + n]);
+            }
+    void* d = nullptr;
+    cudaError_t e = cudaMalloc(&d, img.size() * sizeof(__half));
+    if (e == cudaSuccess) e = cudaMemcpy(d, img.data(), img.size() * sizeof(__half), cudaMemcpyHostToDevice);
+    if (e != cudaSuccess) {
+        set_cuda_error(e, "conv_umma_pack_weights");
+        if (d) cudaFree(d);
+        return SESSD_ERR_CUDA;
+    }
+    *device_out = d;
+    return SESSD_OK;
+}
+
+int launch_conv_umma(const ConvLaunch& c, cudaStream_t stream) {
+    if (c.dtype != SESSD_F16 || !c.umma_weights || c.kvol > KVOL_MAX) return SESSD_ERR_UNSUPPORTED;
+#define SESSD_CASE(CI, CO) \
+    if (c.cin == CI && c.cout == CO) return launch_one<CI, CO>(c, stream);
+    SESSD_CASE(16, 16)
+    SESSD_CASE(16, 32)
+    SESSD_CASE(32, 32)
+    SESSD_CASE(32, 64)
+    SESSD_CASE(64, 64)
+#undef SESSD_CASE
+    return SESSD_ERR_UNSUPPORTED;
+}
 
 }  // namespace sessd
