@@ -46,16 +46,22 @@ def _check_fp32_layers(want, views, tol=1e-5):
         np.testing.assert_array_equal(gf[0, :wn], wf)   # same summation order as the oracle
 
 
-def _check_fp16_layers(oracle, case, want, views, tol=1e-2, drift_tol=5e-2):
-    """fp16 parity: every layer is within `tol` of the oracle applied to the SAME input (the library's own
-    previous layer), which is what a per-layer tolerance means; against the oracle's own chain, where
-    one-ulp differences of earlier layers are inherited, the looser `drift_tol` applies. Row numbering and
-    coordinates must be identical in both comparisons."""
+def _max_norm_err(a, b):
+    b = np.asarray(b, np.float64)
+    return float(np.abs(np.asarray(a, np.float64) - b).max() / max(np.abs(b).max(), 1e-30)) if b.size else 0.0
+
+
+def _check_fp16_layers(oracle, case, want, views, tol=1e-2, drift_tol=2e-2):
+    """fp16 parity: every layer is within `tol` (element-wise relative) of the oracle applied to the SAME
+    input (the library's own previous layer), which is what a per-layer tolerance means. Against the
+    oracle's own chain, one-ulp differences of earlier layers are inherited and values next to the ReLU
+    threshold flip between 0 and tiny, so that comparison is normalised by the layer's largest magnitude
+    (`drift_tol`). Row numbering and coordinates must be identical in both comparisons."""
     params = list(zip(case["layers"], case["weights"], case["scale"], case["shift"]))
     for i, ((wc, wn, wf), (gf, gc, gn)) in enumerate(zip(want, views)):
         assert int(gn[0]) == wn, f"layer {i - 1}"
         np.testing.assert_array_equal(gc[0, :wn], wc)
-        drift = rel_err(gf[0, :wn], wf)
+        drift = _max_norm_err(gf[0, :wn], wf)
         assert drift <= drift_tol, f"layer {i - 1}: drift {drift}"
         if i == 0:
             np.testing.assert_array_equal(gf[0, :wn], wf)   # voxel means are exact
@@ -104,7 +110,8 @@ def test_small_backbone_every_layer(gpu, oracle, dtype, tol):
     # the BEV map is exactly the scatter of the library's own last layer ...
     np.testing.assert_array_equal(dense, oracle.sparse2dense(gf[0, :n], gc[0, :n], n, Cc, D, H, W))
     # ... and stays within the chain tolerance of the oracle's map
-    assert rel_err(dense, oracle.sparse2dense(f, c, n, Cc, D, H, W)) <= (tol if dtype == 0 else 5e-2)
+    want_dense = oracle.sparse2dense(f, c, n, Cc, D, H, W)
+    assert (rel_err(dense, want_dense) <= tol) if dtype == 0 else (_max_norm_err(dense, want_dense) <= 2e-2)
 
 
 def test_small_backbone_matches_committed_golden(gpu):
