@@ -90,6 +90,25 @@ int sessd_voxelize_enqueue(const sessd_voxel_params* p, int batch, int max_point
  * (num_points_per_voxel, voxelGenerator.cu:507-509). */
 void* sessd_voxelize_num_points(const sessd_voxel_params* p, int batch, int max_points, void* workspace);
 
+/* Voxel generator for callers that cannot allocate: same inputs, outputs and results as
+ * sessd_voxelize_enqueue, but the scratch memory is a 4 MiB device array built into the library instead
+ * of a caller workspace, and the call performs no cudaMalloc / cudaFree or any other allocation. It is
+ * meant for hosts whose device memory is fixed before this library runs (a pre-sized plugin arena, a
+ * real-time loop that may not touch the allocator). This entry point has no counterpart in the reference,
+ * whose plugins always receive a TensorRT workspace.
+ * Limits and rules:
+ *   - batch, max_points and p->max_voxels must fit the built-in scratch (e.g. one frame of up to 32768
+ *     points with max_voxels <= 32768); larger requests return SESSD_ERR_WORKSPACE and
+ *     sessd_last_cuda_error() explains why;
+ *   - the first call on each device looks up the array's device address (cudaGetSymbolAddress); make
+ *     that first call outside any stream capture;
+ *   - all calls on one device share the array: it keeps the previous call's contents (each call resets
+ *     what it needs), and two calls that overlap on the GPU (different streams) race. Serialise them;
+ *   - the device status word lives inside the array and is not exposed: detect overflow by
+ *     voxel_num[b] == p->max_voxels. */
+int sessd_voxelize_enqueue_static(const sessd_voxel_params* p, int batch, int max_points, int out_dtype,
+                                  const void* const* inputs, void* const* outputs, void* stream);
+
 /* ------------------------------------------------------------------------------------------
  * Sparse convolutions.  Replace SubmConv3dLayerPlugin (submConv3dlayer.h:19-121) and
  * SparseConv3dLayerPlugin (sparseConv3dlayer.h:18-126). The struct holds the integer lists both

@@ -20,6 +20,7 @@ STATUS_VOXEL_OVERFLOW, STATUS_HASH_FULL, STATUS_PAIR_OVERFLOW, STATUS_BAD_COORD,
 
 EXPORTS = (
     "sessd_voxel_configure", "sessd_voxelize_workspace_bytes", "sessd_voxelize_enqueue", "sessd_voxelize_num_points",
+    "sessd_voxelize_enqueue_static",
     "sessd_conv_weights_create", "sessd_conv_weights_destroy", "sessd_conv_workspace_bytes",
     "sessd_subm_conv_enqueue", "sessd_sparse_conv_enqueue", "sessd_conv_rulebook_export",
     "sessd_sparse2dense_enqueue", "sessd_backbone_create", "sessd_backbone_destroy",
