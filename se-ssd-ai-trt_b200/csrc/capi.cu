@@ -71,11 +71,19 @@ bool voxel_params_ok(const sessd_voxel_params* p, int batch, int max_points) {
     return true;
 }
 
+bool is_subm_333(const ConvGeom& g) {
+    return g.kvol == 27 && g.K[0] == 3 && g.K[1] == 3 && g.K[2] == 3 && g.P[0] == 1 && g.P[1] == 1 && g.P[2] == 1;
+}
+
 struct ConvWorkspace {
     int32_t* status;
-    void* table_base;
-    size_t table_bytes;
-    Table in_table, out_table;
+    void* ones_base;      // tables: every word 0xFFFFFFFF before use
+    size_t ones_bytes;
+    Buckets buckets;      // submanifold 3x3x3: x-grouped table of the input coordinates
+    Table in_table;       // other submanifold geometries: flat table of the input coordinates
+    Table out_table;      // strided: flat table of the output coordinates (keys, rank, vals)
+    uint32_t* tile_mask;  // [B][tiles], zero before use
+    size_t tile_mask_bytes;
     int32_t* slot_of;
     int32_t* chunk_counts;
     int chunks;
@@ -83,26 +91,34 @@ struct ConvWorkspace {
 };
 
 void conv_workspace_layout(Bump& bump, const sessd_conv_params* p, const ConvGeom& g, int batch, ConvWorkspace* w) {
+    *w = ConvWorkspace{};
     w->status = bump.take<int32_t>(kStatusInts);
     const uint32_t cap = pow2_at_least(2ull * (uint64_t)p->max_voxels);
     const size_t per = (size_t)batch * cap;
-    const size_t arrays = p->subm ? 2 : 5;
-    uint32_t* block = bump.take<uint32_t>(per * arrays);
-    w->table_base = block;
-    w->table_bytes = per * arrays * sizeof(uint32_t);
-    auto at = [&](size_t i) { return block ? block + per * i : nullptr; };
-    w->in_table = Table{at(0), nullptr, reinterpret_cast<int32_t*>(at(1)), cap, 32 - ilog2(cap), 1};
-    if (p->subm) {
-        w->out_table = w->in_table;
-        w->slot_of = nullptr;
-        w->chunk_counts = nullptr;
-        w->chunks = 0;
+    const int shift = 32 - ilog2(cap);
+    if (p->subm && is_subm_333(g)) {
+        const uint32_t capb = pow2_at_least((uint64_t)p->max_voxels);
+        w->buckets = Buckets{bump.take<uint32_t>((size_t)batch * capb * 8), capb, 32 - ilog2(capb)};
+        w->ones_base = w->buckets.data;
+        w->ones_bytes = (size_t)batch * capb * 8 * sizeof(uint32_t);
+    } else if (p->subm) {
+        uint32_t* block = bump.take<uint32_t>(per * 2);
+        w->in_table = Table{block, nullptr, reinterpret_cast<int32_t*>(block ? block + per : nullptr), cap, shift, 1};
+        w->ones_base = block;
+        w->ones_bytes = per * 2 * sizeof(uint32_t);
     } else {
-        w->out_table = Table{at(2), at(3), reinterpret_cast<int32_t*>(at(4)), cap, 32 - ilog2(cap), 1};
+        uint32_t* block = bump.take<uint32_t>(per * 3);
+        w->out_table = Table{block, block ? block + per : nullptr,
+                             reinterpret_cast<int32_t*>(block ? block + 2 * per : nullptr), cap, shift, 1};
+        w->ones_base = block;
+        w->ones_bytes = per * 3 * sizeof(uint32_t);
         w->slot_of = bump.take<int32_t>((size_t)batch * p->max_voxels * g.ncand);
         w->chunks = spconv_chunks_per_frame(p->max_voxels, g);
         w->chunk_counts = bump.take<int32_t>((size_t)batch * w->chunks);
     }
+    const size_t tiles = (size_t)(p->max_voxels + 127) / 128;
+    w->tile_mask_bytes = (batch * tiles * sizeof(uint32_t) + 15) / 16 * 16;
+    w->tile_mask = bump.take<uint32_t>(w->tile_mask_bytes / sizeof(uint32_t));
     w->nbr = bump.take<int32_t>((size_t)batch * g.kvol * p->max_voxels);
 }
 
@@ -155,10 +171,15 @@ struct BackboneWorkspace {
     VoxelWorkspace vox;
     void* voxel_feat;
     std::vector<int32_t*> coors, num;
-    std::vector<Table> tables;
-    void* level_table_base;
-    size_t level_table_bytes;
+    std::vector<Table> tables;       // flat output tables of the derived levels (index 0 unused)
+    std::vector<Buckets> buckets;    // x-grouped tables of the levels that feed submanifold layers
+    void* ones_base;
+    size_t ones_bytes;
     std::vector<int32_t*> nbr_subm;
+    std::vector<uint32_t*> mask_subm;     // per level
+    std::vector<uint32_t*> mask_layer;    // per strided layer (indexed by layer)
+    void* zero_base;
+    size_t zero_bytes;
     int32_t* nbr_strided;
     int32_t* slot_of;
     int32_t* chunk_counts;
@@ -175,23 +196,51 @@ void backbone_layout(Bump& bump, const sessd_backbone* bb, int batch, int max_po
     w->coors.assign(bb->nlevels, nullptr);
     w->num.assign(bb->nlevels, nullptr);
     w->tables.assign(bb->nlevels, Table{});
+    w->buckets.assign(bb->nlevels, Buckets{});
     w->nbr_subm.assign(bb->nlevels, nullptr);
+    w->mask_subm.assign(bb->nlevels, nullptr);
+    w->mask_layer.assign(bb->layers.size(), nullptr);
     for (int l = 0; l < bb->nlevels; ++l) {
         w->coors[l] = bump.take<int32_t>((size_t)batch * maxV * 4);
         w->num[l] = bump.take<int32_t>(batch);
     }
+    // one contiguous block of tables, reset to 0xFF by a single fill
     const uint32_t cap = pow2_at_least(2ull * (uint64_t)maxV);
-    const size_t per = (size_t)batch * cap;
-    const int derived = bb->nlevels - 1;
-    uint32_t* block = bump.take<uint32_t>(per * 3 * (derived > 0 ? derived : 0) + 4);
-    w->level_table_base = block;
-    w->level_table_bytes = per * 3 * (derived > 0 ? derived : 0) * sizeof(uint32_t);
-    w->tables[0] = w->vox.table;
+    const uint32_t capb = pow2_at_least((uint64_t)maxV);
+    const size_t per = (size_t)batch * cap, perb = (size_t)batch * capb * 8;
+    size_t words = 0;
+    for (int l = 1; l < bb->nlevels; ++l) words += per * 3;
+    for (int l = 0; l < bb->nlevels; ++l)
+        if (bb->level_has_subm[l]) words += perb;
+    uint32_t* block = bump.take<uint32_t>(words + 4);
+    w->ones_base = block;
+    w->ones_bytes = words * sizeof(uint32_t);
+    size_t off = 0;
     for (int l = 1; l < bb->nlevels; ++l) {
-        uint32_t* base = block ? block + per * 3 * (l - 1) : nullptr;
+        uint32_t* base = block ? block + off : nullptr;
         w->tables[l] = Table{base, base ? base + per : nullptr, reinterpret_cast<int32_t*>(base ? base + 2 * per : nullptr),
                              cap, 32 - ilog2(cap), 1};
+        off += per * 3;
     }
+    for (int l = 0; l < bb->nlevels; ++l)
+        if (bb->level_has_subm[l]) {
+            w->buckets[l] = Buckets{block ? block + off : nullptr, capb, 32 - ilog2(capb)};
+            off += perb;
+        }
+    // tile masks, reset to zero by a single fill
+    const size_t tiles = (size_t)(maxV + 127) / 128;
+    const size_t mask_words = (batch * tiles + 3) / 4 * 4;
+    size_t nmasks = 0;
+    for (int l = 0; l < bb->nlevels; ++l) nmasks += bb->level_has_subm[l] ? 1 : 0;
+    for (auto& L : bb->layers) nmasks += L.p.subm ? 0 : 1;
+    uint32_t* masks = bump.take<uint32_t>(mask_words * nmasks + 4);
+    w->zero_base = masks;
+    w->zero_bytes = mask_words * nmasks * sizeof(uint32_t);
+    size_t mi = 0;
+    for (int l = 0; l < bb->nlevels; ++l)
+        if (bb->level_has_subm[l]) w->mask_subm[l] = masks ? masks + mask_words * mi++ : (mi++, nullptr);
+    for (size_t i = 0; i < bb->layers.size(); ++i)
+        if (!bb->layers[i].p.subm) w->mask_layer[i] = masks ? masks + mask_words * mi++ : (mi++, nullptr);
     for (int l = 0; l < bb->nlevels; ++l)
         if (bb->level_has_subm[l]) w->nbr_subm[l] = bump.take<int32_t>((size_t)batch * 27 * maxV);
     w->nbr_strided = bump.take<int32_t>((size_t)batch * (bb->kvol_strided_max > 0 ? bb->kvol_strided_max : 1) * maxV);
@@ -396,26 +445,40 @@ static int conv_enqueue_common(const sessd_conv_params* p, const sessd_conv_weig
     const int32_t* in_coors = static_cast<const int32_t*>(inputs[1]);
     const int32_t* in_num = static_cast<const int32_t*>(inputs[2]);
     SESSD_CUDA(cudaMemsetAsync(ws.status, 0, kStatusInts * sizeof(int32_t), stream));
-    rc = launch_fill_ones(ws.table_base, ws.table_bytes, stream);
+    rc = launch_fill_ones(ws.ones_base, ws.ones_bytes, stream);
     if (rc) return rc;
-    rc = launch_table_build(in_coors, in_num, batch, maxV, g.in_shape, ws.in_table, ws.status, stream);
+    rc = launch_fill_zero(ws.tile_mask, ws.tile_mask_bytes, stream);
     if (rc) return rc;
     const int32_t* out_coors = in_coors;
     const int32_t* out_num = in_num;
-    if (!subm) {
+    if (subm && is_subm_333(g)) {
+        rc = launch_bucket_build(in_coors, in_num, batch, maxV, g.in_shape, ws.buckets, ws.status, stream);
+        if (rc) return rc;
+        rc = launch_nbr_build_subm(in_coors, in_num, batch, maxV, g.in_shape, ws.buckets, ws.nbr, ws.tile_mask, stream);
+        if (rc) return rc;
+    } else if (subm) {
+        rc = launch_table_build(in_coors, in_num, batch, maxV, g.in_shape, ws.in_table, ws.status, stream);
+        if (rc) return rc;
+        rc = launch_nbr_build(in_coors, in_num, batch, maxV, g, ws.in_table, ws.nbr, stream);
+        if (rc) return rc;
+        rc = launch_tile_mask(ws.nbr, in_num, batch, maxV, g.kvol, ws.tile_mask, stream);
+        if (rc) return rc;
+    } else {
         rc = launch_spconv_outputs(in_coors, in_num, batch, maxV, g, ws.out_table, ws.slot_of, ws.chunk_counts,
                                    ws.chunks, static_cast<int32_t*>(outputs[1]), static_cast<int32_t*>(outputs[2]),
                                    ws.status, stream);
         if (rc) return rc;
         out_coors = static_cast<const int32_t*>(outputs[1]);
         out_num = static_cast<const int32_t*>(outputs[2]);
+        rc = launch_nbr_scatter_strided(in_coors, in_num, out_num, batch, maxV, g, ws.out_table, ws.slot_of, ws.nbr,
+                                        ws.tile_mask, stream);
+        if (rc) return rc;
     }
-    rc = launch_nbr_build(out_coors, out_num, batch, maxV, g, ws.in_table, ws.nbr, stream);
-    if (rc) return rc;
     ConvLaunch c{};
     c.in = inputs[0];
     c.out = outputs[0];
     c.nbr = ws.nbr;
+    c.tile_mask = ws.tile_mask;
     c.out_num = out_num;
     c.weights = w->impl.w;
     c.umma_weights = w->impl.umma_w;
@@ -581,7 +644,9 @@ static int backbone_enqueue_impl(const sessd_backbone* bb, int batch, int max_po
     if (bump.total() > workspace_bytes) return SESSD_ERR_WORKSPACE;
     const int maxV = bb->max_voxels;
     SESSD_CUDA(cudaMemsetAsync(w.status, 0, kStatusInts * sizeof(int32_t), stream));
-    int rc = launch_fill_ones(w.level_table_base, w.level_table_bytes, stream);
+    int rc = launch_fill_ones(w.ones_base, w.ones_bytes, stream);
+    if (rc) return rc;
+    rc = launch_fill_zero(w.zero_base, w.zero_bytes, stream);
     if (rc) return rc;
     if (bb->has_s2d) {
         const size_t bytes = (size_t)batch * bb->s2d.feature_map_channel * bb->s2d.feature_map_size_z *
@@ -601,23 +666,31 @@ static int backbone_enqueue_impl(const sessd_backbone* bb, int batch, int max_po
     for (size_t i = 0; i < bb->layers.size(); ++i) {
         const sessd_backbone::Layer& L = bb->layers[i];
         const int32_t* nbr;
+        const uint32_t* tile_mask;
         if (L.p.subm) {
             if (!nbr_ready[L.level_in]) {
-                rc = launch_nbr_build(w.coors[L.level_in], w.num[L.level_in], batch, maxV, L.g, w.tables[L.level_in],
-                                      w.nbr_subm[L.level_in], stream);
+                rc = launch_bucket_build(w.coors[L.level_in], w.num[L.level_in], batch, maxV, L.g.in_shape,
+                                         w.buckets[L.level_in], w.status, stream);
+                if (rc) return rc;
+                rc = launch_nbr_build_subm(w.coors[L.level_in], w.num[L.level_in], batch, maxV, L.g.in_shape,
+                                           w.buckets[L.level_in], w.nbr_subm[L.level_in], w.mask_subm[L.level_in],
+                                           stream);
                 if (rc) return rc;
                 nbr_ready[L.level_in] = 1;
             }
             nbr = w.nbr_subm[L.level_in];
+            tile_mask = w.mask_subm[L.level_in];
         } else {
             rc = launch_spconv_outputs(w.coors[L.level_in], w.num[L.level_in], batch, maxV, L.g, w.tables[L.level_out],
                                        w.slot_of, w.chunk_counts, w.chunks, w.coors[L.level_out], w.num[L.level_out],
                                        w.status, stream);
             if (rc) return rc;
-            rc = launch_nbr_build(w.coors[L.level_out], w.num[L.level_out], batch, maxV, L.g, w.tables[L.level_in],
-                                  w.nbr_strided, stream);
+            rc = launch_nbr_scatter_strided(w.coors[L.level_in], w.num[L.level_in], w.num[L.level_out], batch, maxV,
+                                            L.g, w.tables[L.level_out], w.slot_of, w.nbr_strided, w.mask_layer[i],
+                                            stream);
             if (rc) return rc;
             nbr = w.nbr_strided;
+            tile_mask = w.mask_layer[i];
         }
         if (count_pairs) {
             auto* counters = reinterpret_cast<unsigned long long*>(reinterpret_cast<char*>(w.status) + 256);
@@ -628,6 +701,7 @@ static int backbone_enqueue_impl(const sessd_backbone* bb, int batch, int max_po
         c.in = cur;
         c.out = w.feat[i];
         c.nbr = nbr;
+        c.tile_mask = tile_mask;
         c.out_num = w.num[L.level_out];
         c.weights = L.w->impl.w;
         c.umma_weights = L.w->impl.umma_w;

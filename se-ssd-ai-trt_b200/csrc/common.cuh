@@ -100,6 +100,15 @@ struct Table {
     int rank_stride;
 };
 
+// x-grouped coordinate table of one resolution level: frame b owns buckets [b*cap, (b+1)*cap), a
+// bucket is 8 words = {row of cell x&3 == 0..3, group key (cell index >> 2), 3 unused}; all words are
+// 0xFFFFFFFF when free.
+struct Buckets {
+    uint32_t* data;
+    uint32_t cap;   // buckets per frame, power of two
+    int shift;      // 32 - log2(cap)
+};
+
 // Geometry of one sparse convolution (z, y, x order everywhere).
 struct ConvGeom {
     int K[3], S[3], P[3];
@@ -207,6 +216,17 @@ int launch_nbr_build(const int32_t* out_coors, const int32_t* out_num, int batch
 int launch_spconv_outputs(const int32_t* in_coors, const int32_t* in_num, int batch, int max_voxels, const ConvGeom& g,
                           const Table& out_table, int32_t* slot_of, int32_t* chunk_counts, int chunks_per_frame,
                           int32_t* out_coors, int32_t* out_num, int32_t* status, cudaStream_t stream);
+int launch_bucket_build(const int32_t* coors, const int32_t* voxel_num, int batch, int max_voxels, const int shape[3],
+                        const Buckets& t, int32_t* status, cudaStream_t stream);
+// 3x3x3 / stride 1 / pad 1 neighbour map from a bucket table, plus the per-128-row-tile offset masks.
+int launch_nbr_build_subm(const int32_t* coors, const int32_t* voxel_num, int batch, int max_voxels, const int shape[3],
+                          const Buckets& t, int32_t* nbr, uint32_t* tile_mask, cudaStream_t stream);
+// Neighbour map of a strided layer from the candidate entries left by launch_spconv_outputs.
+int launch_nbr_scatter_strided(const int32_t* in_coors, const int32_t* in_num, const int32_t* out_num, int batch,
+                               int max_voxels, const ConvGeom& g, const Table& out_table, const int32_t* slot_of,
+                               int32_t* nbr, uint32_t* tile_mask, cudaStream_t stream);
+int launch_tile_mask(const int32_t* nbr, const int32_t* out_num, int batch, int max_voxels, int kvol,
+                     uint32_t* tile_mask, cudaStream_t stream);
 inline int spconv_chunks_per_frame(int max_voxels, const ConvGeom& g) {
     return (int)(((int64_t)max_voxels * g.ncand + kChunk - 1) / kChunk);
 }
@@ -217,6 +237,7 @@ struct ConvLaunch {
     void* out;             // [B][max_voxels][Cout]
     const int32_t* nbr;    // [B][kvol][max_voxels]
     const int32_t* out_num;// [B]
+    const uint32_t* tile_mask; // [B][ceil(max_voxels/128)]: bit k set when offset k has a neighbour in the tile
     const void* weights;   // [kvol][Cin][Cout] in the feature dtype
     const void* umma_weights; // fp16 weights pre-tiled for the tensor-core kernel, or null
     const float* scale;    // [Cout] or null

@@ -6,13 +6,16 @@
 // memory as a K-major, 128-byte-swizzled A operand (one 128-byte row per output row: 64/Cin offsets
 // side by side, missing neighbours zero-filled), streams the matching pre-tiled weight block as the B
 // operand with a bulk asynchronous copy, and issues tcgen05.mma (M=128, N=Cout, K=16 x 4) into one
-// fp32 accumulator in tensor memory that stays resident across all offsets. The epilogue reads the
+// fp32 accumulator in tensor memory that stays resident across all offsets. A CTA iteration covers
+// four such tiles (512 rows, four accumulators) with the offset loop outermost, so that a weight block
+// is fetched once per four tiles; (tile, offset group) pairs without any neighbour are skipped using
+// the per-tile offset masks the rulebook kernels produce. The epilogue reads the
 // accumulator with tcgen05.ld, applies the folded BatchNorm scale/shift and ReLU, and stores fp16
 // rows (and, for the last layer, scatters them into the dense BEV map).
 //
-// Warp roles (192 threads): warps 0-3 gather A tiles with 16-byte cp.async and later run the
+// Warp roles (224 threads): warps 0-3 gather A tiles with 16-byte cp.async and later run the
 // epilogue; warp 4 owns tensor memory and issues the MMAs from one thread; warp 5 streams the weight
-// blocks. Stages hand over through mbarriers; every wait is bounded by a clock limit, after which the
+// blocks; warp 6 copies the neighbour indices of upcoming stages into a small ring ahead of the gathers. Stages hand over through mbarriers; every wait is bounded by a clock limit, after which the
 // CTA raises SESSD_STATUS_TIMEOUT, stops issuing work, frees its tensor memory and returns.
 #include <string>
 #include <vector>
@@ -24,11 +27,25 @@ namespace sessd {
 namespace {
 
 constexpr int TILE_M = 128;
-constexpr int STAGES = 4;
-constexpr int LAG = 2;                       // gather groups kept in flight before a stage is published
+constexpr int TILES = 4;                     // row tiles per CTA iteration; they share each weight block
+constexpr int A_STAGES_MAX = 6;
+constexpr int B_STAGES = 2;
+// Ring depth chosen so that two CTAs fit one SM (about 113 KB of shared memory each): 64-wide outputs
+// have 8 KB weight blocks and get 5 gather stages, narrower ones 6. LAG gather groups stay in flight
+// before a stage is published to the MMA warp.
+constexpr int IDX_STAGES = 6;                // ring of neighbour-index blocks, filled ahead by the index warp
+constexpr int IDX_LAG = 4;
+template <int CIN, int COUT>
+struct RingCfg {
+    static constexpr int KG = 64 / CIN;
+    static constexpr int FIXED = 1024 + 2 * COUT * 128 + IDX_STAGES * KG * 512 + 2 * COUT * 4 + 256;
+    static constexpr int FIT = (115712 - FIXED) / (128 * 128);
+    static constexpr int A_STAGES = FIT >= 6 ? 6 : FIT;
+    static constexpr int LAG = A_STAGES - 2;
+};
 constexpr int ROW_BYTES = 128;               // 64 halves per A/B row
 constexpr int A_BYTES = TILE_M * ROW_BYTES;  // 16 KB
-constexpr int UMMA_THREADS = 192;
+constexpr int UMMA_THREADS = 224;
 constexpr int KVOL_MAX = 27;
 constexpr long long WAIT_LIMIT_CYCLES = 4000000000LL;  // about two seconds
 
@@ -127,40 +144,65 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
 struct SharedCtl {
-    unsigned long long full[STAGES];
-    unsigned long long empty[STAGES];
+    unsigned long long a_full[A_STAGES_MAX];
+    unsigned long long a_empty[A_STAGES_MAX];
+    unsigned long long b_full[B_STAGES];
+    unsigned long long b_empty[B_STAGES];
+    unsigned long long i_full[IDX_STAGES];
+    unsigned long long i_empty[IDX_STAGES];
     unsigned long long acc_full;
+    unsigned long long acc_empty;
     uint32_t tmem_base;
-    uint32_t stage_mask;
     int abort_flag;
-    int pad;
 };
 
-template <int COUT>
+template <int CIN, int COUT>
 constexpr int umma_smem_bytes() {
-    return 1024 /*alignment slack*/ + STAGES * (A_BYTES + COUT * ROW_BYTES) + KVOL_MAX * TILE_M * 4 + 2 * COUT * 4 +
-           (int)sizeof(SharedCtl);
+    return 1024 /*alignment slack*/ + RingCfg<CIN, COUT>::A_STAGES * A_BYTES + B_STAGES * COUT * ROW_BYTES +
+           IDX_STAGES * (64 / CIN) * TILE_M * 4 + 2 * COUT * 4 + (int)sizeof(SharedCtl);
+}
+
+// Offsets g*KG .. g*KG+KG-1 of a tile's 27-bit offset mask.
+template <int KG>
+__device__ __forceinline__ bool stage_active(uint32_t kmask, int g) {
+    return ((kmask >> (g * KG)) & ((1u << KG) - 1u)) != 0u;
+}
+
+// Advances (g, t) to the next (stage, tile) pair with work, in the order stage-major, tile-minor.
+template <int KG>
+__device__ __forceinline__ bool next_item(const uint32_t (&m)[TILES], int nstages, int& g, int& t) {
+    for (;;) {
+        if (++t == TILES) {
+            t = 0;
+            ++g;
+        }
+        if (g >= nstages) return false;
+        if (stage_active<KG>(m[t], g)) return true;
+    }
 }
 
 template <int CIN, int COUT>
 __global__ void __launch_bounds__(UMMA_THREADS, 2)
 conv_umma_kernel(const __half* __restrict__ in, __half* __restrict__ out, const int32_t* __restrict__ nbr,
-                 const int32_t* __restrict__ out_num, const uint8_t* __restrict__ wtiles,
-                 const float* __restrict__ scale, const float* __restrict__ shift, int relu, int batch,
-                 int max_voxels, int kvol, __half* __restrict__ dense, const int4* __restrict__ out_coors, int D, int H,
-                 int W, int32_t* status) {
+                 const uint32_t* __restrict__ tile_mask, const int32_t* __restrict__ out_num,
+                 const uint8_t* __restrict__ wtiles, const float* __restrict__ scale, const float* __restrict__ shift,
+                 int relu, int batch, int max_voxels, int kvol, __half* __restrict__ dense,
+                 const int4* __restrict__ out_coors, int D, int H, int W, int32_t* status) {
     constexpr int KG = 64 / CIN;            // kernel offsets sharing one 128-byte A row
     constexpr int CPO = CIN / 8;            // 16-byte chunks per offset
     constexpr int B_BYTES = COUT * ROW_BYTES;
-    constexpr int TMEM_COLS = COUT < 32 ? 32 : COUT;
+    constexpr int A_STAGES = RingCfg<CIN, COUT>::A_STAGES;
+    constexpr int LAG = RingCfg<CIN, COUT>::LAG;
+    constexpr int IDX_WORDS = KG * TILE_M;  // one index block: KG offsets x 128 rows
+    constexpr int TMEM_COLS = TILES * COUT < 32 ? 32 : TILES * COUT;
     constexpr uint32_t IDESC = umma_idesc(COUT);
 
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint8_t* sA = smem;
-    uint8_t* sB = sA + STAGES * A_BYTES;
-    int32_t* s_nbr = reinterpret_cast<int32_t*>(sB + STAGES * B_BYTES);
-    float* s_scale = reinterpret_cast<float*>(s_nbr + KVOL_MAX * TILE_M);
+    uint8_t* sB = sA + A_STAGES * A_BYTES;
+    int32_t* s_idx = reinterpret_cast<int32_t*>(sB + B_STAGES * B_BYTES);
+    float* s_scale = reinterpret_cast<float*>(s_idx + IDX_STAGES * IDX_WORDS);
     float* s_shift = s_scale + COUT;
     SharedCtl* ctl = reinterpret_cast<SharedCtl*>(s_shift + COUT);
 
@@ -168,12 +210,20 @@ conv_umma_kernel(const __half* __restrict__ in, __half* __restrict__ out, const 
     const int nstages = (kvol + KG - 1) / KG;
 
     if (tid == 0) {
-        for (int s = 0; s < STAGES; ++s) {
-            mbar_init(smem_u32(&ctl->full[s]), TILE_M + 1);
-            mbar_init(smem_u32(&ctl->empty[s]), 1);
+        for (int s = 0; s < A_STAGES; ++s) {
+            mbar_init(smem_u32(&ctl->a_full[s]), TILE_M);
+            mbar_init(smem_u32(&ctl->a_empty[s]), 1);
+        }
+        for (int s = 0; s < B_STAGES; ++s) {
+            mbar_init(smem_u32(&ctl->b_full[s]), 1);
+            mbar_init(smem_u32(&ctl->b_empty[s]), 1);
+        }
+        for (int s = 0; s < IDX_STAGES; ++s) {
+            mbar_init(smem_u32(&ctl->i_full[s]), 32);
+            mbar_init(smem_u32(&ctl->i_empty[s]), TILE_M);
         }
         mbar_init(smem_u32(&ctl->acc_full), 1);
-        ctl->stage_mask = 0;
+        mbar_init(smem_u32(&ctl->acc_empty), TILE_M);
         ctl->abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -194,71 +244,75 @@ conv_umma_kernel(const __half* __restrict__ in, __half* __restrict__ out, const 
     volatile int* abort_flag = &ctl->abort_flag;
 
     const int tiles_per_frame = (max_voxels + TILE_M - 1) / TILE_M;
-    const int items = batch * tiles_per_frame;
-    uint32_t it = 0;        // stages consumed so far by this CTA (same value in every role)
-    uint32_t tile_iter = 0; // tiles with at least one active stage processed so far
+    const int supers_per_frame = (tiles_per_frame + TILES - 1) / TILES;
+    const int items = batch * supers_per_frame;
+    uint32_t a_it = 0, b_it = 0, st_it = 0;   // ring positions; every role advances them identically
 
     for (int item = blockIdx.x; item < items; item += gridDim.x) {
-        const int b = item / tiles_per_frame;
-        const int row0 = (item - b * tiles_per_frame) * TILE_M;
+        const int b = item / supers_per_frame;
+        const int tile0 = (item - b * supers_per_frame) * TILES;
+        const int row0 = tile0 * TILE_M;
         int n = out_num[b];
         n = n > max_voxels ? max_voxels : n;
-        if (row0 >= n) continue;  // uniform over the CTA
-
-        tc_fence_before();
-        __syncthreads();  // previous tile completely finished: s_nbr and the accumulator are free
+        if (row0 >= n) continue;
         if (*abort_flag) break;
-        if (tid == 0) ctl->stage_mask = 0;
-        __syncthreads();
-        {
-            uint32_t m = 0;
-            const int32_t* src = nbr + (size_t)b * kvol * max_voxels + row0;
-            for (int e = tid; e < kvol * TILE_M; e += UMMA_THREADS) {
-                const int k = e / TILE_M, r = e - k * TILE_M;
-                const int v = (row0 + r < n) ? __ldg(src + (size_t)k * max_voxels + r) : -1;
-                s_nbr[e] = v;
-                if (v >= 0) m |= 1u << (k / KG);
-            }
-            m = __reduce_or_sync(0xFFFFFFFFu, m);
-            if (lane == 0 && m) atomicOr(&ctl->stage_mask, m);
+        uint32_t m[TILES];
+        uint32_t any = 0;
+#pragma unroll
+        for (int t = 0; t < TILES; ++t) {
+            m[t] = (row0 + t * TILE_M < n) ? __ldg(tile_mask + (size_t)b * tiles_per_frame + tile0 + t) : 0u;
+            any |= m[t];
         }
-        __syncthreads();
-        tc_fence_after();
-        const uint32_t mask = ctl->stage_mask;
-        const int nactive = __popc(mask);
+        int n_a = 0, n_b = 0;   // A and B stages this super-tile consumes
+        for (int g = 0; g < nstages; ++g) {
+            int act = 0;
+#pragma unroll
+            for (int t = 0; t < TILES; ++t) act += stage_active<KG>(m[t], g) ? 1 : 0;
+            n_a += act;
+            n_b += act ? 1 : 0;
+        }
 
         if (warp < 4) {
             // ---------------- gather producers ----------------
             const int c = tid & 7;                 // 16-byte chunk of the 128-byte row
-            const int koff = c / CPO;              // which offset of the stage's group this chunk belongs to
+            const int koff = c / CPO;              // offset of the stage's group this chunk belongs to
             const int csub = (c % CPO) * 8;        // first channel of the chunk
             const __half* in_b = in + (size_t)b * max_voxels * CIN;
             uint32_t pending[LAG + 1];
             int npending = 0;
-            uint32_t my_it = it;
+            uint32_t my_a = a_it;
             bool ok = true;
-            for (int g = 0; g < nstages && ok; ++g) {
-                if (!((mask >> g) & 1u)) continue;
-                const uint32_t s = my_it % STAGES;
-                ok = mbar_wait(smem_u32(&ctl->empty[s]), ((my_it / STAGES) & 1u) ^ 1u, abort_flag);
+            int g = -1, t = TILES - 1;
+            while (ok && next_item<KG>(m, nstages, g, t)) {
+                const uint32_t s = my_a % A_STAGES, si = my_a % IDX_STAGES;
+                // row indices of this stage, fetched ahead of time by the index warp
+                ok = mbar_wait(smem_u32(&ctl->i_full[si]), (my_a / IDX_STAGES) & 1u, abort_flag);
                 if (!ok) break;
                 const int k = g * KG + koff;
+                int idx[TILE_M / 16];
+#pragma unroll
+                for (int p = 0; p < TILE_M / 16; ++p) {
+                    const int r = (tid >> 3) + 16 * p;
+                    const int v = s_idx[si * IDX_WORDS + koff * TILE_M + r];
+                    idx[p] = (k < kvol && row0 + t * TILE_M + r < n) ? v : -1;
+                }
+                mbar_arrive(smem_u32(&ctl->i_empty[si]));
+                ok = mbar_wait(smem_u32(&ctl->a_empty[s]), ((my_a / A_STAGES) & 1u) ^ 1u, abort_flag);
+                if (!ok) break;
                 const uint32_t a_base = smem_u32(sA + s * A_BYTES);
 #pragma unroll
                 for (int p = 0; p < TILE_M / 16; ++p) {
                     const int r = (tid >> 3) + 16 * p;
-                    const int idx = (k < kvol) ? s_nbr[k * TILE_M + r] : -1;
-                    const __half* src = in_b + (size_t)(idx < 0 ? 0 : idx) * CIN + csub;
-                    const uint32_t dst = a_base + r * ROW_BYTES + ((c ^ (r & 7)) << 4);
-                    cp_async_16(dst, src, idx < 0 ? 0u : 16u);
+                    const __half* src = in_b + (size_t)(idx[p] < 0 ? 0 : idx[p]) * CIN + csub;
+                    cp_async_16(a_base + r * ROW_BYTES + ((c ^ (r & 7)) << 4), src, idx[p] < 0 ? 0u : 16u);
                 }
                 cp_async_commit();
                 pending[npending++] = s;
-                ++my_it;
+                ++my_a;
                 if (npending > LAG) {
                     cp_async_wait<LAG>();
                     fence_proxy_async();
-                    mbar_arrive(smem_u32(&ctl->full[pending[0]]));
+                    mbar_arrive(smem_u32(&ctl->a_full[pending[0]]));
 #pragma unroll
                     for (int q = 0; q < LAG; ++q) pending[q] = pending[q + 1];
                     --npending;
@@ -266,104 +320,171 @@ conv_umma_kernel(const __half* __restrict__ in, __half* __restrict__ out, const 
             }
             cp_async_wait<0>();
             fence_proxy_async();
-            for (int q = 0; q < npending; ++q) mbar_arrive(smem_u32(&ctl->full[pending[q]]));
+            for (int q = 0; q < npending; ++q) mbar_arrive(smem_u32(&ctl->a_full[pending[q]]));
 
             // ---------------- epilogue ----------------
-            const int row = row0 + tid;
-            float acc[COUT];
-            bool have = false;
-            if (nactive > 0) {
-                bool got = ok && mbar_wait(smem_u32(&ctl->acc_full), tile_iter & 1u, abort_flag);
+            bool got = true;
+            if (any) {
+                got = ok && mbar_wait(smem_u32(&ctl->acc_full), st_it & 1u, abort_flag);
                 got = __all_sync(0xFFFFFFFFu, got);
-                if (got) {
-                    tc_fence_after();
+                if (got) tc_fence_after();
+            }
+#pragma unroll 1
+            for (int t2 = 0; t2 < TILES; ++t2) {
+                const int row = row0 + t2 * TILE_M + tid;
+                float acc[COUT];
+                if (any && got && m[t2]) {
 #pragma unroll
                     for (int c0 = 0; c0 < COUT; c0 += 16) {
                         uint32_t r16[16];
-                        tmem_ld16(tmem + ((uint32_t)(warp * 32) << 16) + c0, r16);
+                        tmem_ld16(tmem + ((uint32_t)(warp * 32) << 16) + t2 * COUT + c0, r16);
 #pragma unroll
                         for (int j = 0; j < 16; ++j) acc[c0 + j] = __uint_as_float(r16[j]);
                     }
                     tmem_ld_wait();
-                    have = true;
+                } else {
+#pragma unroll
+                    for (int j = 0; j < COUT; ++j) acc[j] = 0.f;
                 }
-            } else {
+                if (got && row < n) {
+                    __half* dst = out + ((size_t)b * max_voxels + row) * COUT;
 #pragma unroll
-                for (int j = 0; j < COUT; ++j) acc[j] = 0.f;
-                have = true;
-            }
-            if (have && row < n) {
-                __half* dst = out + ((size_t)b * max_voxels + row) * COUT;
+                    for (int c0 = 0; c0 < COUT; c0 += 8) {
+                        uint4 pk;
+                        __half2* h = reinterpret_cast<__half2*>(&pk);
 #pragma unroll
-                for (int c0 = 0; c0 < COUT; c0 += 8) {
-                    uint4 pk;
-                    __half2* h = reinterpret_cast<__half2*>(&pk);
-#pragma unroll
-                    for (int j = 0; j < 4; ++j) {
-                        float v0 = fmaf(acc[c0 + 2 * j], s_scale[c0 + 2 * j], s_shift[c0 + 2 * j]);
-                        float v1 = fmaf(acc[c0 + 2 * j + 1], s_scale[c0 + 2 * j + 1], s_shift[c0 + 2 * j + 1]);
-                        if (relu) {
-                            v0 = v0 > 0.f ? v0 : 0.f;
-                            v1 = v1 > 0.f ? v1 : 0.f;
+                        for (int j = 0; j < 4; ++j) {
+                            float v0 = fmaf(acc[c0 + 2 * j], s_scale[c0 + 2 * j], s_shift[c0 + 2 * j]);
+                            float v1 = fmaf(acc[c0 + 2 * j + 1], s_scale[c0 + 2 * j + 1], s_shift[c0 + 2 * j + 1]);
+                            if (relu) {
+                                v0 = v0 > 0.f ? v0 : 0.f;
+                                v1 = v1 > 0.f ? v1 : 0.f;
+                            }
+                            acc[c0 + 2 * j] = v0;
+                            acc[c0 + 2 * j + 1] = v1;
+                            h[j] = __floats2half2_rn(v0, v1);
                         }
-                        acc[c0 + 2 * j] = v0;
-                        acc[c0 + 2 * j + 1] = v1;
-                        h[j] = __floats2half2_rn(v0, v1);
+                        *reinterpret_cast<uint4*>(dst + c0) = pk;
                     }
-                    *reinterpret_cast<uint4*>(dst + c0) = pk;
-                }
-                if (dense) {
-                    // fused BEV scatter (sparse2Dense.cu:201-206): channel c*D + z, pixel (y, x)
-                    const int4 c4 = __ldg(&out_coors[(size_t)b * max_voxels + row]);
-                    __half* d = dense + (size_t)b * COUT * D * H * W + ((size_t)c4.y * H + c4.z) * W + c4.w;
+                    if (dense) {
+                        // fused BEV scatter (sparse2Dense.cu:201-206): channel c*D + z, pixel (y, x)
+                        const int4 c4 = __ldg(&out_coors[(size_t)b * max_voxels + row]);
+                        __half* d = dense + (size_t)b * COUT * D * H * W + ((size_t)c4.y * H + c4.z) * W + c4.w;
 #pragma unroll
-                    for (int j = 0; j < COUT; ++j) d[(size_t)j * D * H * W] = __float2half_rn(acc[j]);
+                        for (int j = 0; j < COUT; ++j) d[(size_t)j * D * H * W] = __float2half_rn(acc[j]);
+                    }
                 }
+            }
+            if (any) {
+                tc_fence_before();
+                mbar_arrive(smem_u32(&ctl->acc_empty));   // the accumulators may be overwritten
             }
         } else if (warp == 4) {
             // ---------------- MMA issuer ----------------
-            if (lane == 0) {
-                uint32_t my_it = it;
-                bool first = true, ok = true;
+            if (lane == 0 && any) {
+                uint32_t my_a = a_it, my_b = b_it;
+                bool ok = true;
+                if (st_it > 0) ok = mbar_wait(smem_u32(&ctl->acc_empty), (st_it - 1u) & 1u, abort_flag);
+                if (ok) tc_fence_after();
+                uint32_t started = 0;
                 for (int g = 0; g < nstages && ok; ++g) {
-                    if (!((mask >> g) & 1u)) continue;
-                    const uint32_t s = my_it % STAGES;
-                    ok = mbar_wait(smem_u32(&ctl->full[s]), (my_it / STAGES) & 1u, abort_flag);
-                    if (!ok) break;
-                    tc_fence_after();
-                    const uint32_t a_addr = smem_u32(sA + s * A_BYTES), b_addr = smem_u32(sB + s * B_BYTES);
+                    bool stage_any = false;
 #pragma unroll
-                    for (int kk = 0; kk < 4; ++kk) {
-                        umma_f16(tmem, umma_desc(a_addr + kk * 32), umma_desc(b_addr + kk * 32), IDESC,
-                                 (first && kk == 0) ? 0u : 1u);
+                    for (int t = 0; t < TILES; ++t) stage_any |= stage_active<KG>(m[t], g);
+                    if (!stage_any) continue;
+                    const uint32_t sb = my_b % B_STAGES;
+                    ok = mbar_wait(smem_u32(&ctl->b_full[sb]), (my_b / B_STAGES) & 1u, abort_flag);
+                    if (!ok) break;
+                    const uint32_t b_addr = smem_u32(sB + sb * B_BYTES);
+                    for (int t = 0; t < TILES && ok; ++t) {
+                        if (!stage_active<KG>(m[t], g)) continue;
+                        const uint32_t sa = my_a % A_STAGES;
+                        ok = mbar_wait(smem_u32(&ctl->a_full[sa]), (my_a / A_STAGES) & 1u, abort_flag);
+                        if (!ok) break;
+                        tc_fence_after();
+                        const uint32_t a_addr = smem_u32(sA + sa * A_BYTES);
+#pragma unroll
+                        for (int kk = 0; kk < 4; ++kk) {
+                            umma_f16(tmem + t * COUT, umma_desc(a_addr + kk * 32), umma_desc(b_addr + kk * 32), IDESC,
+                                     (((started >> t) & 1u) || kk > 0) ? 1u : 0u);
+                        }
+                        started |= 1u << t;
+                        umma_commit(smem_u32(&ctl->a_empty[sa]));   // frees the A stage once these MMAs have read it
+                        ++my_a;
                     }
-                    first = false;
-                    umma_commit(smem_u32(&ctl->empty[s]));  // frees the stage once these MMAs have read it
-                    ++my_it;
+                    umma_commit(smem_u32(&ctl->b_empty[sb]));
+                    ++my_b;
                 }
-                if (ok && nactive > 0) umma_commit(smem_u32(&ctl->acc_full));
+                if (ok) umma_commit(smem_u32(&ctl->acc_full));
             }
             __syncwarp();
+        } else if (warp == 6) {
+            // ---------------- neighbour-index loader ----------------
+            // Copies, for every (stage, tile) pair in consumption order, the KG x 128 neighbour indices
+            // into the index ring with 4-byte cp.async, several blocks ahead of the gather warps. Rows
+            // past max_voxels are zero-filled; the gather warps ignore rows past the frame's row count.
+            const int32_t* nbr_b = nbr + (size_t)b * kvol * max_voxels;
+            uint32_t pending[IDX_LAG + 1];
+            int npending = 0;
+            uint32_t my_i = a_it;
+            bool ok = true;
+            int g = -1, t = TILES - 1;
+            while (ok && next_item<KG>(m, nstages, g, t)) {
+                const uint32_t si = my_i % IDX_STAGES;
+                ok = mbar_wait(smem_u32(&ctl->i_empty[si]), ((my_i / IDX_STAGES) & 1u) ^ 1u, abort_flag);
+                if (!ok) break;
+#pragma unroll
+                for (int j = 0; j < KG; ++j) {
+                    const int k = g * KG + j;
+#pragma unroll
+                    for (int q = 0; q < TILE_M / 32; ++q) {
+                        const int r = q * 32 + lane;
+                        const int row = row0 + t * TILE_M + r;
+                        const bool in_range = k < kvol && row < max_voxels;
+                        const int32_t* src = nbr_b + (in_range ? (size_t)k * max_voxels + row : 0);
+                        asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;" ::"r"(
+                                         smem_u32(&s_idx[si * IDX_WORDS + j * TILE_M + r])),
+                                     "l"(src), "r"(in_range ? 4u : 0u)
+                                     : "memory");
+                    }
+                }
+                cp_async_commit();
+                pending[npending++] = si;
+                ++my_i;
+                if (npending > IDX_LAG) {
+                    cp_async_wait<IDX_LAG>();
+                    mbar_arrive(smem_u32(&ctl->i_full[pending[0]]));
+#pragma unroll
+                    for (int q = 0; q < IDX_LAG; ++q) pending[q] = pending[q + 1];
+                    --npending;
+                }
+            }
+            cp_async_wait<0>();
+            for (int q = 0; q < npending; ++q) mbar_arrive(smem_u32(&ctl->i_full[pending[q]]));
         } else {
             // ---------------- weight streamer ----------------
             if (lane == 0) {
-                uint32_t my_it = it;
+                uint32_t my_b = b_it;
                 bool ok = true;
                 for (int g = 0; g < nstages && ok; ++g) {
-                    if (!((mask >> g) & 1u)) continue;
-                    const uint32_t s = my_it % STAGES;
-                    ok = mbar_wait(smem_u32(&ctl->empty[s]), ((my_it / STAGES) & 1u) ^ 1u, abort_flag);
+                    bool stage_any = false;
+#pragma unroll
+                    for (int t = 0; t < TILES; ++t) stage_any |= stage_active<KG>(m[t], g);
+                    if (!stage_any) continue;
+                    const uint32_t sb = my_b % B_STAGES;
+                    ok = mbar_wait(smem_u32(&ctl->b_empty[sb]), ((my_b / B_STAGES) & 1u) ^ 1u, abort_flag);
                     if (!ok) break;
-                    const uint32_t bar = smem_u32(&ctl->full[s]);
+                    const uint32_t bar = smem_u32(&ctl->b_full[sb]);
                     mbar_arrive_expect_tx(bar, B_BYTES);
-                    bulk_load(smem_u32(sB + s * B_BYTES), wtiles + (size_t)g * B_BYTES, B_BYTES, bar);
-                    ++my_it;
+                    bulk_load(smem_u32(sB + sb * B_BYTES), wtiles + (size_t)g * B_BYTES, B_BYTES, bar);
+                    ++my_b;
                 }
             }
             __syncwarp();
         }
-        it += nactive;
-        if (nactive > 0) ++tile_iter;
+        a_it += n_a;
+        b_it += n_b;
+        if (any) ++st_it;
     }
 
     tc_fence_before();
@@ -378,14 +499,14 @@ conv_umma_kernel(const __half* __restrict__ in, __half* __restrict__ out, const 
 template <int CIN, int COUT>
 int launch_one(const ConvLaunch& c, cudaStream_t stream) {
     static const std::string name = "conv_umma<f16," + std::to_string(CIN) + "," + std::to_string(COUT) + ">";
-    constexpr int smem = umma_smem_bytes<COUT>();
+    constexpr int smem = umma_smem_bytes<CIN, COUT>();
     static bool configured = false;
     if (!configured) {
         SESSD_CUDA(cudaFuncSetAttribute(conv_umma_kernel<CIN, COUT>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
         configured = true;
     }
     SESSD_LAUNCH_NAMED(name.c_str(), (conv_umma_kernel<CIN, COUT>), persistent_grid(2), UMMA_THREADS, smem, stream,
-                       static_cast<const __half*>(c.in), static_cast<__half*>(c.out), c.nbr, c.out_num,
+                       static_cast<const __half*>(c.in), static_cast<__half*>(c.out), c.nbr, c.tile_mask, c.out_num,
                        static_cast<const uint8_t*>(c.umma_weights), c.scale, c.shift, c.relu, c.batch, c.max_voxels,
                        c.kvol, static_cast<__half*>(c.dense), reinterpret_cast<const int4*>(c.out_coors), c.D, c.H, c.W,
                        c.status);
@@ -428,7 +549,7 @@ int conv_umma_pack_weights(const float* weights, int kvol, int cin, int cout, vo
 }
 
 int launch_conv_umma(const ConvLaunch& c, cudaStream_t stream) {
-    if (c.dtype != SESSD_F16 || !c.umma_weights || c.kvol > KVOL_MAX) return SESSD_ERR_UNSUPPORTED;
+    if (c.dtype != SESSD_F16 || !c.umma_weights || !c.tile_mask || c.kvol > KVOL_MAX) return SESSD_ERR_UNSUPPORTED;
 #define SESSD_CASE(CI, CO) \
     if (c.cin == CI && c.cout == CO) return launch_one<CI, CO>(c, stream);
     SESSD_CASE(16, 16)

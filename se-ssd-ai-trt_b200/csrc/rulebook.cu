@@ -188,7 +188,235 @@ count_pairs_kernel(const int32_t* __restrict__ nbr, const int32_t* __restrict__ 
     if (threadIdx.x == 0 && sum) atomicAdd(total, (unsigned long long)sum);
 }
 
+// ---- x-grouped coordinate table ---------------------------------------------------------------
+// A bucket is one 32-byte sector: the rows of the 4 cells that share (z, y, x >> 2), then the group
+// key. The three x-neighbours of a cell lie in at most two buckets, so a 3x3x3 neighbourhood costs 9-18
+// sector reads instead of 27 probes of a flat table.
+
+__global__ void __launch_bounds__(kThreads)
+bucket_build_kernel(const int4* __restrict__ coors, const int32_t* __restrict__ voxel_num, int batch, int max_voxels,
+                    int Z, int Y, int X, Buckets t, int32_t* status) {
+    const int chunks = (max_voxels + kThreads - 1) / kThreads;
+    const int items = batch * chunks;
+    for (int it = blockIdx.x; it < items; it += gridDim.x) {
+        const int b = it / chunks;
+        const int i = (it - b * chunks) * kThreads + threadIdx.x;
+        int n = voxel_num[b];
+        n = n > max_voxels ? max_voxels : n;
+        if (i >= n) continue;
+        const int4 c = __ldg(&coors[(size_t)b * max_voxels + i]);
+        if (c.y < 0 || c.y >= Z || c.z < 0 || c.z >= Y || c.w < 0 || c.w >= X) {
+            atomicOr(status, SESSD_STATUS_BAD_COORD);
+            continue;
+        }
+        const uint32_t key = ((uint32_t)c.y * Y + c.z) * X + c.w;
+        const uint32_t gkey = key >> 2;
+        uint32_t* base = t.data + (size_t)b * t.cap * 8;
+        uint32_t h = hash_slot(gkey, t.shift);
+        bool done = false;
+        for (uint32_t probe = 0; probe < t.cap && !done; ++probe) {
+            uint32_t* bk = base + (size_t)h * 8;
+            uint32_t cur = bk[4];
+            if (cur == kEmpty) cur = atomicCAS(&bk[4], kEmpty, gkey);
+            if (cur == kEmpty || cur == gkey) {
+                atomicMax(reinterpret_cast<int32_t*>(&bk[key & 3u]), i);  // duplicates: highest row wins
+                done = true;
+            }
+            h = (h + 1) & (t.cap - 1);
+        }
+        if (!done) atomicOr(status, SESSD_STATUS_HASH_FULL);
+    }
+}
+
+__device__ __forceinline__ bool bucket_find(const uint32_t* __restrict__ base, uint32_t cap, int shift, uint32_t gkey,
+                                            int4* vals) {
+    uint32_t h = hash_slot(gkey, shift);
+    for (uint32_t probe = 0; probe < cap; ++probe) {
+        const uint4* bk = reinterpret_cast<const uint4*>(base + (size_t)h * 8);
+        const uint4 hi = __ldg(bk + 1);
+        if (hi.x == gkey) {
+            const uint4 lo = __ldg(bk);
+            *vals = make_int4((int)lo.x, (int)lo.y, (int)lo.z, (int)lo.w);
+            return true;
+        }
+        if (hi.x == kEmpty) return false;
+        h = (h + 1) & (cap - 1);
+    }
+    return false;
+}
+
+__device__ __forceinline__ int pick4(const int4& v, uint32_t i) {
+    return i == 0 ? v.x : (i == 1 ? v.y : (i == 2 ? v.z : v.w));
+}
+
+// Submanifold 3x3x3 neighbour map. One thread per (output row, kz, ky): it resolves the three kx
+// neighbours from one or two buckets and writes nbr[b][k][o] for k = (kz*3 + ky)*3 + {0,1,2}. Threads of
+// a warp share (kz, ky) and cover 32 consecutive rows of one 128-row tile, so the writes are coalesced
+// and the per-tile offset mask (which offsets have any neighbour) costs one ballot per k.
+__global__ void __launch_bounds__(kThreads)
+nbr_build_subm_kernel(const int4* __restrict__ coors, const int32_t* __restrict__ voxel_num, int batch,
+                      int max_voxels, int Z, int Y, int X, Buckets t, int32_t* __restrict__ nbr,
+                      uint32_t* __restrict__ tile_mask, int tiles_per_frame) {
+    const int chunks = (max_voxels + kThreads - 1) / kThreads;
+    const int items = batch * 9 * chunks;
+    for (int it = blockIdx.x; it < items; it += gridDim.x) {
+        const int b = it / (9 * chunks);
+        const int r = it - b * (9 * chunks);
+        const int j = r / chunks;
+        const int o = (r - j * chunks) * kThreads + threadIdx.x;
+        int n = voxel_num[b];
+        n = n > max_voxels ? max_voxels : n;
+        const bool live = o < n;
+        int res[3] = {-1, -1, -1};
+        if (live) {
+            const int4 c = __ldg(&coors[(size_t)b * max_voxels + o]);
+            const int kz = j / 3, ky = j - kz * 3;
+            const int z = c.y + kz - 1, y = c.z + ky - 1, x = c.w;
+            if (z >= 0 && z < Z && y >= 0 && y < Y && x >= 0 && x < X) {
+                const uint32_t center = ((uint32_t)z * Y + y) * X + x;
+                const uint32_t k_lo = x > 0 ? center - 1 : center, k_hi = x + 1 < X ? center + 1 : center;
+                const uint32_t g_lo = k_lo >> 2, g_hi = k_hi >> 2;
+                const uint32_t* base = t.data + (size_t)b * t.cap * 8;
+                int4 va = make_int4(-1, -1, -1, -1), vb = va;
+                bucket_find(base, t.cap, t.shift, g_lo, &va);
+                if (g_hi != g_lo) bucket_find(base, t.cap, t.shift, g_hi, &vb); else vb = va;
+#pragma unroll
+                for (int d = 0; d < 3; ++d) {
+                    const int xx = x + d - 1;
+                    if (xx < 0 || xx >= X) continue;
+                    const uint32_t key = center + d - 1;
+                    res[d] = pick4((key >> 2) == g_lo ? va : vb, key & 3u);
+                }
+            }
+        }
+        uint32_t bits = 0;
+#pragma unroll
+        for (int d = 0; d < 3; ++d) {
+            const int k = j * 3 + d;
+            if (live) nbr[((size_t)b * 27 + k) * max_voxels + o] = res[d];
+            if (__ballot_sync(0xFFFFFFFFu, res[d] >= 0)) bits |= 1u << k;
+        }
+        if ((threadIdx.x & 31) == 0 && bits && live)
+            atomicOr(&tile_mask[(size_t)b * tiles_per_frame + (o >> 7)], bits);
+    }
+}
+
+// Strided layers: the neighbour map falls out of the candidate entries. Entry t = (input row i,
+// candidate e) with output row id contributes nbr[b][k][id] = i, k = in - out*stride + pad per axis
+// (sparseConv3dlayer.cu:366). The map must have been filled with -1 for rows < out_num beforehand.
+__global__ void __launch_bounds__(kThreads)
+nbr_scatter_strided_kernel(const int4* __restrict__ in_coors, const int32_t* __restrict__ in_num, int batch,
+                           int max_voxels, ConvGeom g, Table out_table, const int32_t* __restrict__ slot_of,
+                           int32_t* __restrict__ nbr, uint32_t* __restrict__ tile_mask, int tiles_per_frame) {
+    const int64_t per_frame = (int64_t)max_voxels * g.ncand;
+    const int chunks = (int)((per_frame + kThreads - 1) / kThreads);
+    const int items = batch * chunks;
+    for (int it = blockIdx.x; it < items; it += gridDim.x) {
+        const int b = it / chunks;
+        const int t = (it - b * chunks) * kThreads + threadIdx.x;
+        int n = in_num[b];
+        n = n > max_voxels ? max_voxels : n;
+        if (t >= n * g.ncand) continue;
+        const int slot = slot_of[(size_t)b * per_frame + t];
+        if (slot < 0) continue;
+        const int id = out_table.vals[(size_t)b * out_table.cap + slot];
+        if (id < 0) continue;  // output dropped by the max_voxels cap
+        const int i = t / g.ncand, e = t - i * g.ncand;
+        const int4 c4 = __ldg(&in_coors[(size_t)b * max_voxels + i]);
+        const int c[3] = {c4.y, c4.z, c4.w};
+        int hi[3], span[3];
+#pragma unroll
+        for (int j = 0; j < 3; ++j) {
+            const int lo = (c[j] - (g.K[j] - 1) * g.dil - 1 + g.S[j] + g.P[j]) / g.S[j];
+            hi[j] = (c[j] + g.P[j]) / g.S[j];
+            span[j] = (hi[j] - lo) / g.dil + 1;
+        }
+        const int cx = e % span[2], cy = (e / span[2]) % span[1], cz = e / (span[2] * span[1]);
+        const int oz = hi[0] - cz * g.dil, oy = hi[1] - cy * g.dil, ox = hi[2] - cx * g.dil;
+        const int kz = c[0] - oz * g.S[0] + g.P[0], ky = c[1] - oy * g.S[1] + g.P[1], kx = c[2] - ox * g.S[2] + g.P[2];
+        const int k = (kz * g.K[1] + ky) * g.K[2] + kx;
+        nbr[((size_t)b * g.kvol + k) * max_voxels + id] = i;
+        uint32_t* m = &tile_mask[(size_t)b * tiles_per_frame + (id >> 7)];
+        if (!((*reinterpret_cast<volatile uint32_t*>(m) >> k) & 1u)) atomicOr(m, 1u << k);
+    }
+}
+
+// Fills nbr[b][k][0 .. out_num[b]) with -1 (one int4 per thread where aligned).
+__global__ void __launch_bounds__(kThreads)
+nbr_clear_kernel(int32_t* __restrict__ nbr, const int32_t* __restrict__ out_num, int batch, int max_voxels, int kvol) {
+    const int chunks = (max_voxels + kThreads * 4 - 1) / (kThreads * 4);
+    const int items = batch * kvol * chunks;
+    for (int it = blockIdx.x; it < items; it += gridDim.x) {
+        const int bk = it / chunks;
+        const int b = bk / kvol;
+        const int o = ((it - bk * chunks) * kThreads + threadIdx.x) * 4;
+        int n = out_num[b];
+        n = n > max_voxels ? max_voxels : n;
+        if (o >= n) continue;
+        int32_t* p = nbr + (size_t)bk * max_voxels + o;
+        if ((max_voxels & 3) == 0) {
+            *reinterpret_cast<int4*>(p) = make_int4(-1, -1, -1, -1);   // may run up to 3 rows past n: inside the row block
+        } else {
+            for (int q = 0; q < 4 && o + q < max_voxels; ++q) p[q] = -1;
+        }
+    }
+}
+
+// Generic variant of the tile mask for maps built by nbr_build_kernel: one warp per (tile, k).
+__global__ void __launch_bounds__(kThreads)
+tile_mask_kernel(const int32_t* __restrict__ nbr, const int32_t* __restrict__ out_num, int batch, int max_voxels,
+                 int kvol, uint32_t* __restrict__ tile_mask, int tiles_per_frame) {
+    const int warps_per_block = kThreads / 32;
+    const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+    const int64_t items = (int64_t)batch * tiles_per_frame * kvol;
+    for (int64_t it = (int64_t)blockIdx.x * warps_per_block + w; it < items; it += (int64_t)gridDim.x * warps_per_block) {
+        const int k = (int)(it % kvol);
+        const int64_t bt = it / kvol;
+        const int tile = (int)(bt % tiles_per_frame), b = (int)(bt / tiles_per_frame);
+        int n = out_num[b];
+        n = n > max_voxels ? max_voxels : n;
+        bool any = false;
+        for (int q = 0; q < 4; ++q) {
+            const int o = tile * 128 + q * 32 + lane;
+            if (o < n && nbr[((size_t)b * kvol + k) * max_voxels + o] >= 0) any = true;
+        }
+        if (__ballot_sync(0xFFFFFFFFu, any) && lane == 0) atomicOr(&tile_mask[(size_t)b * tiles_per_frame + tile], 1u << k);
+    }
+}
+
 }  // namespace
+
+int launch_bucket_build(const int32_t* coors, const int32_t* voxel_num, int batch, int max_voxels, const int shape[3],
+                        const Buckets& t, int32_t* status, cudaStream_t stream) {
+    SESSD_LAUNCH(bucket_build_kernel, persistent_grid(8), kThreads, 0, stream, reinterpret_cast<const int4*>(coors),
+                 voxel_num, batch, max_voxels, shape[0], shape[1], shape[2], t, status);
+    return SESSD_OK;
+}
+
+int launch_nbr_build_subm(const int32_t* coors, const int32_t* voxel_num, int batch, int max_voxels, const int shape[3],
+                          const Buckets& t, int32_t* nbr, uint32_t* tile_mask, cudaStream_t stream) {
+    SESSD_LAUNCH(nbr_build_subm_kernel, persistent_grid(8), kThreads, 0, stream, reinterpret_cast<const int4*>(coors),
+                 voxel_num, batch, max_voxels, shape[0], shape[1], shape[2], t, nbr, tile_mask,
+                 (max_voxels + 127) / 128);
+    return SESSD_OK;
+}
+
+int launch_nbr_scatter_strided(const int32_t* in_coors, const int32_t* in_num, const int32_t* out_num, int batch,
+                               int max_voxels, const ConvGeom& g, const Table& out_table, const int32_t* slot_of,
+                               int32_t* nbr, uint32_t* tile_mask, cudaStream_t stream) {
+    SESSD_LAUNCH(nbr_clear_kernel, persistent_grid(8), kThreads, 0, stream, nbr, out_num, batch, max_voxels, g.kvol);
+    SESSD_LAUNCH(nbr_scatter_strided_kernel, persistent_grid(8), kThreads, 0, stream,
+                 reinterpret_cast<const int4*>(in_coors), in_num, batch, max_voxels, g, out_table, slot_of, nbr,
+                 tile_mask, (max_voxels + 127) / 128);
+    return SESSD_OK;
+}
+
+int launch_tile_mask(const int32_t* nbr, const int32_t* out_num, int batch, int max_voxels, int kvol,
+                     uint32_t* tile_mask, cudaStream_t stream) {
+    SESSD_LAUNCH(tile_mask_kernel, persistent_grid(8), kThreads, 0, stream, nbr, out_num, batch, max_voxels, kvol,
+                 tile_mask, (max_voxels + 127) / 128);
+    return SESSD_OK;
+}
 
 int launch_count_pairs(const int32_t* nbr, const int32_t* out_num, int batch, int max_voxels, int kvol,
                        unsigned long long* total, cudaStream_t stream) {
