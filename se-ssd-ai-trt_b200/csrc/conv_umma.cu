@@ -286,8 +286,14 @@ conv_umma_kernel(const __half* __restrict__ in, __half* __restrict__ out, const 
             while (ok && next_item<KG>(m, nstages, g, t)) {
                 const uint32_t s = my_a % A_STAGES, si = my_a % IDX_STAGES;
                 // row indices of this stage, fetched ahead of time by the index warp
+#ifdef SESSD_UMMA_TIMING
+                long long tq0 = clock64();
+#endif
                 ok = mbar_wait(smem_u32(&ctl->i_full[si]), (my_a / IDX_STAGES) & 1u, abort_flag);
                 if (!ok) break;
+#ifdef SESSD_UMMA_TIMING
+                long long tq1 = clock64();
+#endif
                 const int k = g * KG + koff;
                 int idx[TILE_M / 16];
 #pragma unroll
@@ -297,8 +303,14 @@ conv_umma_kernel(const __half* __restrict__ in, __half* __restrict__ out, const 
                     idx[p] = (k < kvol && row0 + t * TILE_M + r < n) ? v : -1;
                 }
                 mbar_arrive(smem_u32(&ctl->i_empty[si]));
+#ifdef SESSD_UMMA_TIMING
+                long long tq2 = clock64();
+#endif
                 ok = mbar_wait(smem_u32(&ctl->a_empty[s]), ((my_a / A_STAGES) & 1u) ^ 1u, abort_flag);
                 if (!ok) break;
+#ifdef SESSD_UMMA_TIMING
+                long long tq3 = clock64();
+#endif
                 const uint32_t a_base = smem_u32(sA + s * A_BYTES);
 #pragma unroll
                 for (int p = 0; p < TILE_M / 16; ++p) {
@@ -309,6 +321,9 @@ conv_umma_kernel(const __half* __restrict__ in, __half* __restrict__ out, const 
                 cp_async_commit();
                 pending[npending++] = s;
                 ++my_a;
+#ifdef SESSD_UMMA_TIMING
+                long long tq4 = clock64();
+#endif
                 if (npending > LAG) {
                     cp_async_wait<LAG>();
                     fence_proxy_async();
@@ -317,18 +332,35 @@ conv_umma_kernel(const __half* __restrict__ in, __half* __restrict__ out, const 
                     for (int q = 0; q < LAG; ++q) pending[q] = pending[q + 1];
                     --npending;
                 }
+#ifdef SESSD_UMMA_TIMING
+                if (tid == 0 && blockIdx.x < 4) {
+                    long long tq5 = clock64();
+                    unsigned long long* dbg = reinterpret_cast<unsigned long long*>(status) + 96 + blockIdx.x * 8;
+                    dbg[0] += (unsigned long long)(tq1 - tq0);  // wait index block
+                    dbg[1] += (unsigned long long)(tq3 - tq2);  // wait free A stage
+                    dbg[2] += (unsigned long long)(tq5 - tq4);  // wait own copies
+                    dbg[3] += (unsigned long long)(tq5 - tq0);  // whole iteration
+                    dbg[4] += 1;
+                }
+#endif
             }
             cp_async_wait<0>();
             fence_proxy_async();
             for (int q = 0; q < npending; ++q) mbar_arrive(smem_u32(&ctl->a_full[pending[q]]));
 
             // ---------------- epilogue ----------------
+#ifdef SESSD_UMMA_TIMING
+            long long te0 = clock64();
+#endif
             bool got = true;
             if (any) {
                 got = ok && mbar_wait(smem_u32(&ctl->acc_full), st_it & 1u, abort_flag);
                 got = __all_sync(0xFFFFFFFFu, got);
                 if (got) tc_fence_after();
             }
+#ifdef SESSD_UMMA_TIMING
+            long long te1 = clock64();
+#endif
 #pragma unroll 1
             for (int t2 = 0; t2 < TILES; ++t2) {
                 const int row = row0 + t2 * TILE_M + tid;
@@ -379,6 +411,14 @@ conv_umma_kernel(const __half* __restrict__ in, __half* __restrict__ out, const 
                 tc_fence_before();
                 mbar_arrive(smem_u32(&ctl->acc_empty));   // the accumulators may be overwritten
             }
+#ifdef SESSD_UMMA_TIMING
+            if (tid == 0 && blockIdx.x < 4) {
+                unsigned long long* dbg = reinterpret_cast<unsigned long long*>(status) + 96 + blockIdx.x * 8;
+                dbg[5] += (unsigned long long)(te1 - te0);          // wait for the accumulators
+                dbg[6] += (unsigned long long)(clock64() - te1);    // epilogue proper
+                dbg[7] += 1;
+            }
+#endif
         } else if (warp == 4) {
             // ---------------- MMA issuer ----------------
             if (lane == 0 && any) {
