@@ -12,7 +12,7 @@ import os
 
 import numpy as np
 
-from . import schedule, sharding, synth  # noqa: F401
+from . import plugins, schedule, sharding, synth  # noqa: F401
 from .build import LIB_PATH, build
 
 F32, F16 = 0, 1

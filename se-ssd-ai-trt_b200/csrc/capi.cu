@@ -449,7 +449,6 @@ static int conv_enqueue_common(const sessd_conv_params* p, const sessd_conv_weig
     if (rc) return rc;
     rc = launch_fill_zero(ws.tile_mask, ws.tile_mask_bytes, stream);
     if (rc) return rc;
-    const int32_t* out_coors = in_coors;
     const int32_t* out_num = in_num;
     if (subm && is_subm_333(g)) {
         rc = launch_bucket_build(in_coors, in_num, batch, maxV, g.in_shape, ws.buckets, ws.status, stream);
@@ -468,7 +467,6 @@ static int conv_enqueue_common(const sessd_conv_params* p, const sessd_conv_weig
                                    ws.chunks, static_cast<int32_t*>(outputs[1]), static_cast<int32_t*>(outputs[2]),
                                    ws.status, stream);
         if (rc) return rc;
-        out_coors = static_cast<const int32_t*>(outputs[1]);
         out_num = static_cast<const int32_t*>(outputs[2]);
         rc = launch_nbr_scatter_strided(in_coors, in_num, out_num, batch, maxV, g, ws.out_table, ws.slot_of, ws.nbr,
                                         ws.tile_mask, stream);
