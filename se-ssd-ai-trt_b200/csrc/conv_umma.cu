@@ -17,6 +17,7 @@
 // epilogue; warp 4 owns tensor memory and issues the MMAs from one thread; warp 5 streams the weight
 // blocks; warp 6 copies the neighbour indices of upcoming stages into a small ring ahead of the gathers. Stages hand over through mbarriers; every wait is bounded by a clock limit, after which the
 // CTA raises SESSD_STATUS_TIMEOUT, stops issuing work, frees its tensor memory and returns.
+#include <cstdlib>
 #include <string>
 #include <vector>
 
@@ -31,17 +32,15 @@ constexpr int TILES = 4;                     // row tiles per CTA iteration; the
 constexpr int A_STAGES_MAX = 6;
 constexpr int B_STAGES = 2;
 // Ring depth chosen so that two CTAs fit one SM (about 113 KB of shared memory each): 64-wide outputs
-// have 8 KB weight blocks and get 5 gather stages, narrower ones 6. LAG gather groups stay in flight
-// before a stage is published to the MMA warp.
+// have 8 KB weight blocks and get 5 gather stages, narrower ones 6. A stage is published to the MMA
+// warp by the copies themselves (cp.async mbarrier arrival), so every free stage can be in flight.
 constexpr int IDX_STAGES = 6;                // ring of neighbour-index blocks, filled ahead by the index warp
-constexpr int IDX_LAG = 4;
 template <int CIN, int COUT>
 struct RingCfg {
     static constexpr int KG = 64 / CIN;
     static constexpr int FIXED = 1024 + 2 * COUT * 128 + IDX_STAGES * KG * 512 + 2 * COUT * 4 + 256;
     static constexpr int FIT = (115712 - FIXED) / (128 * 128);
     static constexpr int A_STAGES = FIT >= 6 ? 6 : FIT;
-    static constexpr int LAG = A_STAGES - 2;
 };
 constexpr int ROW_BYTES = 128;               // 64 halves per A/B row
 constexpr int A_BYTES = TILE_M * ROW_BYTES;  // 16 KB
@@ -92,6 +91,11 @@ __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commi
 template <int N>
 __device__ __forceinline__ void cp_async_wait() {
     asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+// Arrival on `bar` that fires when all cp.async copies this thread has issued so far have landed
+// (the barrier's expected count must include it).
+__device__ __forceinline__ void cp_async_arrive_noinc(uint32_t bar) {
+    asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(bar) : "memory");
 }
 __device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
@@ -192,7 +196,6 @@ conv_umma_kernel(const __half* __restrict__ in, __half* __restrict__ out, const 
     constexpr int CPO = CIN / 8;            // 16-byte chunks per offset
     constexpr int B_BYTES = COUT * ROW_BYTES;
     constexpr int A_STAGES = RingCfg<CIN, COUT>::A_STAGES;
-    constexpr int LAG = RingCfg<CIN, COUT>::LAG;
     constexpr int IDX_WORDS = KG * TILE_M;  // one index block: KG offsets x 128 rows
     constexpr int TMEM_COLS = TILES * COUT < 32 ? 32 : TILES * COUT;
     constexpr uint32_t IDESC = umma_idesc(COUT);
@@ -278,8 +281,6 @@ conv_umma_kernel(const __half* __restrict__ in, __half* __restrict__ out, const 
             const int koff = c / CPO;              // offset of the stage's group this chunk belongs to
             const int csub = (c % CPO) * 8;        // first channel of the chunk
             const __half* in_b = in + (size_t)b * max_voxels * CIN;
-            uint32_t pending[LAG + 1];
-            int npending = 0;
             uint32_t my_a = a_it;
             bool ok = true;
             int g = -1, t = TILES - 1;
@@ -318,35 +319,19 @@ conv_umma_kernel(const __half* __restrict__ in, __half* __restrict__ out, const 
                     const __half* src = in_b + (size_t)(idx[p] < 0 ? 0 : idx[p]) * CIN + csub;
                     cp_async_16(a_base + r * ROW_BYTES + ((c ^ (r & 7)) << 4), src, idx[p] < 0 ? 0u : 16u);
                 }
-                cp_async_commit();
-                pending[npending++] = s;
+                cp_async_arrive_noinc(smem_u32(&ctl->a_full[s]));   // publishes the stage when the copies land
                 ++my_a;
-#ifdef SESSD_UMMA_TIMING
-                long long tq4 = clock64();
-#endif
-                if (npending > LAG) {
-                    cp_async_wait<LAG>();
-                    fence_proxy_async();
-                    mbar_arrive(smem_u32(&ctl->a_full[pending[0]]));
-#pragma unroll
-                    for (int q = 0; q < LAG; ++q) pending[q] = pending[q + 1];
-                    --npending;
-                }
 #ifdef SESSD_UMMA_TIMING
                 if (tid == 0 && blockIdx.x < 4) {
                     long long tq5 = clock64();
                     unsigned long long* dbg = reinterpret_cast<unsigned long long*>(status) + 96 + blockIdx.x * 8;
                     dbg[0] += (unsigned long long)(tq1 - tq0);  // wait index block
                     dbg[1] += (unsigned long long)(tq3 - tq2);  // wait free A stage
-                    dbg[2] += (unsigned long long)(tq5 - tq4);  // wait own copies
                     dbg[3] += (unsigned long long)(tq5 - tq0);  // whole iteration
                     dbg[4] += 1;
                 }
 #endif
             }
-            cp_async_wait<0>();
-            fence_proxy_async();
-            for (int q = 0; q < npending; ++q) mbar_arrive(smem_u32(&ctl->a_full[pending[q]]));
 
             // ---------------- epilogue ----------------
 #ifdef SESSD_UMMA_TIMING
@@ -441,6 +426,7 @@ conv_umma_kernel(const __half* __restrict__ in, __half* __restrict__ out, const 
                         const uint32_t sa = my_a % A_STAGES;
                         ok = mbar_wait(smem_u32(&ctl->a_full[sa]), (my_a / A_STAGES) & 1u, abort_flag);
                         if (!ok) break;
+                        fence_proxy_async();   // the gathered rows were written through the generic proxy
                         tc_fence_after();
                         const uint32_t a_addr = smem_u32(sA + sa * A_BYTES);
 #pragma unroll
@@ -464,8 +450,6 @@ conv_umma_kernel(const __half* __restrict__ in, __half* __restrict__ out, const 
             // into the index ring with 4-byte cp.async, several blocks ahead of the gather warps. Rows
             // past max_voxels are zero-filled; the gather warps ignore rows past the frame's row count.
             const int32_t* nbr_b = nbr + (size_t)b * kvol * max_voxels;
-            uint32_t pending[IDX_LAG + 1];
-            int npending = 0;
             uint32_t my_i = a_it;
             bool ok = true;
             int g = -1, t = TILES - 1;
@@ -488,19 +472,9 @@ conv_umma_kernel(const __half* __restrict__ in, __half* __restrict__ out, const 
                                      : "memory");
                     }
                 }
-                cp_async_commit();
-                pending[npending++] = si;
+                cp_async_arrive_noinc(smem_u32(&ctl->i_full[si]));
                 ++my_i;
-                if (npending > IDX_LAG) {
-                    cp_async_wait<IDX_LAG>();
-                    mbar_arrive(smem_u32(&ctl->i_full[pending[0]]));
-#pragma unroll
-                    for (int q = 0; q < IDX_LAG; ++q) pending[q] = pending[q + 1];
-                    --npending;
-                }
             }
-            cp_async_wait<0>();
-            for (int q = 0; q < npending; ++q) mbar_arrive(smem_u32(&ctl->i_full[pending[q]]));
         } else {
             // ---------------- weight streamer ----------------
             if (lane == 0) {
@@ -539,13 +513,18 @@ conv_umma_kernel(const __half* __restrict__ in, __half* __restrict__ out, const 
 template <int CIN, int COUT>
 int launch_one(const ConvLaunch& c, cudaStream_t stream) {
     static const std::string name = "conv_umma<f16," + std::to_string(CIN) + "," + std::to_string(COUT) + ">";
-    constexpr int smem = umma_smem_bytes<CIN, COUT>();
+    // Tuning knob for experiments: SESSD_UMMA_CTAS_PER_SM=1 pads the request so that one CTA fits per SM.
+    static const int ctas_per_sm = [] {
+        const char* e = std::getenv("SESSD_UMMA_CTAS_PER_SM");
+        return (e && e[0] == '1') ? 1 : 2;
+    }();
+    const int smem = ctas_per_sm == 1 ? 120 * 1024 : umma_smem_bytes<CIN, COUT>();
     static bool configured = false;
     if (!configured) {
         SESSD_CUDA(cudaFuncSetAttribute(conv_umma_kernel<CIN, COUT>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
         configured = true;
     }
-    SESSD_LAUNCH_NAMED(name.c_str(), (conv_umma_kernel<CIN, COUT>), persistent_grid(2), UMMA_THREADS, smem, stream,
+    SESSD_LAUNCH_NAMED(name.c_str(), (conv_umma_kernel<CIN, COUT>), persistent_grid(ctas_per_sm), UMMA_THREADS, smem, stream,
                        static_cast<const __half*>(c.in), static_cast<__half*>(c.out), c.nbr, c.tile_mask, c.out_num,
                        static_cast<const uint8_t*>(c.umma_weights), c.scale, c.shift, c.relu, c.batch, c.max_voxels,
                        c.kvol, static_cast<__half*>(c.dense), reinterpret_cast<const int4*>(c.out_coors), c.D, c.H, c.W,
