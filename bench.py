@@ -242,8 +242,12 @@ def main():
             dist.barrier()
         torch.cuda.synchronize()
 
-    for _ in range(max(args.warmup, 3)):
+    for i in range(max(args.warmup, 3)):
         pipe.run_device(d_pts, d_sizes)
+        if i == 0:   # fail fast if a kernel reported a bounded-wait timeout or a capacity problem
+            bad = pipe.status_bits()
+            if bad & ~pkg.STATUS_VOXEL_OVERFLOW:
+                raise SystemExit(f"device status {bad:#x} after the first pass: aborting the benchmark")
     barrier()
     sampler = ClockSampler(local)
     sampler.start()

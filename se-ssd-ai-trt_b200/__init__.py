@@ -361,6 +361,19 @@ class Pipeline:
                                              C.c_void_p(status.data_ptr()), C.byref(ms)), "sessd_pipeline_run_host")
         return float(ms.value)
 
+    def status_bits(self) -> int:
+        """OR of the status words of all stream workspaces (synchronises the device)."""
+        torch = _torch()
+        torch.cuda.synchronize()
+        bits = 0
+        for s in range(self.nstreams):
+            ws = lib().sessd_pipeline_workspace(self.handle, s)
+            rc = lib().sessd_read_status(C.c_void_p(ws), None)
+            if rc < 0:
+                _check(rc, "sessd_read_status")
+            bits |= rc
+        return bits
+
     def close(self):
         if self.handle:
             lib().sessd_pipeline_destroy(self.handle)

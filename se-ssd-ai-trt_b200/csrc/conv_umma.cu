@@ -13,9 +13,10 @@
 // accumulator with tcgen05.ld, applies the folded BatchNorm scale/shift and ReLU, and stores fp16
 // rows (and, for the last layer, scatters them into the dense BEV map).
 //
-// Warp roles (224 threads): warps 0-3 gather A tiles with 16-byte cp.async and later run the
-// epilogue; warp 4 owns tensor memory and issues the MMAs from one thread; warp 5 streams the weight
-// blocks; warp 6 copies the neighbour indices of upcoming stages into a small ring ahead of the gathers. Stages hand over through mbarriers; every wait is bounded by a clock limit, after which the
+// Warp roles (256 threads, two CTAs per SM): warps 0-3 gather A tiles with 16-byte cp.async and later run
+// the epilogue; warps 4 and 7 each issue the MMAs of two of the four row tiles from one thread (warp 4 also
+// owns the tensor memory allocation); warp 5 streams the weight blocks; warp 6 copies the neighbour
+// indices of upcoming stages into a small ring ahead of the gathers. Stages hand over through mbarriers; every wait is bounded by a clock limit, after which the
 // CTA raises SESSD_STATUS_TIMEOUT, stops issuing work, frees its tensor memory and returns.
 #include <cstdlib>
 #include <string>
@@ -44,9 +45,10 @@ struct RingCfg {
 };
 constexpr int ROW_BYTES = 128;               // 64 halves per A/B row
 constexpr int A_BYTES = TILE_M * ROW_BYTES;  // 16 KB
-constexpr int UMMA_THREADS = 224;
+constexpr int UMMA_THREADS = 256;
+constexpr int MMA_WARPS = 2;                 // MMA issuer warps (4 and 7); each owns TILES / MMA_WARPS row tiles
 constexpr int KVOL_MAX = 27;
-constexpr long long WAIT_LIMIT_CYCLES = 4000000000LL;  // about two seconds
+constexpr long long WAIT_LIMIT_CYCLES = 200000000LL;   // about a tenth of a second; real waits are microseconds
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
@@ -219,13 +221,13 @@ conv_umma_kernel(const __half* __restrict__ in, __half* __restrict__ out, const 
         }
         for (int s = 0; s < B_STAGES; ++s) {
             mbar_init(smem_u32(&ctl->b_full[s]), 1);
-            mbar_init(smem_u32(&ctl->b_empty[s]), 1);
+            mbar_init(smem_u32(&ctl->b_empty[s]), MMA_WARPS);   // every MMA issuer releases the weight block
         }
         for (int s = 0; s < IDX_STAGES; ++s) {
             mbar_init(smem_u32(&ctl->i_full[s]), 32);
             mbar_init(smem_u32(&ctl->i_empty[s]), TILE_M);
         }
-        mbar_init(smem_u32(&ctl->acc_full), 1);
+        mbar_init(smem_u32(&ctl->acc_full), MMA_WARPS);        // every MMA issuer reports its tiles
         mbar_init(smem_u32(&ctl->acc_empty), TILE_M);
         ctl->abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -404,44 +406,65 @@ conv_umma_kernel(const __half* __restrict__ in, __half* __restrict__ out, const 
                 dbg[7] += 1;
             }
 #endif
-        } else if (warp == 4) {
-            // ---------------- MMA issuer ----------------
+        } else if (warp == 4 || warp == 7) {
+            // ---------------- MMA issuers ----------------
+            // Issuing a tcgen05.mma or commit costs the issuing thread on the order of a hundred cycles, so
+            // two threads issue: warp 4 owns row tiles 0-1, warp 7 tiles 2-3 (disjoint accumulators).
             if (lane == 0 && any) {
+                constexpr int TPW = TILES / MMA_WARPS;
+                const int t_lo = warp == 4 ? 0 : TPW, t_hi = t_lo + TPW;
                 uint32_t my_a = a_it, my_b = b_it;
                 bool ok = true;
                 if (st_it > 0) ok = mbar_wait(smem_u32(&ctl->acc_empty), (st_it - 1u) & 1u, abort_flag);
                 if (ok) tc_fence_after();
                 uint32_t started = 0;
                 for (int g = 0; g < nstages && ok; ++g) {
-                    bool stage_any = false;
+                    int act = 0, before = 0;   // active tiles of this stage group: in total / before mine
+                    bool mine = false;
 #pragma unroll
-                    for (int t = 0; t < TILES; ++t) stage_any |= stage_active<KG>(m[t], g);
-                    if (!stage_any) continue;
+                    for (int t = 0; t < TILES; ++t) {
+                        const int a1 = stage_active<KG>(m[t], g) ? 1 : 0;
+                        act += a1;
+                        before += t < t_lo ? a1 : 0;
+                        mine |= (a1 != 0) && t >= t_lo && t < t_hi;
+                    }
+                    if (!act) continue;
                     const uint32_t sb = my_b % B_STAGES;
+                    // Both issuers wait for the block, also one with nothing to do for this group: its
+                    // release below must count for this use of the slot, not for an earlier one.
                     ok = mbar_wait(smem_u32(&ctl->b_full[sb]), (my_b / B_STAGES) & 1u, abort_flag);
                     if (!ok) break;
-                    const uint32_t b_addr = smem_u32(sB + sb * B_BYTES);
-                    for (int t = 0; t < TILES && ok; ++t) {
-                        if (!stage_active<KG>(m[t], g)) continue;
-                        const uint32_t sa = my_a % A_STAGES;
-                        ok = mbar_wait(smem_u32(&ctl->a_full[sa]), (my_a / A_STAGES) & 1u, abort_flag);
-                        if (!ok) break;
-                        fence_proxy_async();   // the gathered rows were written through the generic proxy
-                        tc_fence_after();
-                        const uint32_t a_addr = smem_u32(sA + sa * A_BYTES);
+                    if (mine) {
+                        const uint32_t b_addr = smem_u32(sB + sb * B_BYTES);
+                        uint32_t pos = my_a + before;
+                        for (int t = t_lo; t < t_hi && ok; ++t) {
+                            if (!stage_active<KG>(m[t], g)) continue;
+                            const uint32_t sa = pos % A_STAGES;
+                            ok = mbar_wait(smem_u32(&ctl->a_full[sa]), (pos / A_STAGES) & 1u, abort_flag);
+                            if (!ok) break;
+                            fence_proxy_async();   // the gathered rows were written through the generic proxy
+                            tc_fence_after();
+                            const uint32_t a_addr = smem_u32(sA + sa * A_BYTES);
 #pragma unroll
-                        for (int kk = 0; kk < 4; ++kk) {
-                            umma_f16(tmem + t * COUT, umma_desc(a_addr + kk * 32), umma_desc(b_addr + kk * 32), IDESC,
-                                     (((started >> t) & 1u) || kk > 0) ? 1u : 0u);
+                            for (int kk = 0; kk < 4; ++kk) {
+                                umma_f16(tmem + t * COUT, umma_desc(a_addr + kk * 32), umma_desc(b_addr + kk * 32), IDESC,
+                                         (((started >> t) & 1u) || kk > 0) ? 1u : 0u);
+                            }
+                            started |= 1u << t;
+                            umma_commit(smem_u32(&ctl->a_empty[sa]));   // frees the A stage once these MMAs have read it
+                            ++pos;
                         }
-                        started |= 1u << t;
-                        umma_commit(smem_u32(&ctl->a_empty[sa]));   // frees the A stage once these MMAs have read it
-                        ++my_a;
+                        if (ok) umma_commit(smem_u32(&ctl->b_empty[sb]));
+                    } else {
+                        mbar_arrive(smem_u32(&ctl->b_empty[sb]));   // nothing to read from this weight block
                     }
-                    umma_commit(smem_u32(&ctl->b_empty[sb]));
+                    my_a += act;
                     ++my_b;
                 }
-                if (ok) umma_commit(smem_u32(&ctl->acc_full));
+                if (ok) {
+                    if (started) umma_commit(smem_u32(&ctl->acc_full));
+                    else mbar_arrive(smem_u32(&ctl->acc_full));
+                }
             }
             __syncwarp();
         } else if (warp == 6) {
