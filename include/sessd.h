@@ -183,6 +183,24 @@ int sessd_sparse2dense_enqueue(const sessd_s2d_params* p, int batch, int max_vox
                                const void* const* inputs, void* const* outputs,
                                void* workspace, size_t workspace_bytes, void* stream);
 
+/* ZeroPad2dPlugin (zeroPad2d.h:18-87); the struct is its serialized blob (zeroPad2d.cu:286-289). */
+typedef struct sessd_pad2d_params {
+    int32_t top, bottom, left, right;
+} sessd_pad2d_params;
+
+/* Replaces ZeroPad2dPlugin::enqueue (zeroPad2d.cu:219-246) and zero_padding2d_kernel (:183-200):
+ * inputs = { map [B][C][H][W] }, outputs = { map [B][C][top+H+bottom][left+W+right] }, zero border.
+ * (The reference kernel indexes one frame only; here every frame of the batch is padded.) */
+int sessd_zero_pad2d_enqueue(const sessd_pad2d_params* pad, int batch, int channels, int height, int width, int dtype,
+                             const void* const* inputs, void* const* outputs, void* stream);
+
+/* Sparse2DensePlugin followed by ZeroPad2dPlugin in one pass (the pair wired at se-ssd-ai-trt.cpp:1251-1253):
+ * outputs = { dense [B][C*D][top+H+bottom][left+W+right] }, row i of the features lands at channel c*D+z,
+ * pixel (top + y, left + x); saves the intermediate map, its memset and the copy. */
+int sessd_sparse2dense_padded_enqueue(const sessd_s2d_params* p, const sessd_pad2d_params* pad, int batch,
+                                      int max_voxels, int dtype, const void* const* inputs, void* const* outputs,
+                                      void* stream);
+
 /* ------------------------------------------------------------------------------------------
  * Whole front end: voxelise -> conv stack (BN + ReLU folded) -> dense BEV, the layer sequence
  * wired at se-ssd-ai-trt.cpp:1138-1252, as one call. Coordinate tables and neighbour maps are built
@@ -203,6 +221,10 @@ size_t sessd_backbone_workspace_bytes(const sessd_backbone* bb, int batch, int m
 int sessd_backbone_enqueue(const sessd_backbone* bb, int batch, int max_points,
                            const void* points, const void* points_size, void* dense,
                            void* workspace, size_t workspace_bytes, void* stream);
+
+/* Folds the reference's ZeroPad2dPlugin into the backbone's dense output: after this call
+ * sessd_backbone_enqueue writes dense [B][C*D][top+H+bottom][left+W+right]. Call before creating pipelines. */
+int sessd_backbone_set_padding(sessd_backbone* bb, const sessd_pad2d_params* pad);
 
 /* Same work as sessd_backbone_enqueue, plus a count of the rulebook pairs of every layer (the P of the
  * flop count 2*P*Cin*Cout), copied to host_counts[nlayers] after synchronising the stream. For benchmarks

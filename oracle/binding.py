@@ -149,6 +149,16 @@ def sparse2dense(feat, coors, n, C_, D, H, W, batch=1):
     return dense
 
 
+def zero_pad2d(x, top, bottom, left, right):
+    x = np.ascontiguousarray(x, np.float32)
+    planes = int(np.prod(x.shape[:-2]))
+    H, W = x.shape[-2:]
+    out = np.zeros(x.shape[:-2] + (H + top + bottom, W + left + right), np.float32)
+    lib().oracle_zero_pad2d(_ptr(x, C.c_float), C.c_size_t(planes), C.c_int(H), C.c_int(W), C.c_int(top), C.c_int(bottom),
+                            C.c_int(left), C.c_int(right), _ptr(out, C.c_float))
+    return out
+
+
 def _vparams(point_range, voxel_size):
     xmin, ymin, zmin, xmax, ymax, zmax = point_range
     return np.asarray([xmin, xmax, ymin, ymax, zmin, zmax, *voxel_size, 0, 0, 0], np.float32)

@@ -404,6 +404,18 @@ void oracle_sparse2dense(const float* feat, const int32_t* coors, int n, int C, 
     }
 }
 
+// Zero padding of a [planes][H][W] map. Follows ZeroPad2dPlugin::enqueue (zeroPad2d.cu:219-246: output
+// cleared first) and zero_padding2d_kernel (:183-200: out[c][y+top][x+left] = in[c][y][x]). The reference
+// kernel never adds a batch offset (it runs batch 1); every plane of every frame is padded here.
+void oracle_zero_pad2d(const float* in, size_t planes, int H, int W, int top, int bottom, int left, int right,
+                       float* out) {
+    const int Hp = H + top + bottom, Wp = W + left + right;
+    std::memset(out, 0, sizeof(float) * planes * Hp * Wp);
+    for (size_t p = 0; p < planes; ++p)
+        for (int y = 0; y < H; ++y)
+            for (int x = 0; x < W; ++x) out[(p * Hp + y + top) * Wp + x + left] = in[(p * H + y) * W + x];
+}
+
 void oracle_round_half(float* x, size_t n) {
     for (size_t i = 0; i < n; ++i) x[i] = to_half_and_back(x[i]);
 }

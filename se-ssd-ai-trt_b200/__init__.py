@@ -23,7 +23,8 @@ EXPORTS = (
     "sessd_voxelize_enqueue_static",
     "sessd_conv_weights_create", "sessd_conv_weights_destroy", "sessd_conv_workspace_bytes",
     "sessd_subm_conv_enqueue", "sessd_sparse_conv_enqueue", "sessd_conv_rulebook_export",
-    "sessd_sparse2dense_enqueue", "sessd_backbone_create", "sessd_backbone_destroy",
+    "sessd_sparse2dense_enqueue", "sessd_sparse2dense_padded_enqueue", "sessd_zero_pad2d_enqueue",
+    "sessd_backbone_set_padding", "sessd_backbone_create", "sessd_backbone_destroy",
     "sessd_backbone_workspace_bytes", "sessd_backbone_enqueue", "sessd_backbone_pair_counts",
     "sessd_backbone_layer_view",
     "sessd_backbone_final_level", "sessd_pipeline_create", "sessd_pipeline_destroy", "sessd_pipeline_run_host",
@@ -51,6 +52,10 @@ class ConvParams(C.Structure):
                 ("spatial_shape_x", C.c_int32), ("spatial_shape_y", C.c_int32), ("spatial_shape_z", C.c_int32),
                 ("ksize", C.c_int32 * 3), ("stride", C.c_int32 * 3), ("padding", C.c_int32 * 3),
                 ("dilation", C.c_int32), ("out_padding", C.c_int32), ("subm", C.c_int32)]
+
+
+class Pad2DParams(C.Structure):
+    _fields_ = [("top", C.c_int32), ("bottom", C.c_int32), ("left", C.c_int32), ("right", C.c_int32)]
 
 
 class S2DParams(C.Structure):
@@ -243,14 +248,32 @@ def rulebook_export(params: ConvParams, B, frame, workspace, out_voxel_num):
     return pairs, num
 
 
-def sparse2dense(feat, coors, voxel_num, params: S2DParams, dtype=F32):
+def sparse2dense(feat, coors, voxel_num, params: S2DParams, dtype=F32, pad: Pad2DParams = None):
+    """Sparse rows -> dense BEV map; with `pad` the zero border of ZeroPad2dPlugin is written in the same pass."""
     torch = _torch()
     B, V = feat.shape[0], feat.shape[1]
-    dense = torch.empty((B, params.feature_map_channel * params.feature_map_size_z, params.feature_map_size_y,
-                         params.feature_map_size_x), dtype=_tdtype(dtype), device=feat.device)
-    _check(lib().sessd_sparse2dense_enqueue(C.byref(params), B, V, dtype, _vp(feat, coors, voxel_num), _vp(dense),
-                                            None, C.c_size_t(0), _stream()), "sessd_sparse2dense_enqueue")
+    ph = (pad.top + pad.bottom) if pad else 0
+    pw = (pad.left + pad.right) if pad else 0
+    dense = torch.empty((B, params.feature_map_channel * params.feature_map_size_z, params.feature_map_size_y + ph,
+                         params.feature_map_size_x + pw), dtype=_tdtype(dtype), device=feat.device)
+    if pad is None:
+        _check(lib().sessd_sparse2dense_enqueue(C.byref(params), B, V, dtype, _vp(feat, coors, voxel_num), _vp(dense),
+                                                None, C.c_size_t(0), _stream()), "sessd_sparse2dense_enqueue")
+    else:
+        _check(lib().sessd_sparse2dense_padded_enqueue(C.byref(params), C.byref(pad), B, V, dtype,
+                                                       _vp(feat, coors, voxel_num), _vp(dense), _stream()),
+               "sessd_sparse2dense_padded_enqueue")
     return dense
+
+
+def zero_pad2d(x, pad: Pad2DParams, dtype=F32):
+    """[B, C, H, W] -> [B, C, top+H+bottom, left+W+right] with a zero border (ZeroPad2dPlugin)."""
+    torch = _torch()
+    B, Cc, H, W = x.shape
+    out = torch.empty((B, Cc, H + pad.top + pad.bottom, W + pad.left + pad.right), dtype=_tdtype(dtype), device=x.device)
+    _check(lib().sessd_zero_pad2d_enqueue(C.byref(pad), B, Cc, H, W, dtype, _vp(x), _vp(out), _stream()),
+           "sessd_zero_pad2d_enqueue")
+    return out
 
 
 class Backbone:
@@ -286,9 +309,17 @@ class Backbone:
             raise SessdError("sessd_backbone_workspace_bytes rejected the parameters")
         return n
 
+    def set_padding(self, top, bottom, left, right):
+        """Folds ZeroPad2dPlugin into the dense output (call before run / before creating a Pipeline)."""
+        self.pad = Pad2DParams(top, bottom, left, right)
+        _check(lib().sessd_backbone_set_padding(self.handle, C.byref(self.pad)), "sessd_backbone_set_padding")
+
     def dense_shape(self, batch):
-        return (batch, self.s2d.feature_map_channel * self.s2d.feature_map_size_z, self.s2d.feature_map_size_y,
-                self.s2d.feature_map_size_x)
+        pad = getattr(self, "pad", None)
+        ph = (pad.top + pad.bottom) if pad else 0
+        pw = (pad.left + pad.right) if pad else 0
+        return (batch, self.s2d.feature_map_channel * self.s2d.feature_map_size_z, self.s2d.feature_map_size_y + ph,
+                self.s2d.feature_map_size_x + pw)
 
     def run(self, points, points_size, workspace=None, dense=None):
         """points cuda f32 [B, P, 4], points_size cuda i32 [B] -> (dense, workspace)."""

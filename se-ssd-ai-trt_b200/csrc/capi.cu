@@ -103,13 +103,14 @@ void conv_workspace_layout(Bump& bump, const sessd_conv_params* p, const ConvGeo
         w->ones_bytes = (size_t)batch * capb * 8 * sizeof(uint32_t);
     } else if (p->subm) {
         uint32_t* block = bump.take<uint32_t>(per * 2);
-        w->in_table = Table{block, nullptr, reinterpret_cast<int32_t*>(block ? block + per : nullptr), cap, shift, 1};
+        w->in_table = Table{block, nullptr, reinterpret_cast<int32_t*>(block ? block + per : nullptr), cap, shift, 1, 1};
         w->ones_base = block;
         w->ones_bytes = per * 2 * sizeof(uint32_t);
     } else {
         uint32_t* block = bump.take<uint32_t>(per * 3);
-        w->out_table = Table{block, block ? block + per : nullptr,
-                             reinterpret_cast<int32_t*>(block ? block + 2 * per : nullptr), cap, shift, 1};
+        // 64-bit slots (key << 32 | rank) followed by the row ids
+        w->out_table = Table{block ? block + 1 : nullptr, block, reinterpret_cast<int32_t*>(block ? block + 2 * per : nullptr),
+                             cap, shift, 2, 2};
         w->ones_base = block;
         w->ones_bytes = per * 3 * sizeof(uint32_t);
         w->slot_of = bump.take<int32_t>((size_t)batch * p->max_voxels * g.ncand);
@@ -149,6 +150,7 @@ struct sessd_backbone {
     sessd_voxel_params vp;
     sessd_s2d_params s2d;
     bool has_s2d;
+    sessd_pad2d_params pad;   // zero border folded into the dense output (all zero by default)
     int dtype;
     struct Layer {
         sessd_conv_params p;
@@ -218,8 +220,9 @@ void backbone_layout(Bump& bump, const sessd_backbone* bb, int batch, int max_po
     size_t off = 0;
     for (int l = 1; l < bb->nlevels; ++l) {
         uint32_t* base = block ? block + off : nullptr;
-        w->tables[l] = Table{base, base ? base + per : nullptr, reinterpret_cast<int32_t*>(base ? base + 2 * per : nullptr),
-                             cap, 32 - ilog2(cap), 1};
+        // 64-bit slots (key << 32 | rank) followed by the row ids
+        w->tables[l] = Table{base ? base + 1 : nullptr, base, reinterpret_cast<int32_t*>(base ? base + 2 * per : nullptr),
+                             cap, 32 - ilog2(cap), 2, 2};
         off += per * 3;
     }
     for (int l = 0; l < bb->nlevels; ++l)
@@ -540,7 +543,36 @@ int sessd_sparse2dense_enqueue(const sessd_s2d_params* p, int batch, int max_vox
     if (dtype != SESSD_F32 && dtype != SESSD_F16) return SESSD_ERR_PARAM;
     return launch_sparse2dense(inputs[0], static_cast<const int32_t*>(inputs[1]), static_cast<const int32_t*>(inputs[2]),
                                batch, max_voxels, p->feature_map_channel, p->feature_map_size_z, p->feature_map_size_y,
-                               p->feature_map_size_x, dtype, outputs[0], static_cast<cudaStream_t>(stream));
+                               p->feature_map_size_x, 0, 0, 0, 0, dtype, outputs[0], static_cast<cudaStream_t>(stream));
+}
+
+static bool pad_ok(const sessd_pad2d_params* p) {
+    return p->top >= 0 && p->bottom >= 0 && p->left >= 0 && p->right >= 0 && p->top < 4096 && p->bottom < 4096 &&
+           p->left < 4096 && p->right < 4096;
+}
+
+int sessd_sparse2dense_padded_enqueue(const sessd_s2d_params* p, const sessd_pad2d_params* pad, int batch,
+                                      int max_voxels, int dtype, const void* const* inputs, void* const* outputs,
+                                      void* stream) {
+    if (!p || !pad || !inputs || !outputs) return SESSD_ERR_NULL;
+    if (!inputs[0] || !inputs[1] || !inputs[2] || !outputs[0]) return SESSD_ERR_NULL;
+    if (batch < 1 || batch > kMaxBatch || max_voxels < 1 || p->feature_map_channel < 1 || p->feature_map_size_x < 1 ||
+        p->feature_map_size_y < 1 || p->feature_map_size_z < 1 || !pad_ok(pad))
+        return SESSD_ERR_PARAM;
+    if (dtype != SESSD_F32 && dtype != SESSD_F16) return SESSD_ERR_PARAM;
+    return launch_sparse2dense(inputs[0], static_cast<const int32_t*>(inputs[1]), static_cast<const int32_t*>(inputs[2]),
+                               batch, max_voxels, p->feature_map_channel, p->feature_map_size_z, p->feature_map_size_y,
+                               p->feature_map_size_x, pad->top, pad->bottom, pad->left, pad->right, dtype, outputs[0],
+                               static_cast<cudaStream_t>(stream));
+}
+
+int sessd_zero_pad2d_enqueue(const sessd_pad2d_params* pad, int batch, int channels, int height, int width, int dtype,
+                             const void* const* inputs, void* const* outputs, void* stream) {
+    if (!pad || !inputs || !outputs || !inputs[0] || !outputs[0]) return SESSD_ERR_NULL;
+    if (batch < 1 || batch > kMaxBatch || channels < 1 || height < 1 || width < 1 || !pad_ok(pad)) return SESSD_ERR_PARAM;
+    if (dtype != SESSD_F32 && dtype != SESSD_F16) return SESSD_ERR_PARAM;
+    return launch_zero_pad2d(inputs[0], outputs[0], (size_t)batch * channels, height, width, pad->top, pad->bottom,
+                             pad->left, pad->right, dtype, static_cast<cudaStream_t>(stream));
 }
 
 // ---- whole front end -------------------------------------------------------------------------
@@ -556,6 +588,7 @@ int sessd_backbone_create(const sessd_voxel_params* vp, const sessd_conv_params*
     bb->vp = *vp;
     bb->has_s2d = s2d != nullptr;
     if (s2d) bb->s2d = *s2d;
+    bb->pad = sessd_pad2d_params{0, 0, 0, 0};
     bb->dtype = dtype;
     bb->max_voxels = vp->max_voxels;
     bb->nlevels = 1;
@@ -648,7 +681,8 @@ static int backbone_enqueue_impl(const sessd_backbone* bb, int batch, int max_po
     if (rc) return rc;
     if (bb->has_s2d) {
         const size_t bytes = (size_t)batch * bb->s2d.feature_map_channel * bb->s2d.feature_map_size_z *
-                             bb->s2d.feature_map_size_y * bb->s2d.feature_map_size_x * esize(bb->dtype);
+                             (bb->s2d.feature_map_size_y + bb->pad.top + bb->pad.bottom) *
+                             (bb->s2d.feature_map_size_x + bb->pad.left + bb->pad.right) * esize(bb->dtype);
         if (bytes % 16 == 0)
             rc = launch_fill_zero(dense, bytes, stream);
         else
@@ -714,11 +748,13 @@ static int backbone_enqueue_impl(const sessd_backbone* bb, int batch, int max_po
         c.dtype = bb->dtype;
         c.status = w.status;
         if (bb->has_s2d && i + 1 == bb->layers.size()) {
-            c.dense = dense;
-            c.out_coors = w.coors[L.level_out];
+            // The padded plane is (top + H + bottom) x (left + W + right); starting the scatter (top, left)
+            // into it folds the reference's ZeroPad2dPlugin (zeroPad2d.cu:192-198) into this epilogue.
             c.D = bb->s2d.feature_map_size_z;
-            c.H = bb->s2d.feature_map_size_y;
-            c.W = bb->s2d.feature_map_size_x;
+            c.H = bb->s2d.feature_map_size_y + bb->pad.top + bb->pad.bottom;
+            c.W = bb->s2d.feature_map_size_x + bb->pad.left + bb->pad.right;
+            c.dense = static_cast<char*>(dense) + ((size_t)bb->pad.top * c.W + bb->pad.left) * esize(bb->dtype);
+            c.out_coors = w.coors[L.level_out];
         }
         rc = choose_conv(c, stream);
         if (rc) return rc;
@@ -763,6 +799,13 @@ int sessd_backbone_layer_view(const sessd_backbone* bb, int batch, int max_point
 
 int sessd_backbone_final_level(const sessd_backbone* bb) { return bb ? bb->nlevels - 1 : SESSD_ERR_NULL; }
 
+int sessd_backbone_set_padding(sessd_backbone* bb, const sessd_pad2d_params* pad) {
+    if (!bb || !pad) return SESSD_ERR_NULL;
+    if (!bb->has_s2d || !pad_ok(pad)) return SESSD_ERR_PARAM;
+    bb->pad = *pad;
+    return SESSD_OK;
+}
+
 }  // extern "C"
 
 // ---- host-buffer pipeline ----------------------------------------------------------------------
@@ -806,7 +849,8 @@ int sessd_pipeline_create(const sessd_backbone* bb, int batch, int max_points, i
     pl->ws_bytes = ws_bytes;
     pl->start = nullptr;
     pl->dense_bytes = bb->has_s2d ? (size_t)batch * bb->s2d.feature_map_channel * bb->s2d.feature_map_size_z *
-                                        bb->s2d.feature_map_size_y * bb->s2d.feature_map_size_x *
+                                        (bb->s2d.feature_map_size_y + bb->pad.top + bb->pad.bottom) *
+                                        (bb->s2d.feature_map_size_x + bb->pad.left + bb->pad.right) *
                                         (bb->dtype == SESSD_F32 ? 4 : 2)
                                   : 0;
     pl->streams.assign(nstreams, nullptr);

@@ -91,6 +91,9 @@ inline int ilog2(uint32_t v) {
 //       `rank_stride` between consecutive slots so that the voxeliser's per-slot point lists
 //       (whose first element is that minimum) can serve as the rank array.
 // vals: row index of the key, -1 when the key has no row.
+// Output tables of strided layers pack key and rank into one 64-bit slot (key in the high word), so that
+// claiming a cell and lowering its rank is a single atomic; keys/rank then point into that array with
+// stride 2.
 struct Table {
     uint32_t* keys;
     uint32_t* rank;
@@ -98,6 +101,7 @@ struct Table {
     uint32_t cap;       // power of two
     int shift;          // 32 - log2(cap)
     int rank_stride;
+    int key_stride;     // 1 for separate key / rank arrays; 2 when a slot is one 64-bit word (key << 32 | rank)
 };
 
 // x-grouped coordinate table of one resolution level: frame b owns buckets [b*cap, (b+1)*cap), a
@@ -261,7 +265,11 @@ int launch_conv_umma(const ConvLaunch& c, cudaStream_t stream);
 
 // sparse2dense.cu
 int launch_sparse2dense(const void* feat, const int32_t* coors, const int32_t* voxel_num, int batch, int max_voxels,
-                        int C, int D, int H, int W, int dtype, void* dense, cudaStream_t stream);
+                        int C, int D, int H, int W, int top, int bottom, int left, int right, int dtype, void* dense,
+                        cudaStream_t stream);
+// [planes][H][W] -> [planes][top+H+bottom][left+W+right], zero border.
+int launch_zero_pad2d(const void* in, void* out, size_t planes, int H, int W, int top, int bottom, int left, int right,
+                      int dtype, cudaStream_t stream);
 
 // voxelize.cu
 struct VoxelWorkspace {

@@ -348,6 +348,42 @@ int Sparse2DensePlugin::getOutputDataType(int, const int32_t* inputTypes, int) c
 
 void Sparse2DensePlugin::serialize(void* buffer) const { std::memcpy(buffer, &p_, sizeof(p_)); }
 
+// ---------------------------------------------------------------- ZeroPad2dPlugin
+
+ZeroPad2dPlugin::ZeroPad2dPlugin(int top, int bottom, int left, int right) { p_ = sessd_pad2d_params{top, bottom, left, right}; }
+
+ZeroPad2dPlugin::ZeroPad2dPlugin(const void* data, size_t length) {
+    std::memset(&p_, 0, sizeof(p_));
+    if (data && length >= sizeof(p_)) std::memcpy(&p_, data, sizeof(p_));   // zeroPad2d.cu:111-118
+}
+
+PluginBase* ZeroPad2dPlugin::clone() const { return new ZeroPad2dPlugin(*this); }
+
+int ZeroPad2dPlugin::getOutputDimensions(int outputIndex, const TensorDesc* inputs, int nbInputs, TensorDesc* out) const {
+    if (!inputs || nbInputs < 1 || !out || outputIndex != 0) return -1;
+    *out = make_desc({inputs[0].d[0], inputs[0].d[1], inputs[0].d[2] + p_.top + p_.bottom,
+                      inputs[0].d[3] + p_.left + p_.right},
+                     inputs[0].dtype);   // zeroPad2d.cu:127-151
+    return 0;
+}
+
+bool ZeroPad2dPlugin::supportsFormatCombination(int pos, const TensorDesc* inOut, int, int) const {
+    if (pos == 0) return is_feature_type(inOut[0]);
+    if (pos == 1) return is_feature_type(inOut[1]) && inOut[1].dtype == inOut[0].dtype;
+    return false;
+}
+
+int ZeroPad2dPlugin::enqueue(const TensorDesc* inputDesc, const TensorDesc*, const void* const* inputs,
+                             void* const* outputs, void*, void* stream) {
+    if (!inputDesc) return SESSD_ERR_NULL;
+    return sessd_zero_pad2d_enqueue(&p_, inputDesc[0].d[0], inputDesc[0].d[1], inputDesc[0].d[2], inputDesc[0].d[3],
+                                    feature_dtype(inputDesc[0]), inputs, outputs, stream);
+}
+
+int ZeroPad2dPlugin::getOutputDataType(int, const int32_t* inputTypes, int) const { return inputTypes[0]; }
+
+void ZeroPad2dPlugin::serialize(void* buffer) const { std::memcpy(buffer, &p_, sizeof(p_)); }
+
 // ---------------------------------------------------------------- creators
 
 namespace {
@@ -459,6 +495,23 @@ public:
     }
 };
 
+class PadCreator : public PluginCreator {
+public:
+    const char* getPluginName() const override { return "ZeroPad2dPlugin"; }
+    const std::vector<std::string>& getFieldNames() const override {
+        static const std::vector<std::string> n = {"zero_padding_2d_size"};   // zeroPad2d.cu:315
+        return n;
+    }
+    PluginBase* createPlugin(const char*, const Field* f, int n) const override {
+        const Field* sz = find_field(f, n, "zero_padding_2d_size");
+        // a missing field leaves all four at zero in the reference (zeroPad2d.cu:341-356)
+        return new ZeroPad2dPlugin(int_at(sz, 0), int_at(sz, 1), int_at(sz, 2), int_at(sz, 3));   // top, bottom, left, right
+    }
+    PluginBase* deserializePlugin(const char*, const void* d, size_t len) const override {
+        return len >= sizeof(sessd_pad2d_params) ? new ZeroPad2dPlugin(d, len) : nullptr;
+    }
+};
+
 }  // namespace
 
 const PluginCreator* getPluginCreator(const char* name, const char* version) {
@@ -466,7 +519,8 @@ const PluginCreator* getPluginCreator(const char* name, const char* version) {
     static const SubmCreator subm;
     static const SparseCreator sparse;
     static const S2DCreator s2d;
-    static const PluginCreator* all[] = {&voxel, &subm, &sparse, &s2d};
+    static const PadCreator pad;
+    static const PluginCreator* all[] = {&voxel, &subm, &sparse, &s2d, &pad};
     if (!name || (version && std::strcmp(version, "1"))) return nullptr;
     for (const PluginCreator* c : all)
         if (!std::strcmp(c->getPluginName(), name)) return c;

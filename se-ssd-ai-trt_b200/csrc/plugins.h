@@ -1,4 +1,4 @@
-// Host-side mirror of the reference's four sparse front end plugins.
+// Host-side mirror of the reference's sparse front end plugins (the four of the front end plus ZeroPad2d).
 //
 // Same class names, creator field names, member-function names, tensor orders, return conventions and
 // serialised byte layouts as the reference's TensorRT plugins; the bodies call the C ABI of sessd.h
@@ -148,6 +148,29 @@ public:
 
 private:
     sessd_s2d_params p_;
+};
+
+// zeroPad2d.h:18-87. Input {map [B, C, H, W]}; output {map [B, C, top+H+bottom, left+W+right]}.
+class ZeroPad2dPlugin : public PluginBase {
+public:
+    ZeroPad2dPlugin(int zero_padding_2d_top, int zero_padding_2d_bottom, int zero_padding_2d_left,
+                    int zero_padding_2d_right);
+    ZeroPad2dPlugin(const void* data, size_t length);
+    PluginBase* clone() const override;
+    int getOutputDimensions(int outputIndex, const TensorDesc* inputs, int nbInputs, TensorDesc* out) const override;
+    bool supportsFormatCombination(int pos, const TensorDesc* inOut, int nbInputs, int nbOutputs) const override;
+    void configurePlugin(const TensorDesc*, int, const TensorDesc*, int) override {}
+    size_t getWorkspaceSize(const TensorDesc*, int, const TensorDesc*, int) const override { return 0; }
+    int enqueue(const TensorDesc* inputDesc, const TensorDesc* outputDesc, const void* const* inputs,
+                void* const* outputs, void* workspace, void* stream) override;
+    int getOutputDataType(int index, const int32_t* inputTypes, int nbInputs) const override;
+    const char* getPluginType() const override { return "ZeroPad2dPlugin"; }
+    int getNbOutputs() const override { return 1; }
+    size_t getSerializationSize() const override { return sizeof(sessd_pad2d_params); }
+    void serialize(void* buffer) const override;
+
+private:
+    sessd_pad2d_params p_;
 };
 
 // IPluginCreator mirror: field names as the reference advertises them (e.g. submConv3dlayer.cu:737-748).

@@ -107,11 +107,27 @@ spconv_candidates_kernel(const int4* __restrict__ in_coors, const int32_t* __res
             const int oz = hi[0] - cz * g.dil, oy = hi[1] - cy * g.dil, ox = hi[2] - cx * g.dil;
             if (oz >= 0 && oz < g.out_shape[0] && oy >= 0 && oy < g.out_shape[1] && ox >= 0 && ox < g.out_shape[2]) {
                 const uint32_t key = ((uint32_t)oz * g.out_shape[1] + oy) * g.out_shape[2] + ox;
-                slot = table_insert(out_table.keys + (size_t)b * out_table.cap, out_table.cap, out_table.shift, key);
-                if (slot < 0)
-                    atomicOr(status, SESSD_STATUS_HASH_FULL);
-                else
-                    atomicMin(&out_table.rank[(size_t)b * out_table.cap + slot], (uint32_t)t);
+                // One 64-bit slot per cell: key in the high word, smallest entry index (rank) in the low word.
+                // A free slot is all ones, so both claiming a cell and lowering its rank are one atomic.
+                unsigned long long* slots =
+                    reinterpret_cast<unsigned long long*>(out_table.rank) + (size_t)b * out_table.cap;
+                const unsigned long long mine = ((unsigned long long)key << 32) | (uint32_t)t;
+                uint32_t h = hash_slot(key, out_table.shift);
+                for (uint32_t probe = 0; probe < out_table.cap; ++probe) {
+                    unsigned long long cur = slots[h];
+                    if (cur == ~0ull) cur = atomicCAS(&slots[h], ~0ull, mine);
+                    if (cur == ~0ull) {
+                        slot = (int)h;   // claimed with our rank
+                        break;
+                    }
+                    if ((uint32_t)(cur >> 32) == key) {
+                        if ((uint32_t)cur > (uint32_t)t) atomicMin(&slots[h], mine);
+                        slot = (int)h;
+                        break;
+                    }
+                    h = (h + 1) & (out_table.cap - 1);
+                }
+                if (slot < 0) atomicOr(status, SESSD_STATUS_HASH_FULL);
             }
         }
         slot_of[(size_t)b * per_frame + t] = slot;
@@ -135,7 +151,7 @@ struct OutputEmit {
             return;
         }
         t.vals[gslot] = id;
-        const uint32_t key = t.keys[gslot];
+        const uint32_t key = t.keys[gslot * t.key_stride];
         const int plane = Yo * Xo;
         const int z = key / plane, rem = key - z * plane;
         const int y = rem / Xo, x = rem - y * Xo;

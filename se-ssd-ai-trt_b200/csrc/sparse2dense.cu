@@ -14,7 +14,8 @@ namespace {
 template <typename T>
 __global__ void __launch_bounds__(kThreads)
 sparse2dense_kernel(const T* __restrict__ feat, const int4* __restrict__ coors, const int32_t* __restrict__ voxel_num,
-                    int batch, int max_voxels, int C, int D, int H, int W, T* __restrict__ dense) {
+                    int batch, int max_voxels, int C, int D, int H, int W, int Hp, int Wp, int top, int left,
+                    T* __restrict__ dense) {
     const int64_t per_frame = (int64_t)max_voxels * C;
     const int chunks = (int)((per_frame + kThreads - 1) / kThreads);
     const int items = batch * chunks;
@@ -27,17 +28,55 @@ sparse2dense_kernel(const T* __restrict__ feat, const int4* __restrict__ coors, 
         const int i = (int)(t / C), c = (int)(t - (int64_t)i * C);
         const int4 c4 = __ldg(&coors[(size_t)b * max_voxels + i]);  // (b, z, y, x)
         if (c4.y < 0 || c4.y >= D || c4.z < 0 || c4.z >= H || c4.w < 0 || c4.w >= W) continue;
-        // dense[b][c*D + z][y][x] (sparse2Dense.cu:201-206)
-        dense[(((size_t)b * C * D + (size_t)c * D + c4.y) * H + c4.z) * W + c4.w] = feat[(size_t)b * per_frame + t];
+        // dense[b][c*D + z][y][x] (sparse2Dense.cu:201-206), shifted by (top, left) inside a plane of
+        // Hp x Wp when the zero padding of ZeroPad2dPlugin (zeroPad2d.cu:192-198) is folded in
+        dense[(((size_t)b * C * D + (size_t)c * D + c4.y) * Hp + c4.z + top) * Wp + c4.w + left] =
+            feat[(size_t)b * per_frame + t];
+    }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(kThreads)
+zero_pad2d_kernel(const T* __restrict__ in, T* __restrict__ out, size_t planes, int H, int W, int Hp, int Wp, int top,
+                  int left) {
+    const size_t total = planes * H * W, stride = (size_t)gridDim.x * blockDim.x;
+    for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < total; i += stride) {
+        const size_t plane = i / ((size_t)H * W);
+        const int rem = (int)(i - plane * H * W);
+        const int y = rem / W, x = rem - y * W;
+        out[(plane * Hp + y + top) * Wp + x + left] = in[i];   // zeroPad2d.cu:192-198
     }
 }
 
 }  // namespace
 
-int launch_sparse2dense(const void* feat, const int32_t* coors, const int32_t* voxel_num, int batch, int max_voxels,
-                        int C, int D, int H, int W, int dtype, void* dense, cudaStream_t stream) {
+int launch_zero_pad2d(const void* in, void* out, size_t planes, int H, int W, int top, int bottom, int left, int right,
+                      int dtype, cudaStream_t stream) {
+    const int Hp = H + top + bottom, Wp = W + left + right;
     const size_t esize = dtype == SESSD_F32 ? 4 : 2;
-    const size_t bytes = (size_t)batch * C * D * H * W * esize;
+    const size_t bytes = planes * Hp * Wp * esize;
+    if (bytes % 16 != 0) {
+        SESSD_CUDA(cudaMemsetAsync(out, 0, bytes, stream));
+    } else {
+        int rc = launch_fill_zero(out, bytes, stream);
+        if (rc) return rc;
+    }
+    if (dtype == SESSD_F32) {
+        SESSD_LAUNCH(zero_pad2d_kernel<float>, persistent_grid(8), kThreads, 0, stream, static_cast<const float*>(in),
+                     static_cast<float*>(out), planes, H, W, Hp, Wp, top, left);
+    } else {
+        SESSD_LAUNCH(zero_pad2d_kernel<__half>, persistent_grid(8), kThreads, 0, stream, static_cast<const __half*>(in),
+                     static_cast<__half*>(out), planes, H, W, Hp, Wp, top, left);
+    }
+    return SESSD_OK;
+}
+
+int launch_sparse2dense(const void* feat, const int32_t* coors, const int32_t* voxel_num, int batch, int max_voxels,
+                        int C, int D, int H, int W, int top, int bottom, int left, int right, int dtype, void* dense,
+                        cudaStream_t stream) {
+    const size_t esize = dtype == SESSD_F32 ? 4 : 2;
+    const int Hp = H + top + bottom, Wp = W + left + right;
+    const size_t bytes = (size_t)batch * C * D * Hp * Wp * esize;
     if (bytes % 16 != 0) {
         SESSD_CUDA(cudaMemsetAsync(dense, 0, bytes, stream));
     } else {
@@ -47,11 +86,11 @@ int launch_sparse2dense(const void* feat, const int32_t* coors, const int32_t* v
     if (dtype == SESSD_F32) {
         SESSD_LAUNCH(sparse2dense_kernel<float>, persistent_grid(8), kThreads, 0, stream,
                      static_cast<const float*>(feat), reinterpret_cast<const int4*>(coors), voxel_num, batch,
-                     max_voxels, C, D, H, W, static_cast<float*>(dense));
+                     max_voxels, C, D, H, W, Hp, Wp, top, left, static_cast<float*>(dense));
     } else {
         SESSD_LAUNCH(sparse2dense_kernel<__half>, persistent_grid(8), kThreads, 0, stream,
                      static_cast<const __half*>(feat), reinterpret_cast<const int4*>(coors), voxel_num, batch,
-                     max_voxels, C, D, H, W, static_cast<__half*>(dense));
+                     max_voxels, C, D, H, W, Hp, Wp, top, left, static_cast<__half*>(dense));
     }
     return SESSD_OK;
 }

@@ -224,6 +224,7 @@ void voxel_workspace_layout(Bump& bump, const sessd_voxel_params* p, int batch, 
     w->table.cap = cap;
     w->table.shift = 32 - ilog2(cap);
     w->table.rank_stride = p->max_points_per_voxel;
+    w->table.key_stride = 1;
     w->pt_slot = bump.take<int32_t>((size_t)batch * max_points);
     w->chunk_counts = bump.take<int32_t>((size_t)batch * w->chunks);
     w->num_points = bump.take<int32_t>((size_t)batch * p->max_voxels);

@@ -44,7 +44,8 @@ def test_creators_advertise_the_reference_field_names(pkg):
             "padding", "dilation", "out_padding", "weights"]
     assert P.field_names("SubmConv3dLayerPlugin") == conv and P.field_names("SparseConv3dLayerPlugin") == conv
     assert P.field_names("Sparse2DensePlugin") == ["feature_map_size", "feature_map_channel"]
-    assert P.field_names("ZeroPad2dPlugin") is None
+    assert P.field_names("ZeroPad2dPlugin") == ["zero_padding_2d_size"]
+    assert P.field_names("GenerateAnchorDecodePlugin") is None
     lib = pkg.lib()
     for n in P.PLUGIN_EXPORTS:
         assert hasattr(lib, n)
@@ -113,6 +114,83 @@ def test_sparse2dense_blob_and_dims(pkg):
     assert d.output_dims(0, [feat]).dims() == (1, 128, 200, 176)
     assert d.workspace_size([feat], []) == 0
     assert P.Plugin.deserialize("Sparse2DensePlugin", d.serialize()).type() == "Sparse2DensePlugin"
+
+
+def test_zero_pad2d_blob_and_dims(pkg):
+    P = pkg.plugins
+    z = P.Plugin.create("ZeroPad2dPlugin", {"zero_padding_2d_size": np.array([1, 1, 1, 1], np.int32)})
+    assert z.serialize() == struct.pack("<4i", 1, 1, 1, 1)          # zeroPad2d.cu:286-289
+    m = P.TensorDesc.of((1, 128, 200, 176), P.DT_FLOAT)
+    assert z.output_dims(0, [m]).dims() == (1, 128, 202, 178) and z.nb_outputs() == 1
+    assert z.workspace_size([m], []) == 0
+    assert P.Plugin.deserialize("ZeroPad2dPlugin", struct.pack("<4i", 2, 0, 1, 3)).output_dims(0, [m]).dims() == (1, 128, 202, 180)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dt", [0, 1])
+def test_zero_pad2d_plugin_and_fused_padded_scatter(gpu, oracle, dt):
+    """ZeroPad2dPlugin on its own, and Sparse2Dense + ZeroPad2d fused into one pass, against the oracle."""
+    import torch
+
+    P = gpu.plugins
+    rs = np.random.RandomState(8)
+    tdt = torch.float32 if dt == 0 else torch.float16
+    B, Cc, H, W = 2, 6, 9, 11
+    x = rs.randn(B, Cc, H, W).astype(np.float32)
+    if dt:
+        x = x.astype(np.float16).astype(np.float32)
+    for pad in [(1, 1, 1, 1), (0, 2, 3, 0)]:
+        z = P.Plugin.create("ZeroPad2dPlugin", {"zero_padding_2d_size": np.array(pad, np.int32)})
+        d_in = P.TensorDesc.of((B, Cc, H, W), P.DT_FLOAT if dt == 0 else P.DT_HALF)
+        d_out = z.output_dims(0, [d_in])
+        tin = torch.from_numpy(x).cuda().to(tdt)
+        tout = torch.full(d_out.dims(), 5, dtype=tdt, device="cuda")
+        assert z.enqueue([d_in], [d_out], [tin], [tout], None, torch.cuda.current_stream().cuda_stream) == 0
+        torch.cuda.synchronize()
+        np.testing.assert_array_equal(tout.float().cpu().numpy(), oracle.zero_pad2d(x, *pad))
+    # fused: rows -> padded BEV map directly
+    V, C2, D, H2, W2 = 256, 8, 2, 10, 12
+    feat = np.zeros((B, V, C2), np.float32)
+    coors = np.zeros((B, V, 4), np.int32)
+    num = np.array([100, 37], np.int32)
+    for b in range(B):
+        cells = rs.permutation(D * H2 * W2)[:num[b]]
+        coors[b, :num[b], 0] = b
+        coors[b, :num[b], 1], coors[b, :num[b], 2], coors[b, :num[b], 3] = cells // (H2 * W2), (cells // W2) % H2, cells % W2
+        feat[b, :num[b]] = rs.randn(num[b], C2)
+    if dt:
+        feat = feat.astype(np.float16).astype(np.float32)
+    pad = gpu.Pad2DParams(1, 1, 1, 1)
+    dense = gpu.sparse2dense(torch.from_numpy(feat).cuda().to(tdt), torch.from_numpy(coors).cuda(),
+                             torch.from_numpy(num).cuda(), gpu.S2DParams(W2, H2, D, C2), dt, pad=pad)
+    want = np.stack([oracle.sparse2dense(feat[b, :num[b]], np.concatenate([np.zeros((num[b], 1), np.int32), coors[b, :num[b], 1:]], 1),
+                                         num[b], C2, D, H2, W2)[0] for b in range(B)])
+    np.testing.assert_array_equal(dense.float().cpu().numpy(), oracle.zero_pad2d(want, 1, 1, 1, 1))
+
+
+@pytest.mark.gpu
+def test_backbone_with_folded_zero_padding(gpu, oracle):
+    """sessd_backbone_set_padding: the fused front end writes the padded map the reference's ZeroPad2d layer produces."""
+    import torch
+
+    import make_golden_inputs as mk
+
+    case = mk.small_case(gpu)
+    pts = torch.from_numpy(case["points"][None]).cuda()
+    sizes = torch.tensor([pts.shape[1]], dtype=torch.int32, device="cuda")
+    outs = []
+    for padded in (False, True):
+        bb = gpu.Backbone(case["max_voxels"], case["weights"], case["scale"], case["shift"], dtype=gpu.F16,
+                          layers=case["layers"], point_range=case["range"], voxel_size=case["voxel"])
+        if padded:
+            bb.set_padding(1, 1, 1, 1)
+        dense, ws = bb.run(pts, sizes)
+        torch.cuda.synchronize()
+        assert gpu.read_status(ws) == 0
+        outs.append(dense.float().cpu().numpy())
+        bb.close()
+    assert outs[1].shape == (1, 128, 12, 10)
+    np.testing.assert_array_equal(outs[1], oracle.zero_pad2d(outs[0], 1, 1, 1, 1))
 
 
 @pytest.mark.gpu
