@@ -195,3 +195,18 @@ def test_bad_coordinate_is_reported_not_dereferenced(gpu):
     res, _ = _run_layer(gpu, _layer(gpu, True, 16, 16, (3, 3, 3), (1, 1, 1), (1, 1, 1), shape), [(c, f)],
                         rs.randn(27, 16, 16).astype(np.float32))
     assert res[0]["status"] & gpu.STATUS_BAD_COORD
+
+
+@pytest.mark.parametrize("cin,cout", [(32, 32), (64, 64)])
+def test_more_row_groups_than_resident_blocks_fp16(gpu, oracle, cin, cout):
+    """4 frames x 45,000 rows: 352 groups of 512 rows, more than a persistent grid holds at once, so blocks
+    walk through several groups and their staging rings wrap many times."""
+    rs = np.random.RandomState(77 + cin)
+    shape = (10, 200, 176)
+    frames = []
+    for n in (45000, 44000, 45000, 30001):
+        c = _random_coords(rs, n, shape)
+        frames.append((c, rs.randn(len(c), cin).astype(np.float32)))
+    W = (rs.randn(27, cin, cout) / np.sqrt(5 * cin)).astype(np.float32)
+    layer = _layer(gpu, True, cin, cout, (3, 3, 3), (1, 1, 1), (1, 1, 1), shape)
+    _check_layer(gpu, oracle, layer, frames, W, dtype=gpu.F16, maxV=45056)
