@@ -43,7 +43,7 @@ def load_package():
 
 WORKLOADS = {
     # name: (points per frame, object clusters, frames per GPU per step, max_voxels, frames per launch group)
-    "sweep": dict(points=120000, boxes=40, frames=512, max_voxels=200000, batch=16,
+    "sweep": dict(points=120000, boxes=40, frames=512, max_voxels=200000, batch=8,
                   desc="throughput sweep: 512 frames x 120,000 points per GPU"),
     "single": dict(points=20000, boxes=15, frames=2048, max_voxels=60000, batch=32,
                    desc="20,000-point frames (single-frame backbone case), 2048 per GPU"),
@@ -194,7 +194,7 @@ def main():
     ap.add_argument("--workload", default="sweep", choices=sorted(WORKLOADS))
     ap.add_argument("--frames", type=int, default=0, help="frames per GPU per step (default: the workload's)")
     ap.add_argument("--batch", type=int, default=0, help="frames per launch group")
-    ap.add_argument("--streams", type=int, default=2)
+    ap.add_argument("--streams", type=int, default=4, help="launch groups in flight per GPU")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 0)
