@@ -14,7 +14,7 @@
 // rows (and, for the last layer, scatters them into the dense BEV map).
 //
 // Warp roles (256 threads, two CTAs per SM): warps 0-3 gather A tiles with 16-byte cp.async and later run
-// the epilogue; warps 4 and 7 each issue the MMAs of two of the four row tiles from one thread (warp 4 also
+// the epilogue; warps 4 and 7 each issue the MMAs of every other row tile from one thread (warp 4 also
 // owns the tensor memory allocation); warp 5 streams the weight blocks; warp 6 copies the neighbour
 // indices of upcoming stages into a small ring ahead of the gathers. Stages hand over through mbarriers; every wait is bounded by a clock limit, after which the
 // CTA raises SESSD_STATUS_TIMEOUT, stops issuing work, frees its tensor memory and returns.
@@ -46,7 +46,7 @@ struct RingCfg {
 constexpr int ROW_BYTES = 128;               // 64 halves per A/B row
 constexpr int A_BYTES = TILE_M * ROW_BYTES;  // 16 KB
 constexpr int UMMA_THREADS = 256;
-constexpr int MMA_WARPS = 2;                 // MMA issuer warps (4 and 7); each owns TILES / MMA_WARPS row tiles
+constexpr int MMA_WARPS = 2;                 // MMA issuer warps (4 and 7); one takes the even row tiles, the other the odd ones
 constexpr int KVOL_MAX = 27;
 constexpr long long WAIT_LIMIT_CYCLES = 200000000LL;   // about a tenth of a second; real waits are microseconds
 
@@ -249,23 +249,42 @@ conv_umma_kernel(const __half* __restrict__ in, __half* __restrict__ out, const 
     volatile int* abort_flag = &ctl->abort_flag;
 
     const int tiles_per_frame = (max_voxels + TILE_M - 1) / TILE_M;
-    const int supers_per_frame = (tiles_per_frame + TILES - 1) / TILES;
-    const int items = batch * supers_per_frame;
     uint32_t a_it = 0, b_it = 0, st_it = 0;   // ring positions; every role advances them identically
 
-    for (int item = blockIdx.x; item < items; item += gridDim.x) {
-        const int b = item / supers_per_frame;
-        const int tile0 = (item - b * supers_per_frame) * TILES;
+    // Balanced split: the occupied 128-row tiles of all frames, laid end to end, are cut into gridDim.x
+    // equal contiguous ranges (row counts are read from the device, so no host round trip); a CTA walks
+    // its range in groups of up to TILES tiles of one frame.
+    auto frame_rows = [&](int f) {
+        const int v = __ldg(out_num + f);
+        return v > max_voxels ? max_voxels : (v < 0 ? 0 : v);
+    };
+    long long total_tiles = 0;
+    for (int f = 0; f < batch; ++f) total_tiles += (frame_rows(f) + TILE_M - 1) / TILE_M;
+    const int range_lo = (int)(total_tiles * blockIdx.x / gridDim.x);
+    const int range_hi = (int)(total_tiles * (blockIdx.x + 1) / gridDim.x);
+    int b = 0, frame_first = 0;                 // frame of the cursor and the global index of its first tile
+    int n = batch > 0 ? frame_rows(0) : 0;
+    int frame_tiles = (n + TILE_M - 1) / TILE_M;
+
+    for (int cur = range_lo; cur < range_hi;) {
+        while (cur >= frame_first + frame_tiles) {
+            frame_first += frame_tiles;
+            ++b;
+            n = frame_rows(b);
+            frame_tiles = (n + TILE_M - 1) / TILE_M;
+        }
+        const int tile0 = cur - frame_first;
+        int cnt = range_hi - cur;
+        cnt = cnt > TILES ? TILES : cnt;
+        cnt = cnt > frame_tiles - tile0 ? frame_tiles - tile0 : cnt;
+        cur += cnt;
         const int row0 = tile0 * TILE_M;
-        int n = out_num[b];
-        n = n > max_voxels ? max_voxels : n;
-        if (row0 >= n) continue;
         if (*abort_flag) break;
         uint32_t m[TILES];
         uint32_t any = 0;
 #pragma unroll
         for (int t = 0; t < TILES; ++t) {
-            m[t] = (row0 + t * TILE_M < n) ? __ldg(tile_mask + (size_t)b * tiles_per_frame + tile0 + t) : 0u;
+            m[t] = t < cnt ? __ldg(tile_mask + (size_t)b * tiles_per_frame + tile0 + t) : 0u;
             any |= m[t];
         }
         int n_a = 0, n_b = 0;   // A and B stages this super-tile consumes
@@ -349,7 +368,7 @@ conv_umma_kernel(const __half* __restrict__ in, __half* __restrict__ out, const 
             long long te1 = clock64();
 #endif
 #pragma unroll 1
-            for (int t2 = 0; t2 < TILES; ++t2) {
+            for (int t2 = 0; t2 < cnt; ++t2) {
                 const int row = row0 + t2 * TILE_M + tid;
                 float acc[COUT];
                 if (any && got && m[t2]) {
@@ -409,24 +428,23 @@ conv_umma_kernel(const __half* __restrict__ in, __half* __restrict__ out, const 
         } else if (warp == 4 || warp == 7) {
             // ---------------- MMA issuers ----------------
             // Issuing a tcgen05.mma or commit costs the issuing thread on the order of a hundred cycles, so
-            // two threads issue: warp 4 owns row tiles 0-1, warp 7 tiles 2-3 (disjoint accumulators).
+            // two threads issue: warp 4 owns the even row tiles, warp 7 the odd ones (disjoint accumulators;
+            // the split stays even when a group holds fewer than TILES tiles).
             if (lane == 0 && any) {
-                constexpr int TPW = TILES / MMA_WARPS;
-                const int t_lo = warp == 4 ? 0 : TPW, t_hi = t_lo + TPW;
+                const int parity = warp == 4 ? 0 : 1;
                 uint32_t my_a = a_it, my_b = b_it;
                 bool ok = true;
                 if (st_it > 0) ok = mbar_wait(smem_u32(&ctl->acc_empty), (st_it - 1u) & 1u, abort_flag);
                 if (ok) tc_fence_after();
                 uint32_t started = 0;
                 for (int g = 0; g < nstages && ok; ++g) {
-                    int act = 0, before = 0;   // active tiles of this stage group: in total / before mine
+                    int act = 0;   // active tiles of this stage group
                     bool mine = false;
 #pragma unroll
                     for (int t = 0; t < TILES; ++t) {
                         const int a1 = stage_active<KG>(m[t], g) ? 1 : 0;
                         act += a1;
-                        before += t < t_lo ? a1 : 0;
-                        mine |= (a1 != 0) && t >= t_lo && t < t_hi;
+                        mine |= (a1 != 0) && (t & 1) == parity;
                     }
                     if (!act) continue;
                     const uint32_t sb = my_b % B_STAGES;
@@ -436,9 +454,13 @@ conv_umma_kernel(const __half* __restrict__ in, __half* __restrict__ out, const 
                     if (!ok) break;
                     if (mine) {
                         const uint32_t b_addr = smem_u32(sB + sb * B_BYTES);
-                        uint32_t pos = my_a + before;
-                        for (int t = t_lo; t < t_hi && ok; ++t) {
+                        uint32_t pos = my_a;
+                        for (int t = 0; t < TILES && ok; ++t) {
                             if (!stage_active<KG>(m[t], g)) continue;
+                            if ((t & 1) != parity) {   // the other issuer's stage
+                                ++pos;
+                                continue;
+                            }
                             const uint32_t sa = pos % A_STAGES;
                             ok = mbar_wait(smem_u32(&ctl->a_full[sa]), (pos / A_STAGES) & 1u, abort_flag);
                             if (!ok) break;
