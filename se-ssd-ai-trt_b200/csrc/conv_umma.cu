@@ -188,7 +188,9 @@ __device__ __forceinline__ bool next_item(const uint32_t (&m)[TILES], int nstage
 }
 
 template <int CIN, int COUT>
-__global__ void __launch_bounds__(UMMA_THREADS, 2)
+// Register budget of three CTAs per SM although shared memory admits two: the rest of the register file
+// is what lets blocks of other kernels (other streams) run beside them.
+__global__ void __launch_bounds__(UMMA_THREADS, 3)
 conv_umma_kernel(const __half* __restrict__ in, __half* __restrict__ out, const int32_t* __restrict__ nbr,
                  const uint32_t* __restrict__ tile_mask, const int32_t* __restrict__ out_num,
                  const uint8_t* __restrict__ wtiles, const float* __restrict__ scale, const float* __restrict__ shift,
@@ -247,6 +249,10 @@ conv_umma_kernel(const __half* __restrict__ in, __half* __restrict__ out, const 
     tc_fence_after();
     const uint32_t tmem = ctl->tmem_base;
     volatile int* abort_flag = &ctl->abort_flag;
+#ifdef SESSD_UMMA_TIMING
+    const long long t_cta0 = clock64();
+    unsigned long long tacc[16] = {};   // cycle counters kept in registers, written once at the end
+#endif
 
     const int tiles_per_frame = (max_voxels + TILE_M - 1) / TILE_M;
     uint32_t a_it = 0, b_it = 0, st_it = 0;   // ring positions; every role advances them identically
@@ -343,13 +349,12 @@ conv_umma_kernel(const __half* __restrict__ in, __half* __restrict__ out, const 
                 cp_async_arrive_noinc(smem_u32(&ctl->a_full[s]));   // publishes the stage when the copies land
                 ++my_a;
 #ifdef SESSD_UMMA_TIMING
-                if (tid == 0 && blockIdx.x < 4) {
+                if (tid == 0 && blockIdx.x < 2) {
                     long long tq5 = clock64();
-                    unsigned long long* dbg = reinterpret_cast<unsigned long long*>(status) + 96 + blockIdx.x * 8;
-                    dbg[0] += (unsigned long long)(tq1 - tq0);  // wait index block
-                    dbg[1] += (unsigned long long)(tq3 - tq2);  // wait free A stage
-                    dbg[3] += (unsigned long long)(tq5 - tq0);  // whole iteration
-                    dbg[4] += 1;
+                    tacc[0] += (unsigned long long)(tq1 - tq0);  // wait index block
+                    tacc[1] += (unsigned long long)(tq3 - tq2);  // wait free A stage
+                    tacc[3] += (unsigned long long)(tq5 - tq0);  // whole iteration
+                    tacc[4] += 1;
                 }
 #endif
             }
@@ -367,49 +372,61 @@ conv_umma_kernel(const __half* __restrict__ in, __half* __restrict__ out, const 
 #ifdef SESSD_UMMA_TIMING
             long long te1 = clock64();
 #endif
+            // Column blocks of CB channels keep the register footprint small enough for other kernels'
+            // blocks to share the SM with the two resident CTAs of this one.
+            constexpr int CB = COUT < 32 ? COUT : 32;
 #pragma unroll 1
             for (int t2 = 0; t2 < cnt; ++t2) {
                 const int row = row0 + t2 * TILE_M + tid;
-                float acc[COUT];
-                if (any && got && m[t2]) {
-#pragma unroll
-                    for (int c0 = 0; c0 < COUT; c0 += 16) {
-                        uint32_t r16[16];
-                        tmem_ld16(tmem + ((uint32_t)(warp * 32) << 16) + t2 * COUT + c0, r16);
-#pragma unroll
-                        for (int j = 0; j < 16; ++j) acc[c0 + j] = __uint_as_float(r16[j]);
-                    }
-                    tmem_ld_wait();
-                } else {
-#pragma unroll
-                    for (int j = 0; j < COUT; ++j) acc[j] = 0.f;
+                const bool have = any && got && m[t2];
+                const bool store = got && row < n;
+                __half* dst = out + ((size_t)b * max_voxels + row) * COUT;
+                __half* d = nullptr;
+                if (dense && store) {
+                    // fused BEV scatter (sparse2Dense.cu:201-206): channel c*D + z, pixel (y, x)
+                    const int4 c4 = __ldg(&out_coors[(size_t)b * max_voxels + row]);
+                    d = dense + (size_t)b * COUT * D * H * W + ((size_t)c4.y * H + c4.z) * W + c4.w;
                 }
-                if (got && row < n) {
-                    __half* dst = out + ((size_t)b * max_voxels + row) * COUT;
+#pragma unroll 1
+                for (int cb = 0; cb < COUT; cb += CB) {
+                    float acc[CB];
+                    if (have) {
 #pragma unroll
-                    for (int c0 = 0; c0 < COUT; c0 += 8) {
+                        for (int c0 = 0; c0 < CB; c0 += 16) {
+                            uint32_t r16[16];
+                            tmem_ld16(tmem + ((uint32_t)(warp * 32) << 16) + t2 * COUT + cb + c0, r16);
+#pragma unroll
+                            for (int j = 0; j < 16; ++j) acc[c0 + j] = __uint_as_float(r16[j]);
+                        }
+                        tmem_ld_wait();
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < CB; ++j) acc[j] = 0.f;
+                    }
+                    if (!store) continue;
+#pragma unroll
+                    for (int c0 = 0; c0 < CB; c0 += 8) {
                         uint4 pk;
                         __half2* h = reinterpret_cast<__half2*>(&pk);
 #pragma unroll
                         for (int j = 0; j < 4; ++j) {
-                            float v0 = fmaf(acc[c0 + 2 * j], s_scale[c0 + 2 * j], s_shift[c0 + 2 * j]);
-                            float v1 = fmaf(acc[c0 + 2 * j + 1], s_scale[c0 + 2 * j + 1], s_shift[c0 + 2 * j + 1]);
+                            const int ch = cb + c0 + 2 * j;
+                            float v0 = fmaf(acc[c0 + 2 * j], s_scale[ch], s_shift[ch]);
+                            float v1 = fmaf(acc[c0 + 2 * j + 1], s_scale[ch + 1], s_shift[ch + 1]);
                             if (relu) {
                                 v0 = v0 > 0.f ? v0 : 0.f;
                                 v1 = v1 > 0.f ? v1 : 0.f;
                             }
-                            acc[c0 + 2 * j] = v0;
-                            acc[c0 + 2 * j + 1] = v1;
                             h[j] = __floats2half2_rn(v0, v1);
                         }
-                        *reinterpret_cast<uint4*>(dst + c0) = pk;
-                    }
-                    if (dense) {
-                        // fused BEV scatter (sparse2Dense.cu:201-206): channel c*D + z, pixel (y, x)
-                        const int4 c4 = __ldg(&out_coors[(size_t)b * max_voxels + row]);
-                        __half* d = dense + (size_t)b * COUT * D * H * W + ((size_t)c4.y * H + c4.z) * W + c4.w;
+                        *reinterpret_cast<uint4*>(dst + cb + c0) = pk;
+                        if (d) {
 #pragma unroll
-                        for (int j = 0; j < COUT; ++j) d[(size_t)j * D * H * W] = __float2half_rn(acc[j]);
+                            for (int j = 0; j < 4; ++j) {
+                                d[(size_t)(cb + c0 + 2 * j) * D * H * W] = __low2half(h[j]);
+                                d[(size_t)(cb + c0 + 2 * j + 1) * D * H * W] = __high2half(h[j]);
+                            }
+                        }
                     }
                 }
             }
@@ -418,11 +435,10 @@ conv_umma_kernel(const __half* __restrict__ in, __half* __restrict__ out, const 
                 mbar_arrive(smem_u32(&ctl->acc_empty));   // the accumulators may be overwritten
             }
 #ifdef SESSD_UMMA_TIMING
-            if (tid == 0 && blockIdx.x < 4) {
-                unsigned long long* dbg = reinterpret_cast<unsigned long long*>(status) + 96 + blockIdx.x * 8;
-                dbg[5] += (unsigned long long)(te1 - te0);          // wait for the accumulators
-                dbg[6] += (unsigned long long)(clock64() - te1);    // epilogue proper
-                dbg[7] += 1;
+            if (tid == 0 && blockIdx.x < 2) {
+                tacc[5] += (unsigned long long)(te1 - te0);          // wait for the accumulators
+                tacc[6] += (unsigned long long)(clock64() - te1);    // epilogue proper
+                tacc[7] += 1;
             }
 #endif
         } else if (warp == 4 || warp == 7) {
@@ -450,7 +466,15 @@ conv_umma_kernel(const __half* __restrict__ in, __half* __restrict__ out, const 
                     const uint32_t sb = my_b % B_STAGES;
                     // Both issuers wait for the block, also one with nothing to do for this group: its
                     // release below must count for this use of the slot, not for an earlier one.
+#ifdef SESSD_UMMA_TIMING
+                    const long long tb0 = clock64();
+#endif
                     ok = mbar_wait(smem_u32(&ctl->b_full[sb]), (my_b / B_STAGES) & 1u, abort_flag);
+#ifdef SESSD_UMMA_TIMING
+                    if (warp == 4 && blockIdx.x < 2) {
+                        tacc[11] += (unsigned long long)(clock64() - tb0);
+                    }
+#endif
                     if (!ok) break;
                     if (mine) {
                         const uint32_t b_addr = smem_u32(sB + sb * B_BYTES);
@@ -462,8 +486,16 @@ conv_umma_kernel(const __half* __restrict__ in, __half* __restrict__ out, const 
                                 continue;
                             }
                             const uint32_t sa = pos % A_STAGES;
+#ifdef SESSD_UMMA_TIMING
+                            const long long tm0 = clock64();
+#endif
                             ok = mbar_wait(smem_u32(&ctl->a_full[sa]), (pos / A_STAGES) & 1u, abort_flag);
                             if (!ok) break;
+#ifdef SESSD_UMMA_TIMING
+                            if (warp == 4 && blockIdx.x < 2) {   // cycles this issuer waited for gathered rows
+                                tacc[2] += (unsigned long long)(clock64() - tm0);
+                            }
+#endif
                             fence_proxy_async();   // the gathered rows were written through the generic proxy
                             tc_fence_after();
                             const uint32_t a_addr = smem_u32(sA + sa * A_BYTES);
@@ -474,6 +506,12 @@ conv_umma_kernel(const __half* __restrict__ in, __half* __restrict__ out, const 
                             }
                             started |= 1u << t;
                             umma_commit(smem_u32(&ctl->a_empty[sa]));   // frees the A stage once these MMAs have read it
+#ifdef SESSD_UMMA_TIMING
+                            if (warp == 4 && blockIdx.x < 2) {
+                                tacc[10] += (unsigned long long)(clock64() - tm0);   // wait + issue + commit of one stage
+                                tacc[12] += 1;
+                            }
+#endif
                             ++pos;
                         }
                         if (ok) umma_commit(smem_u32(&ctl->b_empty[sb]));
@@ -548,6 +586,15 @@ conv_umma_kernel(const __half* __restrict__ in, __half* __restrict__ out, const 
 
     tc_fence_before();
     __syncthreads();
+#ifdef SESSD_UMMA_TIMING
+    if ((tid == 0 || tid == 128) && blockIdx.x < 2) {
+        unsigned long long* dbg = reinterpret_cast<unsigned long long*>(status) + 96 + blockIdx.x * 16;
+        tacc[tid == 0 ? 8 : 13] = (unsigned long long)(clock64() - t_cta0);
+#pragma unroll
+        for (int i = 0; i < 16; ++i)
+            if (tacc[i]) dbg[i] = tacc[i];
+    }
+#endif
     if (tid == 0 && *abort_flag) atomicOr(status, SESSD_STATUS_TIMEOUT);
     if (warp == 4) {
         tc_fence_after();
