@@ -72,12 +72,25 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
         : "memory");
     return ok != 0;
 }
+// Same, but the hardware may park the thread for up to `ns` nanoseconds while the phase is incomplete,
+// so a waiting warp does not take issue slots from the warps that feed the pipeline.
+__device__ __forceinline__ bool mbar_try_wait_parked(uint32_t bar, uint32_t parity, uint32_t ns) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity), "r"(ns)
+        : "memory");
+    return ok != 0;
+}
 // Bounded wait: false when the phase did not complete within the clock limit or the CTA is aborting.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
     if (mbar_try_wait(bar, parity)) return true;
     const long long t0 = clock64();
     for (;;) {
-        if (mbar_try_wait(bar, parity)) return true;
+        if (mbar_try_wait_parked(bar, parity, 2000u)) return true;
         if (*abort_flag) return false;
         if (clock64() - t0 > WAIT_LIMIT_CYCLES) {
             *abort_flag = 1;
@@ -174,23 +187,34 @@ __device__ __forceinline__ bool stage_active(uint32_t kmask, int g) {
     return ((kmask >> (g * KG)) & ((1u << KG) - 1u)) != 0u;
 }
 
-// Advances (g, t) to the next (stage, tile) pair with work, in the order stage-major, tile-minor.
+// Bit t set when row tile t has a neighbour under the offsets of stage g. The masks are only ever indexed
+// with compile-time constants, so they stay in registers (local memory would miss in the small L1 that
+// is left beside 200 KB of shared memory).
 template <int KG>
-__device__ __forceinline__ bool next_item(const uint32_t (&m)[TILES], int nstages, int& g, int& t) {
-    for (;;) {
-        if (++t == TILES) {
-            t = 0;
-            ++g;
-        }
-        if (g >= nstages) return false;
-        if (stage_active<KG>(m[t], g)) return true;
-    }
+__device__ __forceinline__ uint32_t active_tiles(const uint32_t (&m)[TILES], int g) {
+    uint32_t bits = 0;
+#pragma unroll
+    for (int t = 0; t < TILES; ++t) bits |= (stage_active<KG>(m[t], g) ? 1u : 0u) << t;
+    return bits;
 }
 
+// Advances to the next (stage g, tile t) pair with work, in the order stage-major, tile-minor; `rem` holds
+// the tiles of stage g not yet visited. Start with g = -1, rem = 0.
+template <int KG>
+__device__ __forceinline__ bool next_item(const uint32_t (&m)[TILES], int nstages, int& g, uint32_t& rem, int& t) {
+    while (rem == 0u) {
+        if (++g >= nstages) return false;
+        rem = active_tiles<KG>(m, g);
+    }
+    t = __ffs((int)rem) - 1;
+    rem &= rem - 1u;
+    return true;
+}
+
+// Register cap well below what two resident CTAs (the shared-memory limit) could take: the rest of the
+// register file is what lets blocks of other kernels (other streams) run beside them.
 template <int CIN, int COUT>
-// Register budget of three CTAs per SM although shared memory admits two: the rest of the register file
-// is what lets blocks of other kernels (other streams) run beside them.
-__global__ void __launch_bounds__(UMMA_THREADS, 3)
+__global__ void __maxnreg__(88)
 conv_umma_kernel(const __half* __restrict__ in, __half* __restrict__ out, const int32_t* __restrict__ nbr,
                  const uint32_t* __restrict__ tile_mask, const int32_t* __restrict__ out_num,
                  const uint8_t* __restrict__ wtiles, const float* __restrict__ scale, const float* __restrict__ shift,
@@ -285,6 +309,9 @@ conv_umma_kernel(const __half* __restrict__ in, __half* __restrict__ out, const 
         cnt = cnt > frame_tiles - tile0 ? frame_tiles - tile0 : cnt;
         cur += cnt;
         const int row0 = tile0 * TILE_M;
+#ifdef SESSD_UMMA_TIMING
+        const long long tg0 = clock64();
+#endif
         if (*abort_flag) break;
         uint32_t m[TILES];
         uint32_t any = 0;
@@ -309,9 +336,14 @@ conv_umma_kernel(const __half* __restrict__ in, __half* __restrict__ out, const 
             const int csub = (c % CPO) * 8;        // first channel of the chunk
             const __half* in_b = in + (size_t)b * max_voxels * CIN;
             uint32_t my_a = a_it;
+#ifdef SESSD_UMMA_TIMING
+            const long long tg1 = clock64();
+            if (tid == 0 && blockIdx.x < 2) tacc[9] += (unsigned long long)(tg1 - tg0);   // group set-up
+#endif
             bool ok = true;
-            int g = -1, t = TILES - 1;
-            while (ok && next_item<KG>(m, nstages, g, t)) {
+            int g = -1, t = 0;
+            uint32_t rem = 0;
+            while (ok && next_item<KG>(m, nstages, g, rem, t)) {
                 const uint32_t s = my_a % A_STAGES, si = my_a % IDX_STAGES;
                 // row indices of this stage, fetched ahead of time by the index warp
 #ifdef SESSD_UMMA_TIMING
@@ -359,6 +391,9 @@ conv_umma_kernel(const __half* __restrict__ in, __half* __restrict__ out, const 
 #endif
             }
 
+#ifdef SESSD_UMMA_TIMING
+            if (tid == 0 && blockIdx.x < 2) tacc[14] += (unsigned long long)(clock64() - tg1);   // whole gather loop of the group
+#endif
             // ---------------- epilogue ----------------
 #ifdef SESSD_UMMA_TIMING
             long long te0 = clock64();
@@ -378,7 +413,8 @@ conv_umma_kernel(const __half* __restrict__ in, __half* __restrict__ out, const 
 #pragma unroll 1
             for (int t2 = 0; t2 < cnt; ++t2) {
                 const int row = row0 + t2 * TILE_M + tid;
-                const bool have = any && got && m[t2];
+                const uint32_t m_t2 = t2 == 0 ? m[0] : (t2 == 1 ? m[1] : (t2 == 2 ? m[2] : m[3]));
+                const bool have = any && got && m_t2;
                 const bool store = got && row < n;
                 __half* dst = out + ((size_t)b * max_voxels + row) * COUT;
                 __half* d = nullptr;
@@ -454,14 +490,9 @@ conv_umma_kernel(const __half* __restrict__ in, __half* __restrict__ out, const 
                 if (ok) tc_fence_after();
                 uint32_t started = 0;
                 for (int g = 0; g < nstages && ok; ++g) {
-                    int act = 0;   // active tiles of this stage group
-                    bool mine = false;
-#pragma unroll
-                    for (int t = 0; t < TILES; ++t) {
-                        const int a1 = stage_active<KG>(m[t], g) ? 1 : 0;
-                        act += a1;
-                        mine |= (a1 != 0) && (t & 1) == parity;
-                    }
+                    const uint32_t bits = active_tiles<KG>(m, g);
+                    const int act = __popc(bits);   // active tiles of this stage group
+                    const bool mine = (bits & (parity ? 0xAAAAAAAAu : 0x55555555u)) != 0u;
                     if (!act) continue;
                     const uint32_t sb = my_b % B_STAGES;
                     // Both issuers wait for the block, also one with nothing to do for this group: its
@@ -480,7 +511,7 @@ conv_umma_kernel(const __half* __restrict__ in, __half* __restrict__ out, const 
                         const uint32_t b_addr = smem_u32(sB + sb * B_BYTES);
                         uint32_t pos = my_a;
                         for (int t = 0; t < TILES && ok; ++t) {
-                            if (!stage_active<KG>(m[t], g)) continue;
+                            if (!((bits >> t) & 1u)) continue;
                             if ((t & 1) != parity) {   // the other issuer's stage
                                 ++pos;
                                 continue;
@@ -535,8 +566,9 @@ conv_umma_kernel(const __half* __restrict__ in, __half* __restrict__ out, const 
             const int32_t* nbr_b = nbr + (size_t)b * kvol * max_voxels;
             uint32_t my_i = a_it;
             bool ok = true;
-            int g = -1, t = TILES - 1;
-            while (ok && next_item<KG>(m, nstages, g, t)) {
+            int g = -1, t = 0;
+            uint32_t rem = 0;
+            while (ok && next_item<KG>(m, nstages, g, rem, t)) {
                 const uint32_t si = my_i % IDX_STAGES;
                 ok = mbar_wait(smem_u32(&ctl->i_empty[si]), ((my_i / IDX_STAGES) & 1u) ^ 1u, abort_flag);
                 if (!ok) break;
