@@ -446,9 +446,12 @@ conv_umma_kernel(const __half* __restrict__ in, __half* __restrict__ out, const 
                         __half2* h = reinterpret_cast<__half2*>(&pk);
 #pragma unroll
                         for (int j = 0; j < 4; ++j) {
+                            // scale and shift of channels ch, ch+1 as two 8-byte shared-memory reads
                             const int ch = cb + c0 + 2 * j;
-                            float v0 = fmaf(acc[c0 + 2 * j], s_scale[ch], s_shift[ch]);
-                            float v1 = fmaf(acc[c0 + 2 * j + 1], s_scale[ch + 1], s_shift[ch + 1]);
+                            const float2 sc = *reinterpret_cast<const float2*>(&s_scale[ch]);
+                            const float2 sh = *reinterpret_cast<const float2*>(&s_shift[ch]);
+                            float v0 = fmaf(acc[c0 + 2 * j], sc.x, sh.x);
+                            float v1 = fmaf(acc[c0 + 2 * j + 1], sc.y, sh.y);
                             if (relu) {
                                 v0 = v0 > 0.f ? v0 : 0.f;
                                 v1 = v1 > 0.f ? v1 : 0.f;

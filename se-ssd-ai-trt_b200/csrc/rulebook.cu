@@ -250,8 +250,8 @@ __device__ __forceinline__ bool bucket_find(const uint32_t* __restrict__ base, u
     for (uint32_t probe = 0; probe < cap; ++probe) {
         const uint4* bk = reinterpret_cast<const uint4*>(base + (size_t)h * 8);
         const uint4 hi = __ldg(bk + 1);
+        const uint4 lo = __ldg(bk);   // same 32-byte sector: issued together, one round trip
         if (hi.x == gkey) {
-            const uint4 lo = __ldg(bk);
             *vals = make_int4((int)lo.x, (int)lo.y, (int)lo.z, (int)lo.w);
             return true;
         }
@@ -265,52 +265,103 @@ __device__ __forceinline__ int pick4(const int4& v, uint32_t i) {
     return i == 0 ? v.x : (i == 1 ? v.y : (i == 2 ? v.z : v.w));
 }
 
-// Submanifold 3x3x3 neighbour map. One thread per (output row, kz, ky): it resolves the three kx
-// neighbours from one or two buckets and writes nbr[b][k][o] for k = (kz*3 + ky)*3 + {0,1,2}. Threads of
-// a warp share (kz, ky) and cover 32 consecutive rows of one 128-row tile, so the writes are coalesced
-// and the per-tile offset mask (which offsets have any neighbour) costs one ballot per k.
+// First probe of a bucket lookup, kept apart from its evaluation so that a thread can have the probes of
+// several lookups in flight at once (the kernel below is bound by dependent round trips to L2, not by bytes).
+struct BucketProbe {
+    uint4 lo, hi;
+    uint32_t h;
+};
+__device__ __forceinline__ void bucket_probe(const uint32_t* __restrict__ base, int shift, uint32_t gkey, bool on,
+                                             BucketProbe* p) {
+    p->h = hash_slot(gkey, shift);
+    p->hi = make_uint4(kEmpty, 0u, 0u, 0u);
+    p->lo = make_uint4(~0u, ~0u, ~0u, ~0u);
+    if (on) {
+        const uint4* bk = reinterpret_cast<const uint4*>(base + (size_t)p->h * 8);
+        p->hi = __ldg(bk + 1);
+        p->lo = __ldg(bk);
+    }
+}
+__device__ __forceinline__ int4 bucket_finish(const uint32_t* __restrict__ base, uint32_t cap, uint32_t gkey,
+                                              const BucketProbe& p) {
+    if (p.hi.x == gkey) return make_int4((int)p.lo.x, (int)p.lo.y, (int)p.lo.z, (int)p.lo.w);
+    int4 none = make_int4(-1, -1, -1, -1);
+    if (p.hi.x == kEmpty) return none;
+    uint32_t h = (p.h + 1) & (cap - 1);   // first slot taken by another group: keep probing
+    for (uint32_t probe = 1; probe < cap; ++probe) {
+        const uint4* bk = reinterpret_cast<const uint4*>(base + (size_t)h * 8);
+        const uint4 hi = __ldg(bk + 1);
+        const uint4 lo = __ldg(bk);
+        if (hi.x == gkey) return make_int4((int)lo.x, (int)lo.y, (int)lo.z, (int)lo.w);
+        if (hi.x == kEmpty) return none;
+        h = (h + 1) & (cap - 1);
+    }
+    return none;
+}
+
+// Submanifold 3x3x3 neighbour map. One thread per output row: it reads its coordinates once and, for each
+// kz, has the bucket probes of the three ky rows (one or two 32-byte buckets each) in flight together,
+// then writes nbr[b][k][o] for the nine offsets of that kz. Threads of a warp cover 32 consecutive rows of
+// one 128-row tile, so the writes are coalesced and the per-tile offset mask (which offsets have any
+// neighbour) costs one ballot per offset and one atomic per warp.
 __global__ void __launch_bounds__(kThreads)
 nbr_build_subm_kernel(const int4* __restrict__ coors, const int32_t* __restrict__ voxel_num, int batch,
                       int max_voxels, int Z, int Y, int X, Buckets t, int32_t* __restrict__ nbr,
                       uint32_t* __restrict__ tile_mask, int tiles_per_frame) {
     const int chunks = (max_voxels + kThreads - 1) / kThreads;
-    const int items = batch * 9 * chunks;
+    const int items = batch * chunks;
     for (int it = blockIdx.x; it < items; it += gridDim.x) {
-        const int b = it / (9 * chunks);
-        const int r = it - b * (9 * chunks);
-        const int j = r / chunks;
-        const int o = (r - j * chunks) * kThreads + threadIdx.x;
+        const int b = it / chunks;
+        const int o0 = (it - b * chunks) * kThreads;
         int n = voxel_num[b];
         n = n > max_voxels ? max_voxels : n;
+        if (o0 >= n) continue;
+        const int o = o0 + threadIdx.x;
         const bool live = o < n;
-        int res[3] = {-1, -1, -1};
-        if (live) {
-            const int4 c = __ldg(&coors[(size_t)b * max_voxels + o]);
-            const int kz = j / 3, ky = j - kz * 3;
-            const int z = c.y + kz - 1, y = c.z + ky - 1, x = c.w;
-            if (z >= 0 && z < Z && y >= 0 && y < Y && x >= 0 && x < X) {
-                const uint32_t center = ((uint32_t)z * Y + y) * X + x;
-                const uint32_t k_lo = x > 0 ? center - 1 : center, k_hi = x + 1 < X ? center + 1 : center;
-                const uint32_t g_lo = k_lo >> 2, g_hi = k_hi >> 2;
-                const uint32_t* base = t.data + (size_t)b * t.cap * 8;
-                int4 va = make_int4(-1, -1, -1, -1), vb = va;
-                bucket_find(base, t.cap, t.shift, g_lo, &va);
-                if (g_hi != g_lo) bucket_find(base, t.cap, t.shift, g_hi, &vb); else vb = va;
-#pragma unroll
-                for (int d = 0; d < 3; ++d) {
-                    const int xx = x + d - 1;
-                    if (xx < 0 || xx >= X) continue;
-                    const uint32_t key = center + d - 1;
-                    res[d] = pick4((key >> 2) == g_lo ? va : vb, key & 3u);
-                }
-            }
-        }
+        int4 c = make_int4(0, -4, -4, -4);
+        if (live) c = __ldg(&coors[(size_t)b * max_voxels + o]);
+        const int x = c.w;
+        const bool x_ok = live && x >= 0 && x < X;
+        const uint32_t* base = t.data + (size_t)b * t.cap * 8;
+        int32_t* out = nbr + (size_t)b * 27 * max_voxels + o;
         uint32_t bits = 0;
 #pragma unroll
-        for (int d = 0; d < 3; ++d) {
-            const int k = j * 3 + d;
-            if (live) nbr[((size_t)b * 27 + k) * max_voxels + o] = res[d];
-            if (__ballot_sync(0xFFFFFFFFu, res[d] >= 0)) bits |= 1u << k;
+        for (int kz = 0; kz < 3; ++kz) {
+            const int z = c.y + kz - 1;
+            BucketProbe pa[3], pb[3];
+            uint32_t center[3], g_lo[3], g_hi[3];
+            bool on[3];
+#pragma unroll
+            for (int ky = 0; ky < 3; ++ky) {
+                const int y = c.z + ky - 1;
+                on[ky] = x_ok && z >= 0 && z < Z && y >= 0 && y < Y;
+                center[ky] = on[ky] ? ((uint32_t)z * Y + y) * X + x : 0u;
+                g_lo[ky] = (x > 0 ? center[ky] - 1 : center[ky]) >> 2;
+                g_hi[ky] = (x + 1 < X ? center[ky] + 1 : center[ky]) >> 2;
+                bucket_probe(base, t.shift, g_lo[ky], on[ky], &pa[ky]);
+                bucket_probe(base, t.shift, g_hi[ky], on[ky] && g_hi[ky] != g_lo[ky], &pb[ky]);
+            }
+#pragma unroll
+            for (int ky = 0; ky < 3; ++ky) {
+                int res[3] = {-1, -1, -1};
+                if (on[ky]) {
+                    const int4 va = bucket_finish(base, t.cap, g_lo[ky], pa[ky]);
+                    const int4 vb = g_hi[ky] != g_lo[ky] ? bucket_finish(base, t.cap, g_hi[ky], pb[ky]) : va;
+#pragma unroll
+                    for (int d = 0; d < 3; ++d) {
+                        const int xx = x + d - 1;
+                        if (xx < 0 || xx >= X) continue;
+                        const uint32_t key = center[ky] + d - 1;
+                        res[d] = pick4((key >> 2) == g_lo[ky] ? va : vb, key & 3u);
+                    }
+                }
+#pragma unroll
+                for (int d = 0; d < 3; ++d) {
+                    const int k = (kz * 3 + ky) * 3 + d;
+                    if (live) out[(size_t)k * max_voxels] = res[d];
+                    if (__ballot_sync(0xFFFFFFFFu, res[d] >= 0)) bits |= 1u << k;
+                }
+            }
         }
         if ((threadIdx.x & 31) == 0 && bits && live)
             atomicOr(&tile_mask[(size_t)b * tiles_per_frame + (o >> 7)], bits);
