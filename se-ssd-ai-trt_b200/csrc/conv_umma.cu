@@ -86,11 +86,20 @@ __device__ __forceinline__ bool mbar_try_wait_parked(uint32_t bar, uint32_t pari
     return ok != 0;
 }
 // Bounded wait: false when the phase did not complete within the clock limit or the CTA is aborting.
+// The polling loop is kept to a handful of instructions (abort flag and clock are looked at every 32
+// polls): the role warps spend most of their life here and must not take the issue slots of the warps
+// that feed the pipeline. RELAXED waits (roles with slack: weight and index prefetch) also sleep
+// between polls.
+template <bool RELAXED = false>
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
     if (mbar_try_wait(bar, parity)) return true;
     const long long t0 = clock64();
     for (;;) {
-        if (mbar_try_wait_parked(bar, parity, 2000u)) return true;
+#pragma unroll 1
+        for (int i = 0; i < 32; ++i) {
+            if (RELAXED) __nanosleep(200);
+            if (mbar_try_wait_parked(bar, parity, 1000u)) return true;
+        }
         if (*abort_flag) return false;
         if (clock64() - t0 > WAIT_LIMIT_CYCLES) {
             *abort_flag = 1;
@@ -573,7 +582,7 @@ conv_umma_kernel(const __half* __restrict__ in, __half* __restrict__ out, const 
             uint32_t rem = 0;
             while (ok && next_item<KG>(m, nstages, g, rem, t)) {
                 const uint32_t si = my_i % IDX_STAGES;
-                ok = mbar_wait(smem_u32(&ctl->i_empty[si]), ((my_i / IDX_STAGES) & 1u) ^ 1u, abort_flag);
+                ok = mbar_wait<true>(smem_u32(&ctl->i_empty[si]), ((my_i / IDX_STAGES) & 1u) ^ 1u, abort_flag);
                 if (!ok) break;
 #pragma unroll
                 for (int j = 0; j < KG; ++j) {
@@ -604,7 +613,7 @@ conv_umma_kernel(const __half* __restrict__ in, __half* __restrict__ out, const 
                     for (int t = 0; t < TILES; ++t) stage_any |= stage_active<KG>(m[t], g);
                     if (!stage_any) continue;
                     const uint32_t sb = my_b % B_STAGES;
-                    ok = mbar_wait(smem_u32(&ctl->b_empty[sb]), ((my_b / B_STAGES) & 1u) ^ 1u, abort_flag);
+                    ok = mbar_wait<true>(smem_u32(&ctl->b_empty[sb]), ((my_b / B_STAGES) & 1u) ^ 1u, abort_flag);
                     if (!ok) break;
                     const uint32_t bar = smem_u32(&ctl->b_full[sb]);
                     mbar_arrive_expect_tx(bar, B_BYTES);
