@@ -41,6 +41,13 @@ def load_package():
     return mod
 
 
+# DRAM bytes (dram__bytes_read.sum + dram__bytes_write.sum) per frame and launch, averaged over the launches
+# of each kernel, from the ncu capture summarised in profiles/conv_umma_64x64_sweep_4frames.md (sweep
+# workload, 4 frames per launch); traffic grows in proportion to the frames of a launch.
+NCU_DRAM_BYTES_PER_FRAME = {
+    "sweep": {"conv_umma<f16,64,64>": 14.5e6, "conv_umma<f16,32,32>": 36.1e6},
+}
+
 WORKLOADS = {
     # name: (points per frame, object clusters, frames per GPU per step, max_voxels, frames per launch group)
     "sweep": dict(points=120000, boxes=40, frames=512, max_voxels=200000, batch=8,
@@ -179,7 +186,9 @@ def run_reference(args, pkg, wl, rank, world):
                 warmup=args.warmup, ms_per_step=1000.0 * total_s / max(args.steps, 1), higher_is_better=True,
                 scaling="weak", vs_baseline=None, dtype="f16", data="synthetic",
                 config=dict(workload=args.workload, description=wl["desc"], points_per_frame=wl["points"],
-                            frames_per_step=total_f // max(args.steps, 1)),
+                            frames_per_gpu_per_step=wl["frames"], max_voxels=wl["max_voxels"],
+                            sample_frames_per_step=total_f // max(args.steps, 1),
+                            parallelism="host threads of rank 0, one frame per thread"),
                 cpu_baseline=info,
                 e2e=dict(value=value, unit="frames/s", h2d_bytes_per_step=0, d2h_bytes_per_step=0))
     print(json.dumps(line), flush=True)
@@ -322,7 +331,10 @@ def main():
             else:
                 ach = byts / (ms / 1e3) / 1e9
                 roof = dict(bound="hbm", achieved=ach, peak=pk["hbm"], unit="GB/s", frac=ach / pk["hbm"], traffic=None)
-            roof.update(kernel=top, launches=len(idx), avg_launch_ms=ms / len(idx), peak_source=pk["source"])
+            per_frame = NCU_DRAM_BYTES_PER_FRAME.get(args.workload, {}).get(top)
+            roof.update(kernel=top, launches=len(idx), avg_launch_ms=ms / len(idx), peak_source=pk["source"],
+                        traffic=per_frame * B if per_frame else None,
+                        traffic_source="ncu capture of a 4-frame launch scaled by frames per launch" if per_frame else None)
         else:
             vox_rows = int(bb.layer_view(ws, B, P, -1)[2].sum())
             byts = 16.0 * float(grp_sizes.sum()) + vox_rows * (16 + 8 + 4) + 4 * B
