@@ -51,6 +51,7 @@ typedef enum sessd_error {
 #define SESSD_STATUS_PAIR_OVERFLOW 4  /* a rulebook column exceeded max_voxels entries on export */
 #define SESSD_STATUS_BAD_COORD 8      /* an input coordinate lies outside the declared grid; row ignored */
 #define SESSD_STATUS_TIMEOUT 16       /* a bounded wait inside a kernel gave up; the call's outputs are invalid */
+#define SESSD_STATUS_BOX_OVERFLOW 32  /* more boxes passed the score filter than max_box_num; extra ones dropped */
 
 typedef enum sessd_dtype { SESSD_F32 = 0, SESSD_F16 = 1 } sessd_dtype;
 
@@ -261,6 +262,56 @@ void* sessd_pipeline_dense(sessd_pipeline* pl, int s);
 void* sessd_pipeline_workspace(sessd_pipeline* pl, int s);
 /* Index of the last coordinate level of a backbone (number of strided layers). */
 int sessd_backbone_final_level(const sessd_backbone* bb);
+
+/* ------------------------------------------------------------------------------------------
+ * Detection post-processing (the two plugins after the 2D head, se-ssd-ai-trt.cpp:1421-1461).
+ * Tensors: box_preds f32 [B][N][7], cls_preds f32 [B][N][1], iou_preds f32 [B][N][1], dir_preds f32 [B][N][2],
+ * N = feature_map_height * feature_map_width * direction_angle_num anchors per frame (70,400).
+ * ---------------------------------------------------------------------------------------- */
+
+/* GenerateAnchorDecodePlugin's serialized blob, field for field (generateAnchorDecode.cu:400-421; note
+ * that the reference writes max_y a second time where max_z belongs, :409 - the plugin mirror repeats it). */
+typedef struct sessd_anchor_params {
+    float min_x, max_x, min_y, max_y, min_z, max_z;
+    int32_t feature_map_height, feature_map_width;
+    float car_length, car_width, car_height;
+    float direction_angle_0, direction_angle_1;
+    int32_t direction_angle_num;   /* 1 or 2 */
+} sessd_anchor_params;
+
+/* FilterBoxByScorePlugin's serialized blob, field for field (filterBoxByScore.cu:430-441). */
+typedef struct sessd_filter_params {
+    int32_t feature_map_height, feature_map_width, direction_angle_num, max_box_num;
+    float score_threshold, direction_offset;
+} sessd_filter_params;
+
+/* Replaces GenerateAnchorDecodePlugin::enqueue (generateAnchorDecode.cu:331-360: memset, generate_anchor_kernel
+ * :201-247, decode_kernel :268-316). inputs = { box_preds }, outputs = { boxes f32 [B][N][7] =
+ * (x, y, z, w, l, h, yaw) }. No workspace (as the reference, :193-198). Anchors are computed in registers,
+ * not stored. */
+int sessd_anchor_decode_enqueue(const sessd_anchor_params* p, int batch, const void* const* inputs,
+                                void* const* outputs, void* stream);
+
+/* Replaces FilterBoxByScorePlugin::getWorkspaceSize (filterBoxByScore.cu:252-256, which returns 0): the ordered
+ * compaction needs one counter per 256 anchors and the status block. */
+size_t sessd_filter_boxes_workspace_bytes(const sessd_filter_params* p, int batch);
+
+/* Replaces FilterBoxByScorePlugin::enqueue (filterBoxByScore.cu:339-381) and filter_box_by_score_kernel (:260-324).
+ * inputs = { boxes (decoded), cls_preds, iou_preds, dir_preds },
+ * outputs = { box f32 [B][max_box][9] = (x, y, z, w, l, h, yaw', 0, score), score f32 [B][max_box],
+ *             iou f32 [B][max_box], direction f32 [B][max_box], valid_line_num u32 [B] }.
+ * Rows are appended in ascending anchor index (the reference: arrival order of an atomic) and only the first
+ * max_box_num are kept: valid_line_num = min(passed, max_box_num), SESSD_STATUS_BOX_OVERFLOW when more passed
+ * (the reference writes past its outputs). Outputs are cleared first, as the reference does. */
+int sessd_filter_boxes_enqueue(const sessd_filter_params* p, int batch, const void* const* inputs,
+                               void* const* outputs, void* workspace, size_t workspace_bytes, void* stream);
+
+/* Both plugins in one pass: inputs[0] holds the regression outputs (what GenerateAnchorDecodePlugin receives)
+ * and only the anchors that pass the score threshold are decoded; outputs and workspace as
+ * sessd_filter_boxes_enqueue. The two parameter blocks must agree on the feature map and direction count. */
+int sessd_decode_filter_enqueue(const sessd_anchor_params* anchors, const sessd_filter_params* p, int batch,
+                                const void* const* inputs, void* const* outputs, void* workspace,
+                                size_t workspace_bytes, void* stream);
 
 /* Per-launch timing for benchmarks (takes the place of the reference's unused Tn::Profiler,
  * Utils.h:24-49). Between begin and end every kernel this library launches from the calling thread is

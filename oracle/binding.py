@@ -159,6 +159,41 @@ def zero_pad2d(x, top, bottom, left, right):
     return out
 
 
+def anchor_params(point_range, car_size, direction_angles):
+    """{min_x, max_x, min_y, max_y, min_z, max_z, car_length, car_width, car_height, angle0, angle1} as fp32."""
+    xmin, ymin, zmin, xmax, ymax, zmax = point_range
+    return np.asarray([xmin, xmax, ymin, ymax, zmin, zmax, *car_size, *direction_angles], np.float32)
+
+
+def anchor_decode(box_preds, aparams, height, width, dir_num):
+    """[N, 7] regression outputs -> [N, 7] boxes (N = height * width * dir_num), one frame."""
+    box_preds = np.ascontiguousarray(box_preds, np.float32)
+    assert box_preds.shape == (height * width * dir_num, 7)
+    out = np.empty_like(box_preds)
+    lib().oracle_anchor_decode(_ptr(box_preds, C.c_float), _ptr(np.ascontiguousarray(aparams, np.float32), C.c_float),
+                               C.c_int(height), C.c_int(width), C.c_int(dir_num), _ptr(out, C.c_float))
+    return out
+
+
+def filter_boxes(boxes, cls, iou, dirs, dir_num, max_box, threshold, dir_offset):
+    """Score filter + ordered compaction of one frame; returns (box9, cls, iou, dir, valid, passed)."""
+    boxes = np.ascontiguousarray(boxes, np.float32)
+    n = boxes.shape[0]
+    cls = np.ascontiguousarray(cls, np.float32).reshape(n)
+    iou = np.ascontiguousarray(iou, np.float32).reshape(n)
+    dirs = np.ascontiguousarray(dirs, np.float32).reshape(n, 2)
+    ob, oc = np.empty((max_box, 9), np.float32), np.empty(max_box, np.float32)
+    oi, od = np.empty(max_box, np.float32), np.empty(max_box, np.float32)
+    valid = np.zeros(1, np.uint32)
+    lib().oracle_filter_boxes.restype = C.c_int
+    passed = lib().oracle_filter_boxes(_ptr(boxes, C.c_float), _ptr(cls, C.c_float), _ptr(iou, C.c_float),
+                                       _ptr(dirs, C.c_float), C.c_int(n), C.c_int(dir_num), C.c_int(max_box),
+                                       C.c_float(threshold), C.c_float(dir_offset), _ptr(ob, C.c_float),
+                                       _ptr(oc, C.c_float), _ptr(oi, C.c_float), _ptr(od, C.c_float),
+                                       _ptr(valid, C.c_uint32))
+    return ob, oc, oi, od, int(valid[0]), int(passed)
+
+
 def _vparams(point_range, voxel_size):
     xmin, ymin, zmin, xmax, ymax, zmax = point_range
     return np.asarray([xmin, xmax, ymin, ymax, zmin, zmax, *voxel_size, 0, 0, 0], np.float32)

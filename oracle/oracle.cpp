@@ -416,6 +416,85 @@ void oracle_zero_pad2d(const float* in, size_t planes, int H, int W, int top, in
             for (int x = 0; x < W; ++x) out[(p * Hp + y + top) * Wp + x + left] = in[(p * H + y) * W + x];
 }
 
+// Anchor generation followed by SECOND-style box decoding, one frame. Follows generate_anchor_kernel
+// (generateAnchorDecode.cu:201-247: anchor centre from the cell index and the range, z = -1, size = car
+// size in (w, l, h) order, yaw = direction_angle_[idx % num] for the first two directions, else 0) and
+// decode_kernel (:268-316: x, y scaled by the anchor's diagonal, z by its height, sizes by exp, yaw
+// added). aparams = {min_x, max_x, min_y, max_y, min_z, max_z, car_length, car_width, car_height,
+// direction_angle_0, direction_angle_1}; all arithmetic in fp32 without contraction.
+void oracle_anchor_decode(const float* box_preds, const float* aparams, int height, int width, int dir_num,
+                          float* out) {
+    const float min_x = aparams[0], max_x = aparams[1], min_y = aparams[2], max_y = aparams[3];
+    const float car_l = aparams[6], car_w = aparams[7], car_h = aparams[8];
+    const float angle[2] = {aparams[9], aparams[10]};
+    const float stride_x = (max_x - min_x) / (float)width, stride_y = (max_y - min_y) / (float)height;
+    const float x_start = min_x + stride_x / 2, y_start = min_y + stride_y / 2;
+    const int n = height * width * dir_num;
+    for (int i = 0; i < n; ++i) {
+        const float ax = x_start + (float)((i % (width * dir_num)) / dir_num) * stride_x;
+        const float ay = y_start + (float)(i / (width * dir_num)) * stride_y;
+        const float az = -1.0f, aw = car_w, al = car_l, ah = car_h;
+        const int d = i % dir_num;
+        const float ar = d < 2 ? angle[d] : 0.0f;
+        const float* t = box_preds + (size_t)i * 7;
+        float* o = out + (size_t)i * 7;
+        const float diagonal = std::sqrt(al * al + aw * aw);
+        o[0] = t[0] * diagonal + ax;
+        o[1] = t[1] * diagonal + ay;
+        o[2] = t[2] * ah + az;
+        o[3] = std::exp(t[3]) * aw;
+        o[4] = std::exp(t[4]) * al;
+        o[5] = std::exp(t[5]) * ah;
+        o[6] = t[6] + ar;
+    }
+}
+
+// Score filter with compaction, one frame. Follows filter_box_by_score_kernel (filterBoxByScore.cu:260-324):
+// score = sigmoid(cls); kept when score >= threshold; iou' = (iou + 1) / 2; output score = score * iou'^4;
+// direction = last arg-max of dir_preds[i][0 .. dir_num) (row stride 2, as the reference hard-codes);
+// yaw + 3.1415926 when (direction 1 and yaw - offset < 0) or (direction 0 and yaw - offset > 0);
+// out_box = {x, y, z, w, l, h, yaw', 0, output score}. The reference appends in the arrival order of an
+// atomic and never checks max_box_num; the rule here is ascending anchor index, the first max_box rows
+// kept. Outputs are cleared first (enqueue, :353-371). Returns the number of anchors that passed (which
+// may exceed max_box); *valid receives min(passed, max_box).
+int oracle_filter_boxes(const float* boxes, const float* cls, const float* iou, const float* dir, int n, int dir_num,
+                        int max_box, float threshold, float dir_offset, float* out_box, float* out_cls,
+                        float* out_iou, float* out_dir, uint32_t* valid) {
+    std::memset(out_box, 0, sizeof(float) * (size_t)max_box * 9);
+    std::memset(out_cls, 0, sizeof(float) * (size_t)max_box);
+    std::memset(out_iou, 0, sizeof(float) * (size_t)max_box);
+    std::memset(out_dir, 0, sizeof(float) * (size_t)max_box);
+    int passed = 0;
+    for (int i = 0; i < n; ++i) {
+        const float score = 1.0f / (1.0f + std::exp(-cls[i]));
+        if (!(score >= threshold)) continue;
+        const int idx = passed++;
+        if (idx >= max_box) continue;
+        const float q = (iou[i] + 1.0f) * 0.5f;
+        out_iou[idx] = q;
+        const float s = score * q * q * q * q;
+        out_cls[idx] = s;
+        int best = 0;
+        float best_v = -1000000.0f;
+        for (int j = 0; j < dir_num; ++j)
+            if (dir[(size_t)i * 2 + j] >= best_v) {
+                best_v = dir[(size_t)i * 2 + j];
+                best = j;
+            }
+        out_dir[idx] = (float)best;
+        const float* bx = boxes + (size_t)i * 7;
+        float* o = out_box + (size_t)idx * 9;
+        for (int j = 0; j < 6; ++j) o[j] = bx[j];
+        const float yaw = bx[6];
+        const bool flip = (best == 1 && yaw - dir_offset < 0) || (best == 0 && yaw - dir_offset > 0);
+        o[6] = flip ? yaw + 3.1415926f : yaw;
+        o[7] = 0.0f;
+        o[8] = s;
+    }
+    *valid = (uint32_t)(passed < max_box ? passed : max_box);
+    return passed;
+}
+
 void oracle_round_half(float* x, size_t n) {
     for (size_t i = 0; i < n; ++i) x[i] = to_half_and_back(x[i]);
 }

@@ -17,6 +17,7 @@ from .build import LIB_PATH, build
 
 F32, F16 = 0, 1
 STATUS_VOXEL_OVERFLOW, STATUS_HASH_FULL, STATUS_PAIR_OVERFLOW, STATUS_BAD_COORD, STATUS_TIMEOUT = 1, 2, 4, 8, 16
+STATUS_BOX_OVERFLOW = 32
 
 EXPORTS = (
     "sessd_voxel_configure", "sessd_voxelize_workspace_bytes", "sessd_voxelize_enqueue", "sessd_voxelize_num_points",
@@ -30,6 +31,8 @@ EXPORTS = (
     "sessd_backbone_final_level", "sessd_pipeline_create", "sessd_pipeline_destroy", "sessd_pipeline_run_host",
     "sessd_pipeline_run_device", "sessd_pipeline_dense", "sessd_pipeline_workspace", "sessd_launch_count",
     "sessd_profile_begin", "sessd_profile_end", "sessd_read_status", "sessd_last_cuda_error", "sessd_version",
+    "sessd_anchor_decode_enqueue", "sessd_filter_boxes_workspace_bytes", "sessd_filter_boxes_enqueue",
+    "sessd_decode_filter_enqueue",
 )
 
 
@@ -58,6 +61,22 @@ class Pad2DParams(C.Structure):
     _fields_ = [("top", C.c_int32), ("bottom", C.c_int32), ("left", C.c_int32), ("right", C.c_int32)]
 
 
+class AnchorParams(C.Structure):
+    """GenerateAnchorDecodePlugin's parameters in its serialisation order (generateAnchorDecode.cu:400-421)."""
+    _fields_ = [("min_x", C.c_float), ("max_x", C.c_float), ("min_y", C.c_float), ("max_y", C.c_float),
+                ("min_z", C.c_float), ("max_z", C.c_float),
+                ("feature_map_height", C.c_int32), ("feature_map_width", C.c_int32),
+                ("car_length", C.c_float), ("car_width", C.c_float), ("car_height", C.c_float),
+                ("direction_angle_0", C.c_float), ("direction_angle_1", C.c_float), ("direction_angle_num", C.c_int32)]
+
+
+class FilterParams(C.Structure):
+    """FilterBoxByScorePlugin's parameters in its serialisation order (filterBoxByScore.cu:430-441)."""
+    _fields_ = [("feature_map_height", C.c_int32), ("feature_map_width", C.c_int32),
+                ("direction_angle_num", C.c_int32), ("max_box_num", C.c_int32),
+                ("score_threshold", C.c_float), ("direction_offset", C.c_float)]
+
+
 class S2DParams(C.Structure):
     _fields_ = [("feature_map_size_x", C.c_int32), ("feature_map_size_y", C.c_int32),
                 ("feature_map_size_z", C.c_int32), ("feature_map_channel", C.c_int32)]
@@ -73,7 +92,8 @@ def lib():
         if not os.path.exists(LIB_PATH):
             raise SessdError(f"{LIB_PATH} is missing: run build() (needs nvcc); there is no CPU fallback")
         L = C.CDLL(LIB_PATH)
-        for name in ("sessd_voxelize_workspace_bytes", "sessd_conv_workspace_bytes", "sessd_backbone_workspace_bytes"):
+        for name in ("sessd_voxelize_workspace_bytes", "sessd_conv_workspace_bytes", "sessd_backbone_workspace_bytes",
+                     "sessd_filter_boxes_workspace_bytes"):
             getattr(L, name).restype = C.c_size_t
         for name in ("sessd_voxelize_num_points", "sessd_pipeline_dense", "sessd_pipeline_workspace"):
             getattr(L, name).restype = C.c_void_p
@@ -273,6 +293,52 @@ def zero_pad2d(x, pad: Pad2DParams, dtype=F32):
     out = torch.empty((B, Cc, H + pad.top + pad.bottom, W + pad.left + pad.right), dtype=_tdtype(dtype), device=x.device)
     _check(lib().sessd_zero_pad2d_enqueue(C.byref(pad), B, Cc, H, W, dtype, _vp(x), _vp(out), _stream()),
            "sessd_zero_pad2d_enqueue")
+    return out
+
+
+def anchor_params(point_range=synth.POINT_RANGE, height=schedule.FEATURE_MAP_HEIGHT, width=schedule.FEATURE_MAP_WIDTH,
+                  car_size=schedule.CAR_SIZE, direction_angles=schedule.DIRECTION_ANGLES) -> AnchorParams:
+    """AnchorParams from (xmin, ymin, zmin, xmax, ymax, zmax), (length, width, height) and the anchor yaws."""
+    xmin, ymin, zmin, xmax, ymax, zmax = point_range
+    return AnchorParams(xmin, xmax, ymin, ymax, zmin, zmax, height, width, *car_size, direction_angles[0],
+                        direction_angles[1], len(direction_angles))
+
+
+def filter_params(height=schedule.FEATURE_MAP_HEIGHT, width=schedule.FEATURE_MAP_WIDTH, direction_angle_num=2,
+                  max_box_num=schedule.MAX_BOX_NUM, score_threshold=schedule.SCORE_THRESHOLD,
+                  direction_offset=schedule.DIRECTION_OFFSET) -> FilterParams:
+    return FilterParams(height, width, direction_angle_num, max_box_num, score_threshold, direction_offset)
+
+
+def anchor_decode(box_preds, params: AnchorParams):
+    """[B, N, 7] regression outputs -> [B, N, 7] boxes (GenerateAnchorDecodePlugin)."""
+    torch = _torch()
+    out = torch.empty_like(box_preds)
+    _check(lib().sessd_anchor_decode_enqueue(C.byref(params), box_preds.shape[0], _vp(box_preds), _vp(out), _stream()),
+           "sessd_anchor_decode_enqueue")
+    return out
+
+
+def filter_boxes(boxes, cls, iou, dirs, params: FilterParams, anchors: AnchorParams = None):
+    """Score filter + ordered compaction (FilterBoxByScorePlugin). With `anchors`, `boxes` holds the regression
+    outputs and decoding is fused in. Returns dict(box, score, iou, direction, valid, status)."""
+    torch = _torch()
+    B, M = boxes.shape[0], params.max_box_num
+    f32 = dict(dtype=torch.float32, device=boxes.device)
+    out = dict(box=torch.empty((B, M, 9), **f32), score=torch.empty((B, M), **f32), iou=torch.empty((B, M), **f32),
+               direction=torch.empty((B, M), **f32), valid=torch.empty((B,), dtype=torch.int32, device=boxes.device))
+    nbytes = lib().sessd_filter_boxes_workspace_bytes(C.byref(params), B)
+    ws = torch.empty((nbytes,), dtype=torch.uint8, device=boxes.device)
+    ins = _vp(boxes, cls, iou, dirs)
+    outs = _vp(out["box"], out["score"], out["iou"], out["direction"], out["valid"])
+    if anchors is None:
+        _check(lib().sessd_filter_boxes_enqueue(C.byref(params), B, ins, outs, C.c_void_p(ws.data_ptr()),
+                                                C.c_size_t(nbytes), _stream()), "sessd_filter_boxes_enqueue")
+    else:
+        _check(lib().sessd_decode_filter_enqueue(C.byref(anchors), C.byref(params), B, ins, outs,
+                                                 C.c_void_p(ws.data_ptr()), C.c_size_t(nbytes), _stream()),
+               "sessd_decode_filter_enqueue")
+    out["status"] = read_status(ws)
     return out
 
 

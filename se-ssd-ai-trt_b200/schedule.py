@@ -20,6 +20,15 @@ BACKBONE_FEATURE_MAP_SIZE_Y = 200   # params.h:195
 BACKBONE_FEATURE_MAP_SIZE_Z = 2     # params.h:196
 BACKBONE_FEATURE_MAP_CHANNEL = 64   # params.h:197
 
+# Detection post-processing (anchor decode + score filter), params.h:357-368
+FEATURE_MAP_HEIGHT = 200
+FEATURE_MAP_WIDTH = 176
+DIRECTION_ANGLES = (0.0, 1.57)
+CAR_SIZE = (3.9, 1.6, 1.56)         # length, width, height
+MAX_BOX_NUM = 500
+SCORE_THRESHOLD = 0.45
+DIRECTION_OFFSET = 0.0
+
 
 @dataclass(frozen=True)
 class ConvLayer:

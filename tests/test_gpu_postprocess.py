@@ -1,0 +1,103 @@
+"""GPU parity: anchor decode and score filter entry points against the oracle.
+
+Indices, counts and the direction class are exact; floating-point columns within 1e-5 relative (the GPU's
+expf and the host's differ in the last place; everything else is computed in the same order).
+"""
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+
+TOL = 1e-5
+
+
+def _head_outputs(gpu, seed, frames, height, width, dirs, logit_mean=-4.0):
+    """Seeded stand-ins for the 2D head's four outputs, [frames, N, *]."""
+    rs = np.random.RandomState(seed)
+    n = height * width * dirs
+    box = (rs.randn(frames, n, 7) * 0.3).astype(np.float32)
+    cls = (logit_mean + 1.5 * rs.randn(frames, n, 1)).astype(np.float32)
+    iou = rs.uniform(-1, 1, (frames, n, 1)).astype(np.float32)
+    dr = rs.randn(frames, n, 2).astype(np.float32)
+    dr[:, ::7, 1] = dr[:, ::7, 0]          # ties: the later direction must win
+    # keep every score clear of the threshold so that a last-place difference of expf cannot flip a decision
+    thr = gpu.schedule.SCORE_THRESHOLD
+    score = 1.0 / (1.0 + np.exp(-cls.astype(np.float64)))
+    cls[np.abs(score - thr) < 1e-4] = -10.0
+    return box, cls, iou, dr
+
+
+def _close(got, want):
+    np.testing.assert_allclose(got, want, rtol=TOL, atol=1e-6)
+
+
+def _to_gpu(*arrays):
+    import torch
+
+    return [torch.from_numpy(a).cuda() for a in arrays]
+
+
+def test_anchor_decode_full_size(gpu, oracle):
+    S = gpu.schedule
+    box, _, _, _ = _head_outputs(gpu, 1, 2, S.FEATURE_MAP_HEIGHT, S.FEATURE_MAP_WIDTH, 2)
+    ap = gpu.anchor_params()
+    got = gpu.anchor_decode(_to_gpu(box)[0], ap).cpu().numpy()
+    oparams = oracle.anchor_params(gpu.synth.POINT_RANGE, S.CAR_SIZE, S.DIRECTION_ANGLES)
+    for b in range(2):
+        want = oracle.anchor_decode(box[b], oparams, S.FEATURE_MAP_HEIGHT, S.FEATURE_MAP_WIDTH, 2)
+        _close(got[b], want)
+        # columns without exp are computed in the same order: identical
+        np.testing.assert_array_equal(got[b][:, [0, 1, 2, 6]], want[:, [0, 1, 2, 6]])
+
+
+def _check_filter(gpu, oracle, frames, height, width, max_box, logit_mean, fused, seed):
+    S = gpu.schedule
+    box, cls, iou, dr = _head_outputs(gpu, seed, frames, height, width, 2, logit_mean)
+    ap = gpu.anchor_params(height=height, width=width)
+    fp = gpu.filter_params(height=height, width=width, max_box_num=max_box)
+    oparams = oracle.anchor_params(gpu.synth.POINT_RANGE, S.CAR_SIZE, S.DIRECTION_ANGLES)
+    decoded = np.stack([oracle.anchor_decode(box[b], oparams, height, width, 2) for b in range(frames)])
+    tb, tc, ti, td = _to_gpu(box if fused else decoded, cls, iou, dr)
+    r = gpu.filter_boxes(tb, tc, ti, td, fp, anchors=ap if fused else None)
+    overflow = False
+    for b in range(frames):
+        ob, oc, oi, od, valid, passed = oracle.filter_boxes(decoded[b], cls[b], iou[b], dr[b], 2, max_box,
+                                                            S.SCORE_THRESHOLD, S.DIRECTION_OFFSET)
+        overflow |= passed > max_box
+        assert int(r["valid"][b]) == valid
+        np.testing.assert_array_equal(r["direction"][b].cpu().numpy(), od)
+        _close(r["box"][b].cpu().numpy(), ob)
+        _close(r["score"][b].cpu().numpy(), oc)
+        _close(r["iou"][b].cpu().numpy(), oi)
+        assert not r["box"][b, valid:].any() and not r["score"][b, valid:].any()
+    assert bool(r["status"] & gpu.STATUS_BOX_OVERFLOW) == overflow
+    return overflow
+
+
+@pytest.mark.parametrize("fused", [False, True])
+def test_filter_full_size(gpu, oracle, fused):
+    S = gpu.schedule
+    assert not _check_filter(gpu, oracle, 3, S.FEATURE_MAP_HEIGHT, S.FEATURE_MAP_WIDTH, S.MAX_BOX_NUM, -4.0, fused, 2)
+
+
+@pytest.mark.parametrize("fused", [False, True])
+def test_filter_clamps_at_max_box_and_reports(gpu, oracle, fused):
+    assert _check_filter(gpu, oracle, 2, 40, 36, 50, -1.0, fused, 3)
+
+
+def test_filter_nothing_passes_and_ragged_last_chunk(gpu, oracle):
+    # 7 x 9 x 2 = 126 anchors: less than one chunk; all scores far below the threshold
+    assert not _check_filter(gpu, oracle, 1, 7, 9, 10, -30.0, True, 4)
+    # 13 x 21 x 2 = 546 anchors: two full chunks and a ragged one
+    _check_filter(gpu, oracle, 2, 13, 21, 500, 0.0, False, 5)
+
+
+def test_filter_rejects_bad_arguments(gpu):
+    import torch
+
+    fp = gpu.filter_params(max_box_num=0)
+    x = torch.zeros((1, 70400, 7), device="cuda")
+    with pytest.raises(gpu.SessdError):
+        gpu.filter_boxes(x, x, x, x, fp)
+    with pytest.raises(gpu.SessdError):   # the two parameter blocks disagree on the feature map
+        gpu.filter_boxes(x, x, x, x, gpu.filter_params(), anchors=gpu.anchor_params(height=100))

@@ -178,3 +178,89 @@ def test_golden_vectors(oracle, pkg):
     nz = np.flatnonzero(r["dense"])
     np.testing.assert_array_equal(nz, g["dense_nz"])
     np.testing.assert_array_equal(r["dense"].ravel()[nz], g["dense_val"])
+
+
+# ---- detection post-processing (anchor decode, score filter) -------------------------------------------
+
+KITTI_RANGE = (0.0, -40.0, -3.0, 70.4, 40.0, 1.0)
+CAR = (3.9, 1.6, 1.56)
+ANGLES = (0.0, 1.57)
+
+
+def test_anchor_layout_and_identity_decode(oracle):
+    """Zero regression outputs give the anchors themselves (generateAnchorDecode.cu:201-247): x fastest,
+    two yaws per cell, centres at half a stride from the range minimum, z = -1, (w, l, h) order."""
+    H, W = 200, 176
+    ap = oracle.anchor_params(KITTI_RANGE, CAR, ANGLES)
+    out = oracle.anchor_decode(np.zeros((H * W * 2, 7), np.float32), ap, H, W, 2)
+    f = np.float32
+    sx, sy = f(f(70.4) - f(0.0)) / f(W), f(f(40.0) - f(-40.0)) / f(H)
+    assert out[0].tolist() == [f(0.0) + sx / f(2), f(-40.0) + sy / f(2), -1.0, f(1.6), f(3.9), f(1.56), 0.0]
+    assert out[1, 6] == f(1.57) and out[1, 0] == out[0, 0]
+    assert out[2, 0] == f(0.0) + sx / f(2) + f(1) * sx                 # next cell along x
+    assert out[2 * W, 1] == f(-40.0) + sy / f(2) + f(1) * sy           # next row along y
+    assert out[-1, 0] == f(0.0) + sx / f(2) + f(W - 1) * sx and out[-1, 1] == f(-40.0) + sy / f(2) + f(H - 1) * sy
+
+
+def test_anchor_decode_against_numpy(oracle):
+    H, W = 9, 11
+    rs = np.random.RandomState(3)
+    t = (rs.randn(H * W * 2, 7) * 0.5).astype(np.float32)
+    out = oracle.anchor_decode(t, oracle.anchor_params(KITTI_RANGE, CAR, ANGLES), H, W, 2)
+    idx = np.arange(H * W * 2)
+    f = np.float32
+    sx, sy = f(70.4) / f(W), f(80.0) / f(H)
+    ax = (f(0.0) + sx / f(2)) + ((idx % (W * 2)) // 2).astype(np.float32) * sx
+    ay = (f(-40.0) + sy / f(2)) + (idx // (W * 2)).astype(np.float32) * sy
+    diag = np.sqrt(f(3.9) * f(3.9) + f(1.6) * f(1.6), dtype=np.float32)
+    want = np.stack([t[:, 0] * diag + ax, t[:, 1] * diag + ay, t[:, 2] * f(1.56) + f(-1.0),
+                     np.exp(t[:, 3]) * f(1.6), np.exp(t[:, 4]) * f(3.9), np.exp(t[:, 5]) * f(1.56),
+                     t[:, 6] + np.where(idx % 2 == 0, f(0.0), f(1.57))], axis=1).astype(np.float32)
+    np.testing.assert_allclose(out, want, rtol=1e-6, atol=1e-6)
+
+
+def test_filter_boxes_hand_case(oracle):
+    """Six anchors, threshold 0.45 (logit of 0.45 is about -0.2007)."""
+    boxes = np.arange(42, dtype=np.float32).reshape(6, 7)
+    boxes[:, 6] = [0.5, -0.5, 0.5, -0.5, 0.0, 2.0]
+    cls = np.array([3.0, -5.0, 0.0, -0.19, -0.21, 10.0], np.float32)     # pass: 0, 2, 3, 5
+    iou = np.array([1.0, 1.0, 0.0, -1.0, 1.0, 0.5], np.float32)
+    dirs = np.array([[1, 0], [0, 0], [0, 1], [0, 1], [0, 0], [2, 2]], np.float32)
+    ob, oc, oi, od, valid, passed = oracle.filter_boxes(boxes, cls, iou, dirs, 2, 3, 0.45, 0.0)
+    assert (valid, passed) == (3, 4)                       # anchor 5 passes too but the table holds 3 rows
+    np.testing.assert_array_equal(ob[:, :6], boxes[[0, 2, 3], :6])
+    np.testing.assert_array_equal(od, [0, 1, 1])
+    np.testing.assert_array_equal(oi, [1.0, 0.5, 0.0])
+    f = np.float32
+    # anchor 0: direction 0 and yaw > 0 -> yaw + pi; anchor 2: direction 1, yaw > 0 -> kept; anchor 3:
+    # direction 1 and yaw < 0 -> yaw + pi
+    np.testing.assert_array_equal(ob[:, 6], [f(0.5) + f(3.1415926), f(0.5), f(-0.5) + f(3.1415926)])
+    s0 = f(1) / (f(1) + np.exp(f(-3.0)))
+    np.testing.assert_allclose(oc, [s0, f(0.5) * f(0.5) ** 4, 0.0], rtol=1e-6)
+    np.testing.assert_array_equal(ob[:, 8], oc)
+    assert not ob[:, 7].any()
+    # a tie between the two directions selects the later one (>= in the reference loop)
+    _, _, _, od2, _, _ = oracle.filter_boxes(boxes, cls, iou, dirs, 2, 6, 0.45, 0.0)
+    assert od2[3] == 1 and od2[:4].tolist() == [0, 1, 1, 1]
+
+
+def test_filter_boxes_against_numpy(oracle):
+    rs = np.random.RandomState(8)
+    n = 5000
+    boxes = rs.randn(n, 7).astype(np.float32)
+    cls = (rs.randn(n) * 2 - 2).astype(np.float32)
+    iou = rs.uniform(-1, 1, n).astype(np.float32)
+    dirs = rs.randn(n, 2).astype(np.float32)
+    ob, oc, oi, od, valid, passed = oracle.filter_boxes(boxes, cls, iou, dirs, 2, 10000, 0.45, 0.0)
+    score = (np.float32(1) / (np.float32(1) + np.exp(-cls))).astype(np.float32)
+    keep = np.nonzero(score >= np.float32(0.45))[0]
+    assert valid == passed == len(keep)
+    q = ((iou[keep] + np.float32(1)) * np.float32(0.5)).astype(np.float32)
+    np.testing.assert_array_equal(oi[:valid], q)
+    np.testing.assert_allclose(oc[:valid], score[keep] * q * q * q * q, rtol=1e-6)
+    best = (dirs[keep, 1] >= dirs[keep, 0]).astype(np.float32)
+    np.testing.assert_array_equal(od[:valid], best)
+    yaw = boxes[keep, 6]
+    flip = ((best == 1) & (yaw < 0)) | ((best == 0) & (yaw > 0))
+    np.testing.assert_array_equal(ob[:valid, 6], np.where(flip, yaw + np.float32(3.1415926), yaw).astype(np.float32))
+    assert not ob[valid:].any() and not oc[valid:].any()
