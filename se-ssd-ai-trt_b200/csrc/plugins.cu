@@ -384,6 +384,107 @@ int ZeroPad2dPlugin::getOutputDataType(int, const int32_t* inputTypes, int) cons
 
 void ZeroPad2dPlugin::serialize(void* buffer) const { std::memcpy(buffer, &p_, sizeof(p_)); }
 
+// ---------------------------------------------------------------- GenerateAnchorDecodePlugin
+
+GenerateAnchorDecodePlugin::GenerateAnchorDecodePlugin(float min_x_range, float max_x_range, float min_y_range,
+                                                       float max_y_range, float min_z_range, float max_z_range,
+                                                       int feature_map_height, int feature_map_width, float car_length,
+                                                       float car_width, float car_height, float direction_angle_0,
+                                                       float direction_angle_1, int direction_angle_num) {
+    // argument order of the reference constructor (generateAnchorDecode.cu:105-114)
+    p_ = sessd_anchor_params{min_x_range, max_x_range, min_y_range, max_y_range, min_z_range, max_z_range,
+                             feature_map_height, feature_map_width, car_length, car_width, car_height,
+                             direction_angle_0, direction_angle_1, direction_angle_num};
+}
+
+GenerateAnchorDecodePlugin::GenerateAnchorDecodePlugin(const void* data, size_t length) {
+    std::memset(&p_, 0, sizeof(p_));
+    if (data && length >= sizeof(p_)) std::memcpy(&p_, data, sizeof(p_));   // generateAnchorDecode.cu:116-137
+}
+
+PluginBase* GenerateAnchorDecodePlugin::clone() const { return new GenerateAnchorDecodePlugin(*this); }
+
+int GenerateAnchorDecodePlugin::getOutputDimensions(int outputIndex, const TensorDesc* inputs, int nbInputs,
+                                                    TensorDesc* out) const {
+    if (!inputs || nbInputs < 1 || !out || outputIndex != 0) return -1;
+    *out = make_desc({inputs[0].d[0], inputs[0].d[1], inputs[0].d[2]}, inputs[0].dtype);   // :150-171
+    return 0;
+}
+
+bool GenerateAnchorDecodePlugin::supportsFormatCombination(int pos, const TensorDesc* inOut, int, int) const {
+    return (pos == 0 || pos == 1) && inOut[pos].dtype == SESSD_DT_FLOAT && inOut[pos].format == 0;   // :173-187
+}
+
+int GenerateAnchorDecodePlugin::enqueue(const TensorDesc* inputDesc, const TensorDesc*, const void* const* inputs,
+                                        void* const* outputs, void*, void* stream) {
+    if (!inputDesc) return SESSD_ERR_NULL;
+    return sessd_anchor_decode_enqueue(&p_, inputDesc[0].d[0], inputs, outputs, stream);
+}
+
+int GenerateAnchorDecodePlugin::getOutputDataType(int, const int32_t* inputTypes, int) const { return inputTypes[0]; }
+
+void GenerateAnchorDecodePlugin::serialize(void* buffer) const {
+    // The reference writes max_y_range_ where max_z_range_ belongs (generateAnchorDecode.cu:409), so a
+    // deserialised plugin has max_z = max_y; the blob is reproduced byte for byte (max_z is never used).
+    sessd_anchor_params blob = p_;
+    blob.max_z = p_.max_y;
+    std::memcpy(buffer, &blob, sizeof(blob));
+}
+
+// ---------------------------------------------------------------- FilterBoxByScorePlugin
+
+FilterBoxByScorePlugin::FilterBoxByScorePlugin(int feature_map_height, int feature_map_width, int direction_angle_num,
+                                               int max_box_num, float score_threshold, float direction_offset) {
+    p_ = sessd_filter_params{feature_map_height, feature_map_width, direction_angle_num, max_box_num, score_threshold,
+                             direction_offset};
+}
+
+FilterBoxByScorePlugin::FilterBoxByScorePlugin(const void* data, size_t length) {
+    std::memset(&p_, 0, sizeof(p_));
+    if (data && length >= sizeof(p_)) std::memcpy(&p_, data, sizeof(p_));   // filterBoxByScore.cu:115-128
+}
+
+PluginBase* FilterBoxByScorePlugin::clone() const { return new FilterBoxByScorePlugin(*this); }
+
+int FilterBoxByScorePlugin::getOutputDimensions(int outputIndex, const TensorDesc* inputs, int nbInputs,
+                                                TensorDesc* out) const {
+    if (!inputs || nbInputs < 4 || !out) return -1;
+    const int batch = inputs[0].d[0];
+    switch (outputIndex) {   // filterBoxByScore.cu:138-199
+        case 0: *out = make_desc({batch, p_.max_box_num, inputs[0].d[2] + 2}, inputs[0].dtype); return 0;
+        case 1: *out = make_desc({batch, p_.max_box_num}, inputs[0].dtype); return 0;
+        case 2: *out = make_desc({batch, p_.max_box_num, inputs[2].d[2]}, inputs[0].dtype); return 0;
+        case 3: *out = make_desc({batch, p_.max_box_num, 1}, inputs[0].dtype); return 0;
+        case 4: *out = make_desc({batch, 1}, SESSD_DT_INT32); return 0;
+        default: return -1;
+    }
+}
+
+bool FilterBoxByScorePlugin::supportsFormatCombination(int pos, const TensorDesc* inOut, int, int) const {
+    if (pos < 0 || pos > 8) return false;
+    const TensorDesc& t = inOut[pos];
+    return t.format == 0 && t.dtype == (pos == 8 ? SESSD_DT_INT32 : SESSD_DT_FLOAT);   // :202-243
+}
+
+size_t FilterBoxByScorePlugin::getWorkspaceSize(const TensorDesc* inputs, int nbInputs, const TensorDesc*, int) const {
+    if (!inputs || nbInputs < 1) return 0;
+    return sessd_filter_boxes_workspace_bytes(&p_, inputs[0].d[0]);
+}
+
+int FilterBoxByScorePlugin::enqueue(const TensorDesc* inputDesc, const TensorDesc*, const void* const* inputs,
+                                    void* const* outputs, void* workspace, void* stream) {
+    if (!inputDesc) return SESSD_ERR_NULL;
+    const int batch = inputDesc[0].d[0];
+    return sessd_filter_boxes_enqueue(&p_, batch, inputs, outputs, workspace,
+                                      sessd_filter_boxes_workspace_bytes(&p_, batch), stream);
+}
+
+int FilterBoxByScorePlugin::getOutputDataType(int index, const int32_t* inputTypes, int) const {
+    return index == 4 ? SESSD_DT_INT32 : inputTypes[0];   // filterBoxByScore.cu:384-390
+}
+
+void FilterBoxByScorePlugin::serialize(void* buffer) const { std::memcpy(buffer, &p_, sizeof(p_)); }
+
 // ---------------------------------------------------------------- creators
 
 namespace {
@@ -512,6 +613,52 @@ public:
     }
 };
 
+class AnchorCreator : public PluginCreator {
+public:
+    const char* getPluginName() const override { return "GenerateAnchorDecodePlugin"; }
+    const std::vector<std::string>& getFieldNames() const override {
+        static const std::vector<std::string> n = {"point_cloud_range", "feature_map_size", "car_size", "direction_angle",
+                                                   "direction_angle_num"};   // generateAnchorDecode.cu:443-447
+        return n;
+    }
+    PluginBase* createPlugin(const char*, const Field* f, int n) const override {
+        const Field *rng = find_field(f, n, "point_cloud_range"), *sz = find_field(f, n, "feature_map_size"),
+                    *car = find_field(f, n, "car_size"), *ang = find_field(f, n, "direction_angle"),
+                    *num = find_field(f, n, "direction_angle_num");
+        if (!rng || !sz || !car || !ang || !num) return nullptr;
+        // range arrives as (xmin, ymin, zmin, xmax, ymax, zmax), size as (height, width), car as
+        // (length, width, height) (generateAnchorDecode.cu:492-527)
+        return new GenerateAnchorDecodePlugin(float_at(rng, 0), float_at(rng, 3), float_at(rng, 1), float_at(rng, 4),
+                                              float_at(rng, 2), float_at(rng, 5), int_at(sz, 0), int_at(sz, 1),
+                                              float_at(car, 0), float_at(car, 1), float_at(car, 2), float_at(ang, 0),
+                                              float_at(ang, 1), int_at(num, 0));
+    }
+    PluginBase* deserializePlugin(const char*, const void* d, size_t len) const override {
+        return len >= sizeof(sessd_anchor_params) ? new GenerateAnchorDecodePlugin(d, len) : nullptr;
+    }
+};
+
+class FilterCreator : public PluginCreator {
+public:
+    const char* getPluginName() const override { return "FilterBoxByScorePlugin"; }
+    const std::vector<std::string>& getFieldNames() const override {
+        static const std::vector<std::string> n = {"feature_map_size", "direction_angle_num", "max_box_num",
+                                                   "score_threshold", "direction_offset"};   // filterBoxByScore.cu:466-470
+        return n;
+    }
+    PluginBase* createPlugin(const char*, const Field* f, int n) const override {
+        const Field *sz = find_field(f, n, "feature_map_size"), *num = find_field(f, n, "direction_angle_num"),
+                    *mb = find_field(f, n, "max_box_num"), *thr = find_field(f, n, "score_threshold"),
+                    *off = find_field(f, n, "direction_offset");
+        if (!sz || !num || !mb || !thr) return nullptr;
+        return new FilterBoxByScorePlugin(int_at(sz, 0), int_at(sz, 1), int_at(num, 0), int_at(mb, 0), float_at(thr, 0),
+                                          float_at(off, 0));
+    }
+    PluginBase* deserializePlugin(const char*, const void* d, size_t len) const override {
+        return len >= sizeof(sessd_filter_params) ? new FilterBoxByScorePlugin(d, len) : nullptr;
+    }
+};
+
 }  // namespace
 
 const PluginCreator* getPluginCreator(const char* name, const char* version) {
@@ -520,7 +667,9 @@ const PluginCreator* getPluginCreator(const char* name, const char* version) {
     static const SparseCreator sparse;
     static const S2DCreator s2d;
     static const PadCreator pad;
-    static const PluginCreator* all[] = {&voxel, &subm, &sparse, &s2d, &pad};
+    static const AnchorCreator anchor;
+    static const FilterCreator filter;
+    static const PluginCreator* all[] = {&voxel, &subm, &sparse, &s2d, &pad, &anchor, &filter};
     if (!name || (version && std::strcmp(version, "1"))) return nullptr;
     for (const PluginCreator* c : all)
         if (!std::strcmp(c->getPluginName(), name)) return c;

@@ -1,4 +1,5 @@
-// Host-side mirror of the reference's sparse front end plugins (the four of the front end plus ZeroPad2d).
+// Host-side mirror of the reference's plugins: the four of the sparse front end, ZeroPad2d, and the two
+// detection post-processing plugins (GenerateAnchorDecode, FilterBoxByScore).
 //
 // Same class names, creator field names, member-function names, tensor orders, return conventions and
 // serialised byte layouts as the reference's TensorRT plugins; the bodies call the C ABI of sessd.h
@@ -171,6 +172,57 @@ public:
 
 private:
     sessd_pad2d_params p_;
+};
+
+// generateAnchorDecode.h:19-106. Input {box_preds f32 [B, N, 7]}; output {boxes f32 [B, N, 7]}.
+class GenerateAnchorDecodePlugin : public PluginBase {
+public:
+    GenerateAnchorDecodePlugin(float min_x_range, float max_x_range, float min_y_range, float max_y_range,
+                               float min_z_range, float max_z_range, int feature_map_height, int feature_map_width,
+                               float car_length, float car_width, float car_height, float direction_angle_0,
+                               float direction_angle_1, int direction_angle_num);
+    GenerateAnchorDecodePlugin(const void* data, size_t length);
+    PluginBase* clone() const override;
+    int getOutputDimensions(int outputIndex, const TensorDesc* inputs, int nbInputs, TensorDesc* out) const override;
+    bool supportsFormatCombination(int pos, const TensorDesc* inOut, int nbInputs, int nbOutputs) const override;
+    void configurePlugin(const TensorDesc*, int, const TensorDesc*, int) override {}
+    size_t getWorkspaceSize(const TensorDesc*, int, const TensorDesc*, int) const override { return 0; }
+    int enqueue(const TensorDesc* inputDesc, const TensorDesc* outputDesc, const void* const* inputs,
+                void* const* outputs, void* workspace, void* stream) override;
+    int getOutputDataType(int index, const int32_t* inputTypes, int nbInputs) const override;
+    const char* getPluginType() const override { return "GenerateAnchorDecodePlugin"; }
+    int getNbOutputs() const override { return 1; }
+    size_t getSerializationSize() const override { return sizeof(sessd_anchor_params); }
+    void serialize(void* buffer) const override;
+    const sessd_anchor_params& params() const { return p_; }
+
+private:
+    sessd_anchor_params p_;
+};
+
+// filterBoxByScore.h:18-90. Inputs {boxes [B, N, 7], cls_preds [B, N, 1], iou_preds [B, N, 1], dir_preds
+// [B, N, 2]}; outputs {box [B, max_box, 9], score [B, max_box], iou [B, max_box, 1], direction
+// [B, max_box, 1], valid_line_num i32 [B, 1]}.
+class FilterBoxByScorePlugin : public PluginBase {
+public:
+    FilterBoxByScorePlugin(int feature_map_height, int feature_map_width, int direction_angle_num, int max_box_num,
+                           float score_threshold, float direction_offset);
+    FilterBoxByScorePlugin(const void* data, size_t length);
+    PluginBase* clone() const override;
+    int getOutputDimensions(int outputIndex, const TensorDesc* inputs, int nbInputs, TensorDesc* out) const override;
+    bool supportsFormatCombination(int pos, const TensorDesc* inOut, int nbInputs, int nbOutputs) const override;
+    void configurePlugin(const TensorDesc*, int, const TensorDesc*, int) override {}
+    size_t getWorkspaceSize(const TensorDesc* inputs, int nbInputs, const TensorDesc* outputs, int nbOutputs) const override;
+    int enqueue(const TensorDesc* inputDesc, const TensorDesc* outputDesc, const void* const* inputs,
+                void* const* outputs, void* workspace, void* stream) override;
+    int getOutputDataType(int index, const int32_t* inputTypes, int nbInputs) const override;
+    const char* getPluginType() const override { return "FilterBoxByScorePlugin"; }
+    int getNbOutputs() const override { return 5; }
+    size_t getSerializationSize() const override { return sizeof(sessd_filter_params); }
+    void serialize(void* buffer) const override;
+
+private:
+    sessd_filter_params p_;
 };
 
 // IPluginCreator mirror: field names as the reference advertises them (e.g. submConv3dlayer.cu:737-748).

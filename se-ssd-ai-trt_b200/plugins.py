@@ -98,6 +98,10 @@ class Plugin:
         rc = _lib().sessd_plugin_output_dims(self.handle, index, arr, len(inputs), C.byref(out))
         return None if rc else out
 
+    def output_dtype(self, index, input_types):
+        arr = (C.c_int32 * len(input_types))(*input_types)
+        return _lib().sessd_plugin_output_dtype(self.handle, index, arr, len(input_types))
+
     def supports_format(self, pos, in_out, nb_inputs):
         arr = (TensorDesc * len(in_out))(*in_out)
         return bool(_lib().sessd_plugin_supports_format(self.handle, pos, arr, nb_inputs, len(in_out) - nb_inputs))

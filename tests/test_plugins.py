@@ -45,7 +45,11 @@ def test_creators_advertise_the_reference_field_names(pkg):
     assert P.field_names("SubmConv3dLayerPlugin") == conv and P.field_names("SparseConv3dLayerPlugin") == conv
     assert P.field_names("Sparse2DensePlugin") == ["feature_map_size", "feature_map_channel"]
     assert P.field_names("ZeroPad2dPlugin") == ["zero_padding_2d_size"]
-    assert P.field_names("GenerateAnchorDecodePlugin") is None
+    assert P.field_names("GenerateAnchorDecodePlugin") == ["point_cloud_range", "feature_map_size", "car_size",
+                                                           "direction_angle", "direction_angle_num"]
+    assert P.field_names("FilterBoxByScorePlugin") == ["feature_map_size", "direction_angle_num", "max_box_num",
+                                                       "score_threshold", "direction_offset"]
+    assert P.field_names("NoSuchPlugin") is None
     lib = pkg.lib()
     for n in P.PLUGIN_EXPORTS:
         assert hasattr(lib, n)
@@ -283,3 +287,73 @@ def test_frame_through_the_four_plugins_like_the_reference_network(gpu, oracle, 
     assert (np.abs(got6 - y6) / denom).max() <= tol
     want_dense = oracle.sparse2dense(got6, c6, n6, 32, Z, Y, X)
     np.testing.assert_array_equal(dense.float().cpu().numpy(), want_dense)
+
+
+def _anchor_fields():
+    return {"point_cloud_range": np.array([0.0, -40.0, -3.0, 70.4, 40.0, 1.0], np.float32),
+            "feature_map_size": np.array([200, 176], np.int32), "car_size": np.array([3.9, 1.6, 1.56], np.float32),
+            "direction_angle": np.array([0.0, 1.57], np.float32), "direction_angle_num": np.array([2], np.int32)}
+
+
+def _filter_fields(max_box=500):
+    return {"feature_map_size": np.array([200, 176], np.int32), "direction_angle_num": np.array([2], np.int32),
+            "max_box_num": np.array([max_box], np.int32), "score_threshold": np.array([0.45], np.float32),
+            "direction_offset": np.array([0.0], np.float32)}
+
+
+def test_post_processing_blobs_and_dims(pkg):
+    P = pkg.plugins
+    a = P.Plugin.create("GenerateAnchorDecodePlugin", _anchor_fields())
+    # 6 range floats, 2 ints, 5 floats, 1 int; the sixth float repeats max_y (generateAnchorDecode.cu:409)
+    assert a.serialize() == struct.pack("<6f2i5fi", 0.0, 70.4, -40.0, 40.0, -3.0, 40.0, 200, 176, 3.9, 1.6, 1.56, 0.0, 1.57, 2)
+    box = P.TensorDesc.of((1, 70400, 7), P.DT_FLOAT)
+    assert a.nb_outputs() == 1 and a.output_dims(0, [box]).dims() == (1, 70400, 7) and a.workspace_size([box], []) == 0
+    assert a.supports_format(0, [box, box], 1) and not a.supports_format(1, [box, P.TensorDesc.of((1, 70400, 7), P.DT_HALF)], 1)
+    assert P.Plugin.deserialize("GenerateAnchorDecodePlugin", a.serialize()).serialize() == a.serialize()
+
+    f = P.Plugin.create("FilterBoxByScorePlugin", _filter_fields())
+    assert f.serialize() == struct.pack("<4i2f", 200, 176, 2, 500, 0.45, 0.0)     # filterBoxByScore.cu:430-441
+    ins = [box, P.TensorDesc.of((1, 70400, 1), P.DT_FLOAT), P.TensorDesc.of((1, 70400, 1), P.DT_FLOAT),
+           P.TensorDesc.of((1, 70400, 2), P.DT_FLOAT)]
+    assert f.nb_outputs() == 5
+    assert [f.output_dims(i, ins).dims() for i in range(5)] == [(1, 500, 9), (1, 500), (1, 500, 1), (1, 500, 1), (1, 1)]
+    assert f.output_dtype(4, [P.DT_FLOAT] * 4) == P.DT_INT32 and f.output_dtype(0, [P.DT_FLOAT] * 4) == P.DT_FLOAT
+    assert f.workspace_size(ins, []) >= 1024 + 4 * 275
+
+
+@pytest.mark.gpu
+def test_post_processing_plugins_chained(gpu, oracle):
+    """GenerateAnchorDecodePlugin -> FilterBoxByScorePlugin, wired as at se-ssd-ai-trt.cpp:1421-1461."""
+    import torch
+
+    P, S = gpu.plugins, gpu.schedule
+    rs = np.random.RandomState(12)
+    n = 70400
+    box = (rs.randn(1, n, 7) * 0.3).astype(np.float32)
+    cls = (-4.0 + 1.5 * rs.randn(1, n, 1)).astype(np.float32)
+    score = 1.0 / (1.0 + np.exp(-cls.astype(np.float64)))
+    cls[np.abs(score - 0.45) < 1e-4] = -10.0
+    iou = rs.uniform(-1, 1, (1, n, 1)).astype(np.float32)
+    dr = rs.randn(1, n, 2).astype(np.float32)
+    a = P.Plugin.create("GenerateAnchorDecodePlugin", _anchor_fields())
+    f = P.Plugin.deserialize("FilterBoxByScorePlugin", struct.pack("<4i2f", 200, 176, 2, 500, 0.45, 0.0))
+    stream = torch.cuda.current_stream().cuda_stream
+    d_box = P.TensorDesc.of((1, n, 7), P.DT_FLOAT)
+    t_box, t_cls, t_iou, t_dir = [torch.from_numpy(x).cuda() for x in (box, cls, iou, dr)]
+    decoded = torch.empty_like(t_box)
+    assert a.enqueue([d_box], [d_box], [t_box], [decoded], None, stream) == 0
+    ins = [d_box, P.TensorDesc.of((1, n, 1), P.DT_FLOAT), P.TensorDesc.of((1, n, 1), P.DT_FLOAT),
+           P.TensorDesc.of((1, n, 2), P.DT_FLOAT)]
+    outs_d = [f.output_dims(i, ins) for i in range(5)]
+    outs = [torch.full(d.dims(), 7, dtype=torch.int32 if i == 4 else torch.float32, device="cuda")
+            for i, d in enumerate(outs_d)]
+    ws = torch.empty(f.workspace_size(ins, outs_d), dtype=torch.uint8, device="cuda")
+    assert f.enqueue(ins, outs_d, [decoded, t_cls, t_iou, t_dir], outs, ws, stream) == 0
+    torch.cuda.synchronize()
+    op = oracle.anchor_params(gpu.synth.POINT_RANGE, S.CAR_SIZE, S.DIRECTION_ANGLES)
+    want_dec = oracle.anchor_decode(box[0], op, 200, 176, 2)
+    ob, oc, oi, od, valid, passed = oracle.filter_boxes(want_dec, cls[0], iou[0], dr[0], 2, 500, 0.45, 0.0)
+    assert int(outs[4][0, 0]) == valid and 0 < valid <= 500
+    np.testing.assert_allclose(outs[0][0].cpu().numpy(), ob, rtol=1e-5, atol=1e-6)
+    np.testing.assert_allclose(outs[1][0].cpu().numpy(), oc, rtol=1e-5, atol=1e-6)
+    np.testing.assert_array_equal(outs[3][0, :, 0].cpu().numpy(), od)
