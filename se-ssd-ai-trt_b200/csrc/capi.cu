@@ -124,7 +124,8 @@ void conv_workspace_layout(Bump& bump, const sessd_conv_params* p, const ConvGeo
 }
 
 bool conv_params_ok(const sessd_conv_params* p, int batch) {
-    if (p->in_channel < 1 || p->out_channel < 1 || p->max_voxels < 1) return false;
+    // table slots travel in 24 bits beside the kernel offset (strided rulebook entries)
+    if (p->in_channel < 1 || p->out_channel < 1 || p->max_voxels < 1 || p->max_voxels > (1 << 22)) return false;
     if (batch < 1 || batch > kMaxBatch) return false;
     if ((uint64_t)batch * p->max_voxels * 27ull > 0x7FFFFFFFull) return false;
     return true;

@@ -122,6 +122,7 @@ struct ConvGeom {
     int kvol;
     int span_max[3];  // most candidate outputs one input can have per axis
     int ncand;        // product of span_max
+    int cand_shift;   // log2(ncand) when ncand is a power of two, else -1
 };
 
 // ---- device side -------------------------------------------------------------------------
@@ -194,6 +195,7 @@ __device__ __forceinline__ int block_sum(int v) {
 // numbered 0,1,2,... in entry order. count pass + emit pass, no block waits on another block.
 struct NumberingArgs {
     const int32_t* slot_of;     // [B][entry_stride]
+    uint32_t slot_mask;         // bits of a non-negative slot_of value that hold the slot (the rest is the caller's)
     int64_t entry_stride;
     const int32_t* entry_count; // [B] device counts (points_size or voxel_num)
     int entry_mul;              // entries(b) = min(entry_count[b], entry_limit) * entry_mul

@@ -21,7 +21,8 @@ __device__ __forceinline__ int numbering_entries(const NumberingArgs& a, int b) 
 __device__ __forceinline__ bool numbering_is_owner(const NumberingArgs& a, const Table& t, int b, int e, int n,
                                                    int* slot_out) {
     if (e >= n) return false;
-    const int s = a.slot_of[(int64_t)b * a.entry_stride + e];
+    int s = a.slot_of[(int64_t)b * a.entry_stride + e];
+    if (s >= 0) s = (int)((uint32_t)s & a.slot_mask);
     *slot_out = s;
     if (s < 0) return false;
     return t.rank[((size_t)b * t.cap + (uint32_t)s) * t.rank_stride] == (uint32_t)e;

@@ -73,10 +73,36 @@ nbr_build_kernel(const int4* __restrict__ out_coors, const int32_t* __restrict__
     }
 }
 
-// Candidate outputs of every input row of a strided convolution. Entry t = i*ncand + e, where e
-// counts this row's candidates in the reference's enumeration order (from the upper corner
-// downward, x fastest: sparseConv3dlayer.cu:351-383). Each in-bounds candidate claims its cell in
-// the output table and lowers the cell's rank to t.
+// Integer helpers for the candidate geometry. Strides and candidate spans are 1, 2 or 3; a division by a
+// run-time divisor costs some 25 instructions on the GPU and these kernels are bound by instruction issue,
+// so the common divisors get shifts.
+__device__ __forceinline__ int div_trunc(int a, int s) {   // C division (rounds toward zero)
+    if (s == 1) return a;
+    if (s == 2) return (a + (a < 0 ? 1 : 0)) >> 1;
+    return a / s;
+}
+__device__ __forceinline__ void split_small(int e, int m, int* q, int* r) {   // e = q * m + r, e >= 0
+    if (m == 1) {
+        *q = e;
+        *r = 0;
+    } else if (m == 2) {
+        *q = e >> 1;
+        *r = e & 1;
+    } else {
+        *q = e / m;
+        *r = e - *q * m;
+    }
+}
+
+constexpr int kSlotBits = 24;                       // slot_of = kernel offset << 24 | table slot
+constexpr uint32_t kSlotMask = (1u << kSlotBits) - 1u;
+
+// Candidate outputs of every input row of a strided convolution. Entry t = i*ncand + e, where
+// e = (cz * span_max_y + cy) * span_max_x + cx walks the row's candidate box from its upper corner downward,
+// x fastest: the reference's enumeration order (sparseConv3dlayer.cu:351-383) with the slots of candidates
+// that do not exist for this row left empty, so entry order = the order a sequential pass meets them.
+// Each in-bounds candidate claims its cell in the output table, lowers the cell's rank to t, and records
+// table slot and kernel offset k = in - out*stride + pad per axis (:366) in slot_of.
 __global__ void __launch_bounds__(kThreads)
 spconv_candidates_kernel(const int4* __restrict__ in_coors, const int32_t* __restrict__ in_num, int batch,
                          int max_voxels, ConvGeom g, Table out_table, int32_t* __restrict__ slot_of,
@@ -90,47 +116,54 @@ spconv_candidates_kernel(const int4* __restrict__ in_coors, const int32_t* __res
         int n = in_num[b];
         n = n > max_voxels ? max_voxels : n;
         if (t >= n * g.ncand) continue;
-        const int i = t / g.ncand, e = t - i * g.ncand;
+        const int i = g.cand_shift >= 0 ? (t >> g.cand_shift) : t / g.ncand;
+        const int e = t - i * g.ncand;
+        int cz, cy, cx, rest;
+        split_small(e, g.span_max[2], &rest, &cx);
+        split_small(rest, g.span_max[1], &cz, &cy);
         const int4 c4 = __ldg(&in_coors[(size_t)b * max_voxels + i]);
         const int c[3] = {c4.y, c4.z, c4.w};
-        int hi[3], span[3];
+        const int cj[3] = {cz, cy, cx};
+        int o[3];
+        bool ok = true;
+        int k = 0;
 #pragma unroll
         for (int j = 0; j < 3; ++j) {
-            // C integer division, as in the reference (sparseConv3dlayer.cu:339-348).
-            const int lo = (c[j] - (g.K[j] - 1) * g.dil - 1 + g.S[j] + g.P[j]) / g.S[j];
-            hi[j] = (c[j] + g.P[j]) / g.S[j];
-            span[j] = (hi[j] - lo) / g.dil + 1;
+            // C integer division, as in the reference (sparseConv3dlayer.cu:339-348); dilation is 1
+            const int lo = div_trunc(c[j] - (g.K[j] - 1) - 1 + g.S[j] + g.P[j], g.S[j]);
+            const int hi = div_trunc(c[j] + g.P[j], g.S[j]);
+            o[j] = hi - cj[j];
+            ok = ok && cj[j] <= hi - lo && o[j] >= 0 && o[j] < g.out_shape[j];
+            k = k * g.K[j] + (c[j] - o[j] * g.S[j] + g.P[j]);
         }
-        int slot = -1;
-        if (e < span[0] * span[1] * span[2]) {
-            const int cx = e % span[2], cy = (e / span[2]) % span[1], cz = e / (span[2] * span[1]);
-            const int oz = hi[0] - cz * g.dil, oy = hi[1] - cy * g.dil, ox = hi[2] - cx * g.dil;
-            if (oz >= 0 && oz < g.out_shape[0] && oy >= 0 && oy < g.out_shape[1] && ox >= 0 && ox < g.out_shape[2]) {
-                const uint32_t key = ((uint32_t)oz * g.out_shape[1] + oy) * g.out_shape[2] + ox;
-                // One 64-bit slot per cell: key in the high word, smallest entry index (rank) in the low word.
-                // A free slot is all ones, so both claiming a cell and lowering its rank are one atomic.
-                unsigned long long* slots =
-                    reinterpret_cast<unsigned long long*>(out_table.rank) + (size_t)b * out_table.cap;
-                const unsigned long long mine = ((unsigned long long)key << 32) | (uint32_t)t;
-                uint32_t h = hash_slot(key, out_table.shift);
-                for (uint32_t probe = 0; probe < out_table.cap; ++probe) {
-                    unsigned long long cur = slots[h];
-                    if (cur == ~0ull) cur = atomicCAS(&slots[h], ~0ull, mine);
-                    if (cur == ~0ull) {
-                        slot = (int)h;   // claimed with our rank
-                        break;
-                    }
-                    if ((uint32_t)(cur >> 32) == key) {
-                        if ((uint32_t)cur > (uint32_t)t) atomicMin(&slots[h], mine);
-                        slot = (int)h;
-                        break;
-                    }
-                    h = (h + 1) & (out_table.cap - 1);
+        int value = -1;
+        if (ok) {
+            const uint32_t key = ((uint32_t)o[0] * g.out_shape[1] + o[1]) * g.out_shape[2] + o[2];
+            // One 64-bit slot per cell: key in the high word, smallest entry index (rank) in the low word.
+            // A free slot is all ones, so both claiming a cell and lowering its rank are one atomic.
+            unsigned long long* slots =
+                reinterpret_cast<unsigned long long*>(out_table.rank) + (size_t)b * out_table.cap;
+            const unsigned long long mine = ((unsigned long long)key << 32) | (uint32_t)t;
+            uint32_t h = hash_slot(key, out_table.shift);
+            int slot = -1;
+            for (uint32_t probe = 0; probe < out_table.cap; ++probe) {
+                unsigned long long cur = slots[h];
+                if (cur == ~0ull) cur = atomicCAS(&slots[h], ~0ull, mine);
+                if (cur == ~0ull) {
+                    slot = (int)h;   // claimed with our rank
+                    break;
                 }
-                if (slot < 0) atomicOr(status, SESSD_STATUS_HASH_FULL);
+                if ((uint32_t)(cur >> 32) == key) {
+                    if ((uint32_t)cur > (uint32_t)t) atomicMin(&slots[h], mine);
+                    slot = (int)h;
+                    break;
+                }
+                h = (h + 1) & (out_table.cap - 1);
             }
+            if (slot < 0) atomicOr(status, SESSD_STATUS_HASH_FULL);
+            else value = (k << kSlotBits) | slot;
         }
-        slot_of[(size_t)b * per_frame + t] = slot;
+        slot_of[(size_t)b * per_frame + t] = value;
     }
 }
 
@@ -244,23 +277,6 @@ bucket_build_kernel(const int4* __restrict__ coors, const int32_t* __restrict__ 
     }
 }
 
-__device__ __forceinline__ bool bucket_find(const uint32_t* __restrict__ base, uint32_t cap, int shift, uint32_t gkey,
-                                            int4* vals) {
-    uint32_t h = hash_slot(gkey, shift);
-    for (uint32_t probe = 0; probe < cap; ++probe) {
-        const uint4* bk = reinterpret_cast<const uint4*>(base + (size_t)h * 8);
-        const uint4 hi = __ldg(bk + 1);
-        const uint4 lo = __ldg(bk);   // same 32-byte sector: issued together, one round trip
-        if (hi.x == gkey) {
-            *vals = make_int4((int)lo.x, (int)lo.y, (int)lo.z, (int)lo.w);
-            return true;
-        }
-        if (hi.x == kEmpty) return false;
-        h = (h + 1) & (cap - 1);
-    }
-    return false;
-}
-
 __device__ __forceinline__ int pick4(const int4& v, uint32_t i) {
     return i == 0 ? v.x : (i == 1 ? v.y : (i == 2 ? v.z : v.w));
 }
@@ -368,13 +384,13 @@ nbr_build_subm_kernel(const int4* __restrict__ coors, const int32_t* __restrict_
     }
 }
 
-// Strided layers: the neighbour map falls out of the candidate entries. Entry t = (input row i,
-// candidate e) with output row id contributes nbr[b][k][id] = i, k = in - out*stride + pad per axis
-// (sparseConv3dlayer.cu:366). The map must have been filled with -1 for rows < out_num beforehand.
+// Strided layers: the neighbour map falls out of the candidate entries. Entry t = (input row i, candidate e)
+// carries its table slot and kernel offset k; with output row id = vals[slot] it contributes
+// nbr[b][k][id] = i. The map must have been filled with -1 for rows < out_num beforehand.
 __global__ void __launch_bounds__(kThreads)
-nbr_scatter_strided_kernel(const int4* __restrict__ in_coors, const int32_t* __restrict__ in_num, int batch,
-                           int max_voxels, ConvGeom g, Table out_table, const int32_t* __restrict__ slot_of,
-                           int32_t* __restrict__ nbr, uint32_t* __restrict__ tile_mask, int tiles_per_frame) {
+nbr_scatter_strided_kernel(const int32_t* __restrict__ in_num, int batch, int max_voxels, ConvGeom g, Table out_table,
+                           const int32_t* __restrict__ slot_of, int32_t* __restrict__ nbr,
+                           uint32_t* __restrict__ tile_mask, int tiles_per_frame) {
     const int64_t per_frame = (int64_t)max_voxels * g.ncand;
     const int chunks = (int)((per_frame + kThreads - 1) / kThreads);
     const int items = batch * chunks;
@@ -384,24 +400,12 @@ nbr_scatter_strided_kernel(const int4* __restrict__ in_coors, const int32_t* __r
         int n = in_num[b];
         n = n > max_voxels ? max_voxels : n;
         if (t >= n * g.ncand) continue;
-        const int slot = slot_of[(size_t)b * per_frame + t];
-        if (slot < 0) continue;
-        const int id = out_table.vals[(size_t)b * out_table.cap + slot];
+        const int v = slot_of[(size_t)b * per_frame + t];
+        if (v < 0) continue;
+        const int id = out_table.vals[(size_t)b * out_table.cap + ((uint32_t)v & kSlotMask)];
         if (id < 0) continue;  // output dropped by the max_voxels cap
-        const int i = t / g.ncand, e = t - i * g.ncand;
-        const int4 c4 = __ldg(&in_coors[(size_t)b * max_voxels + i]);
-        const int c[3] = {c4.y, c4.z, c4.w};
-        int hi[3], span[3];
-#pragma unroll
-        for (int j = 0; j < 3; ++j) {
-            const int lo = (c[j] - (g.K[j] - 1) * g.dil - 1 + g.S[j] + g.P[j]) / g.S[j];
-            hi[j] = (c[j] + g.P[j]) / g.S[j];
-            span[j] = (hi[j] - lo) / g.dil + 1;
-        }
-        const int cx = e % span[2], cy = (e / span[2]) % span[1], cz = e / (span[2] * span[1]);
-        const int oz = hi[0] - cz * g.dil, oy = hi[1] - cy * g.dil, ox = hi[2] - cx * g.dil;
-        const int kz = c[0] - oz * g.S[0] + g.P[0], ky = c[1] - oy * g.S[1] + g.P[1], kx = c[2] - ox * g.S[2] + g.P[2];
-        const int k = (kz * g.K[1] + ky) * g.K[2] + kx;
+        const int k = v >> kSlotBits;
+        const int i = g.cand_shift >= 0 ? (t >> g.cand_shift) : t / g.ncand;
         nbr[((size_t)b * g.kvol + k) * max_voxels + id] = i;
         uint32_t* m = &tile_mask[(size_t)b * tiles_per_frame + (id >> 7)];
         if (!((*reinterpret_cast<volatile uint32_t*>(m) >> k) & 1u)) atomicOr(m, 1u << k);
@@ -472,8 +476,8 @@ int launch_nbr_scatter_strided(const int32_t* in_coors, const int32_t* in_num, c
                                int max_voxels, const ConvGeom& g, const Table& out_table, const int32_t* slot_of,
                                int32_t* nbr, uint32_t* tile_mask, cudaStream_t stream) {
     SESSD_LAUNCH(nbr_clear_kernel, persistent_grid(8), kThreads, 0, stream, nbr, out_num, batch, max_voxels, g.kvol);
-    SESSD_LAUNCH(nbr_scatter_strided_kernel, persistent_grid(8), kThreads, 0, stream,
-                 reinterpret_cast<const int4*>(in_coors), in_num, batch, max_voxels, g, out_table, slot_of, nbr,
+    (void)in_coors;   // the entries carry their kernel offset; coordinates are not needed again
+    SESSD_LAUNCH(nbr_scatter_strided_kernel, persistent_grid(8), kThreads, 0, stream, in_num, batch, max_voxels, g, out_table, slot_of, nbr,
                  tile_mask, (max_voxels + 127) / 128);
     return SESSD_OK;
 }
@@ -515,6 +519,9 @@ int conv_geom_from_params(const sessd_conv_params* p, ConvGeom* g) {
         g->span_max[j] = (g->K[j] - 1) / g->S[j] + 1;
         g->ncand *= g->span_max[j];
     }
+    g->cand_shift = -1;
+    for (int sh = 0; sh < 6; ++sh)
+        if (g->ncand == (1 << sh)) g->cand_shift = sh;
     const uint64_t vin = (uint64_t)g->in_shape[0] * g->in_shape[1] * g->in_shape[2];
     const uint64_t vout = (uint64_t)g->out_shape[0] * g->out_shape[1] * g->out_shape[2];
     if (vin >= 0xFFFFFFFFull || vout >= 0xFFFFFFFFull) return SESSD_ERR_PARAM;  // keys are 32-bit cell indices
@@ -545,6 +552,7 @@ int launch_spconv_outputs(const int32_t* in_coors, const int32_t* in_num, int ba
     a.entry_stride = (int64_t)max_voxels * g.ncand;
     a.entry_count = in_num;
     a.entry_mul = g.ncand;
+    a.slot_mask = kSlotMask;
     a.entry_limit = max_voxels;
     a.chunk_counts = chunk_counts;
     a.chunks_per_frame = chunks_per_frame;

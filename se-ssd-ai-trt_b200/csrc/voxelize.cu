@@ -245,6 +245,7 @@ int voxelize_run(const sessd_voxel_params* p, int batch, int max_points, int out
     a.entry_stride = max_points;
     a.entry_count = points_size;
     a.entry_mul = 1;
+    a.slot_mask = 0x7FFFFFFFu;
     a.entry_limit = max_points;
     a.chunk_counts = w.chunk_counts;
     a.chunks_per_frame = w.chunks;
