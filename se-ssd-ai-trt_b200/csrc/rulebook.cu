@@ -320,7 +320,7 @@ __device__ __forceinline__ int4 bucket_finish(const uint32_t* __restrict__ base,
 // then writes nbr[b][k][o] for the nine offsets of that kz. Threads of a warp cover 32 consecutive rows of
 // one 128-row tile, so the writes are coalesced and the per-tile offset mask (which offsets have any
 // neighbour) costs one ballot per offset and one atomic per warp.
-__global__ void __launch_bounds__(kThreads)
+__global__ void __launch_bounds__(kThreads, 4)
 nbr_build_subm_kernel(const int4* __restrict__ coors, const int32_t* __restrict__ voxel_num, int batch,
                       int max_voxels, int Z, int Y, int X, Buckets t, int32_t* __restrict__ nbr,
                       uint32_t* __restrict__ tile_mask, int tiles_per_frame) {
