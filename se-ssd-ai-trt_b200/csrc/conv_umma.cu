@@ -29,19 +29,18 @@ namespace sessd {
 namespace {
 
 constexpr int TILE_M = 128;
+constexpr int MMA_WARPS_MAX = 2;
 constexpr int TILES = 4;                     // row tiles per CTA iteration; they share each weight block
-constexpr int A_STAGES_MAX = 6;
+constexpr int GATHER_WARPS = 4;               // warps 0-3: gather, later epilogue
+constexpr int A_STAGES_MAX = GATHER_WARPS;
 constexpr int B_STAGES = 2;
-// Ring depth chosen so that two CTAs fit one SM (about 113 KB of shared memory each): 64-wide outputs
-// have 8 KB weight blocks and get 5 gather stages, narrower ones 6. A stage is published to the MMA
-// warp by the copies themselves (cp.async mbarrier arrival), so every free stage can be in flight.
+// One gather stage (16 KB) per gather warp: ring position q lives in slot q % 4 and is filled by warp q % 4, so
+// every barrier of a slot has one producer warp that uses it in order. With the weight ring (2 x Cout x 128 B),
+// the index ring and the control block a CTA takes about 85 KB of shared memory; two CTAs fit one SM.
 constexpr int IDX_STAGES = 6;                // ring of neighbour-index blocks, filled ahead by the index warp
 template <int CIN, int COUT>
 struct RingCfg {
-    static constexpr int KG = 64 / CIN;
-    static constexpr int FIXED = 1024 + 2 * COUT * 128 + IDX_STAGES * KG * 512 + 2 * COUT * 4 + 256;
-    static constexpr int FIT = (115712 - FIXED) / (128 * 128);
-    static constexpr int A_STAGES = FIT >= 6 ? 6 : FIT;
+    static constexpr int A_STAGES = GATHER_WARPS;
 };
 constexpr int ROW_BYTES = 128;               // 64 halves per A/B row
 constexpr int A_BYTES = TILE_M * ROW_BYTES;  // 16 KB
@@ -91,7 +90,7 @@ __device__ __forceinline__ bool mbar_try_wait_parked(uint32_t bar, uint32_t pari
 // that feed the pipeline. RELAXED waits (roles with slack: weight and index prefetch) also sleep
 // between polls.
 template <bool RELAXED = false>
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int where = 0) {
     if (mbar_try_wait(bar, parity)) return true;
     const long long t0 = clock64();
     for (;;) {
@@ -102,6 +101,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
         }
         if (*abort_flag) return false;
         if (clock64() - t0 > WAIT_LIMIT_CYCLES) {
+            if (*abort_flag == 0) abort_flag[1] = where;   // abort_where follows abort_flag in SharedCtl
             *abort_flag = 1;
             return false;
         }
@@ -171,7 +171,10 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
 struct SharedCtl {
-    unsigned long long a_full[A_STAGES_MAX];
+    // a_full[i][s]: stage s has landed, for MMA issuer i (the issuer that owns the stage's row tile). One
+    // barrier per (issuer, slot) keeps a single consumer per barrier: parity waits are only safe when the
+    // waiter has itself seen every earlier phase complete.
+    unsigned long long a_full[MMA_WARPS_MAX][A_STAGES_MAX];
     unsigned long long a_empty[A_STAGES_MAX];
     unsigned long long b_full[B_STAGES];
     unsigned long long b_empty[B_STAGES];
@@ -181,6 +184,11 @@ struct SharedCtl {
     unsigned long long acc_empty;
     uint32_t tmem_base;
     int abort_flag;
+    int abort_where;   // code of the first wait that ran out (role and ring position), for the status block
+#ifdef SESSD_UMMA_TIMING
+    long long t_issue[A_STAGES_MAX];    // when the gathers of the stage were issued
+    long long t_commit[A_STAGES_MAX];   // when the MMAs reading the stage were committed
+#endif
 };
 
 template <int CIN, int COUT>
@@ -222,7 +230,7 @@ __device__ __forceinline__ bool next_item(const uint32_t (&m)[TILES], int nstage
 // Register cap well below what two resident CTAs (the shared-memory limit) could take: the rest of the
 // register file is what lets blocks of other kernels (other streams) run beside them.
 template <int CIN, int COUT>
-__global__ void __maxnreg__(88)
+__global__ void __maxnreg__(96)
 conv_umma_kernel(const __half* __restrict__ in, __half* __restrict__ out, const int32_t* __restrict__ nbr,
                  const uint32_t* __restrict__ tile_mask, const int32_t* __restrict__ out_num,
                  const uint8_t* __restrict__ wtiles, const float* __restrict__ scale, const float* __restrict__ shift,
@@ -250,7 +258,8 @@ conv_umma_kernel(const __half* __restrict__ in, __half* __restrict__ out, const 
 
     if (tid == 0) {
         for (int s = 0; s < A_STAGES; ++s) {
-            mbar_init(smem_u32(&ctl->a_full[s]), TILE_M);
+            for (int i = 0; i < MMA_WARPS_MAX; ++i)
+                mbar_init(smem_u32(&ctl->a_full[i][s]), 32);   // the lanes of the gather warp that owns the stage
             mbar_init(smem_u32(&ctl->a_empty[s]), 1);
         }
         for (int s = 0; s < B_STAGES; ++s) {
@@ -259,11 +268,12 @@ conv_umma_kernel(const __half* __restrict__ in, __half* __restrict__ out, const 
         }
         for (int s = 0; s < IDX_STAGES; ++s) {
             mbar_init(smem_u32(&ctl->i_full[s]), 32);
-            mbar_init(smem_u32(&ctl->i_empty[s]), TILE_M);
+            mbar_init(smem_u32(&ctl->i_empty[s]), 32);
         }
         mbar_init(smem_u32(&ctl->acc_full), MMA_WARPS);        // every MMA issuer reports its tiles
         mbar_init(smem_u32(&ctl->acc_empty), TILE_M);
         ctl->abort_flag = 0;
+        ctl->abort_where = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     for (int c = tid; c < COUT; c += UMMA_THREADS) {
@@ -283,11 +293,12 @@ conv_umma_kernel(const __half* __restrict__ in, __half* __restrict__ out, const 
     volatile int* abort_flag = &ctl->abort_flag;
 #ifdef SESSD_UMMA_TIMING
     const long long t_cta0 = clock64();
-    unsigned long long tacc[16] = {};   // cycle counters kept in registers, written once at the end
+    unsigned long long tacc[32] = {};   // cycle counters kept in registers, written once at the end
 #endif
 
     const int tiles_per_frame = (max_voxels + TILE_M - 1) / TILE_M;
     uint32_t a_it = 0, b_it = 0, st_it = 0;   // ring positions; every role advances them identically
+    uint32_t full_phase = 0;                  // MMA issuers: bit s = parity of the next phase of their a_full[.][s]
 
     // Balanced split: the occupied 128-row tiles of all frames, laid end to end, are cut into gridDim.x
     // equal contiguous ranges (row counts are read from the device, so no host round trip); a CTA walks
@@ -339,58 +350,74 @@ conv_umma_kernel(const __half* __restrict__ in, __half* __restrict__ out, const 
 
         if (warp < 4) {
             // ---------------- gather producers ----------------
-            const int c = tid & 7;                 // 16-byte chunk of the 128-byte row
+            // Each of the four gather warps owns every fourth stage and issues all of its copies: while one
+            // warp sits in the latency of its barrier hand-offs the other three keep the copy pipe busy.
+            // Lane = (row group j, 16-byte chunk c): the eight lanes j*8..j*8+7 copy rows 32j..32j+31 of the
+            // stage, one row per step, chunk c of the row landing at chunk c ^ (row & 7) (128-byte swizzle).
+            const int c = lane & 7;                // 16-byte chunk of the 128-byte row
+            const int jrow = (lane >> 3) * 32;     // first row of this lane group
             const int koff = c / CPO;              // offset of the stage's group this chunk belongs to
             const int csub = (c % CPO) * 8;        // first channel of the chunk
             const __half* in_b = in + (size_t)b * max_voxels * CIN;
             uint32_t my_a = a_it;
 #ifdef SESSD_UMMA_TIMING
             const long long tg1 = clock64();
-            if (tid == 0 && blockIdx.x < 2) tacc[9] += (unsigned long long)(tg1 - tg0);   // group set-up
+            if (tid == 0 && blockIdx.x < 1) tacc[9] += (unsigned long long)(tg1 - tg0);   // group set-up
 #endif
             bool ok = true;
             int g = -1, t = 0;
             uint32_t rem = 0;
             while (ok && next_item<KG>(m, nstages, g, rem, t)) {
+                if ((my_a % GATHER_WARPS) != (uint32_t)warp) {   // another gather warp's stage
+                    ++my_a;
+                    continue;
+                }
                 const uint32_t s = my_a % A_STAGES, si = my_a % IDX_STAGES;
-                // row indices of this stage, fetched ahead of time by the index warp
 #ifdef SESSD_UMMA_TIMING
                 long long tq0 = clock64();
 #endif
-                ok = mbar_wait(smem_u32(&ctl->i_full[si]), (my_a / IDX_STAGES) & 1u, abort_flag);
+                // row indices of this stage, fetched ahead of time by the index warp
+                ok = mbar_wait(smem_u32(&ctl->i_full[si]), (my_a / IDX_STAGES) & 1u, abort_flag, 1 | (int)(my_a << 4));
                 if (!ok) break;
 #ifdef SESSD_UMMA_TIMING
                 long long tq1 = clock64();
+                long long tq2 = tq1;
 #endif
-                const int k = g * KG + koff;
-                int idx[TILE_M / 16];
-#pragma unroll
-                for (int p = 0; p < TILE_M / 16; ++p) {
-                    const int r = (tid >> 3) + 16 * p;
-                    const int v = s_idx[si * IDX_WORDS + koff * TILE_M + r];
-                    idx[p] = (k < kvol && row0 + t * TILE_M + r < n) ? v : -1;
-                }
-                mbar_arrive(smem_u32(&ctl->i_empty[si]));
-#ifdef SESSD_UMMA_TIMING
-                long long tq2 = clock64();
-#endif
-                ok = mbar_wait(smem_u32(&ctl->a_empty[s]), ((my_a / A_STAGES) & 1u) ^ 1u, abort_flag);
+                ok = mbar_wait(smem_u32(&ctl->a_empty[s]), ((my_a / A_STAGES) & 1u) ^ 1u, abort_flag, 2 | (int)(my_a << 4));
                 if (!ok) break;
 #ifdef SESSD_UMMA_TIMING
                 long long tq3 = clock64();
-#endif
-                const uint32_t a_base = smem_u32(sA + s * A_BYTES);
-#pragma unroll
-                for (int p = 0; p < TILE_M / 16; ++p) {
-                    const int r = (tid >> 3) + 16 * p;
-                    const __half* src = in_b + (size_t)(idx[p] < 0 ? 0 : idx[p]) * CIN + csub;
-                    cp_async_16(a_base + r * ROW_BYTES + ((c ^ (r & 7)) << 4), src, idx[p] < 0 ? 0u : 16u);
+                if (tid == 0 && blockIdx.x < 1 && my_a >= (uint32_t)A_STAGES) {
+                    tacc[16] += (unsigned long long)(tq3 - ctl->t_commit[s]);   // commit issued -> stage seen free
+                    tacc[17] += 1;
+                    if (tq3 - tq2 < 100) tacc[18] += 1;                         // free already when asked
                 }
-                cp_async_arrive_noinc(smem_u32(&ctl->a_full[s]));   // publishes the stage when the copies land
+#endif
+                const bool k_ok = g * KG + koff < kvol;
+                const int rows_left = n - (row0 + t * TILE_M + jrow);   // rows of this lane group inside the frame
+                const int32_t* ip = &s_idx[si * IDX_WORDS + koff * TILE_M + jrow];
+                const uint32_t a_base = smem_u32(sA + s * A_BYTES) + jrow * ROW_BYTES;
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    const int4 v0 = *reinterpret_cast<const int4*>(ip + 8 * q);
+                    const int4 v1 = *reinterpret_cast<const int4*>(ip + 8 * q + 4);
+                    const int vv[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
+#pragma unroll
+                    for (int u = 0; u < 8; ++u) {
+                        const int p = 8 * q + u;
+                        const int id = (k_ok && p < rows_left) ? vv[u] : -1;
+                        const __half* src = in_b + (size_t)(id < 0 ? 0 : id) * CIN + csub;
+                        cp_async_16(a_base + p * ROW_BYTES + ((c ^ u) << 4), src, id < 0 ? 0u : 16u);
+                    }
+                }
+                mbar_arrive(smem_u32(&ctl->i_empty[si]));           // the index block has been read
+                // publishes the stage, when the copies land, to the issuer that owns row tile t
+                cp_async_arrive_noinc(smem_u32(&ctl->a_full[t & 1][s]));
                 ++my_a;
 #ifdef SESSD_UMMA_TIMING
-                if (tid == 0 && blockIdx.x < 2) {
+                if (tid == 0 && blockIdx.x < 1) {
                     long long tq5 = clock64();
+                    ctl->t_issue[s] = tq5;
                     tacc[0] += (unsigned long long)(tq1 - tq0);  // wait index block
                     tacc[1] += (unsigned long long)(tq3 - tq2);  // wait free A stage
                     tacc[3] += (unsigned long long)(tq5 - tq0);  // whole iteration
@@ -398,17 +425,17 @@ conv_umma_kernel(const __half* __restrict__ in, __half* __restrict__ out, const 
                 }
 #endif
             }
-
 #ifdef SESSD_UMMA_TIMING
-            if (tid == 0 && blockIdx.x < 2) tacc[14] += (unsigned long long)(clock64() - tg1);   // whole gather loop of the group
+            if (tid == 0 && blockIdx.x < 1) tacc[14] += (unsigned long long)(clock64() - tg1);   // whole gather loop of the group
 #endif
+
             // ---------------- epilogue ----------------
 #ifdef SESSD_UMMA_TIMING
             long long te0 = clock64();
 #endif
             bool got = true;
             if (any) {
-                got = ok && mbar_wait(smem_u32(&ctl->acc_full), st_it & 1u, abort_flag);
+                got = ok && mbar_wait(smem_u32(&ctl->acc_full), st_it & 1u, abort_flag, 3 | (int)(st_it << 4));
                 got = __all_sync(0xFFFFFFFFu, got);
                 if (got) tc_fence_after();
             }
@@ -482,7 +509,7 @@ conv_umma_kernel(const __half* __restrict__ in, __half* __restrict__ out, const 
                 mbar_arrive(smem_u32(&ctl->acc_empty));   // the accumulators may be overwritten
             }
 #ifdef SESSD_UMMA_TIMING
-            if (tid == 0 && blockIdx.x < 2) {
+            if (tid == 0 && blockIdx.x < 1) {
                 tacc[5] += (unsigned long long)(te1 - te0);          // wait for the accumulators
                 tacc[6] += (unsigned long long)(clock64() - te1);    // epilogue proper
                 tacc[7] += 1;
@@ -497,7 +524,7 @@ conv_umma_kernel(const __half* __restrict__ in, __half* __restrict__ out, const 
                 const int parity = warp == 4 ? 0 : 1;
                 uint32_t my_a = a_it, my_b = b_it;
                 bool ok = true;
-                if (st_it > 0) ok = mbar_wait(smem_u32(&ctl->acc_empty), (st_it - 1u) & 1u, abort_flag);
+                if (st_it > 0) ok = mbar_wait(smem_u32(&ctl->acc_empty), (st_it - 1u) & 1u, abort_flag, 4 | (int)(st_it << 4));
                 if (ok) tc_fence_after();
                 uint32_t started = 0;
                 for (int g = 0; g < nstages && ok; ++g) {
@@ -511,9 +538,9 @@ conv_umma_kernel(const __half* __restrict__ in, __half* __restrict__ out, const 
 #ifdef SESSD_UMMA_TIMING
                     const long long tb0 = clock64();
 #endif
-                    ok = mbar_wait(smem_u32(&ctl->b_full[sb]), (my_b / B_STAGES) & 1u, abort_flag);
+                    ok = mbar_wait(smem_u32(&ctl->b_full[sb]), (my_b / B_STAGES) & 1u, abort_flag, 5 | (int)(my_b << 4));
 #ifdef SESSD_UMMA_TIMING
-                    if (warp == 4 && blockIdx.x < 2) {
+                    if (warp == 4 && blockIdx.x < 1) {
                         tacc[11] += (unsigned long long)(clock64() - tb0);
                     }
 #endif
@@ -531,11 +558,16 @@ conv_umma_kernel(const __half* __restrict__ in, __half* __restrict__ out, const 
 #ifdef SESSD_UMMA_TIMING
                             const long long tm0 = clock64();
 #endif
-                            ok = mbar_wait(smem_u32(&ctl->a_full[sa]), (pos / A_STAGES) & 1u, abort_flag);
+                            ok = mbar_wait(smem_u32(&ctl->a_full[parity][sa]), (full_phase >> sa) & 1u, abort_flag,
+                                           6 | (int)(pos << 4));
+                            full_phase ^= 1u << sa;   // this issuer's next use of the slot is the next phase
                             if (!ok) break;
 #ifdef SESSD_UMMA_TIMING
-                            if (warp == 4 && blockIdx.x < 2) {   // cycles this issuer waited for gathered rows
-                                tacc[2] += (unsigned long long)(clock64() - tm0);
+                            if (warp == 4 && blockIdx.x < 1) {   // cycles this issuer waited for gathered rows
+                                const long long tm1 = clock64();
+                                tacc[2] += (unsigned long long)(tm1 - tm0);
+                                tacc[19] += (unsigned long long)(tm1 - ctl->t_issue[sa]);   // gathers issued -> seen landed
+                                if (tm1 - tm0 < 100) tacc[20] += 1;                          // landed already when asked
                             }
 #endif
                             fence_proxy_async();   // the gathered rows were written through the generic proxy
@@ -549,7 +581,8 @@ conv_umma_kernel(const __half* __restrict__ in, __half* __restrict__ out, const 
                             started |= 1u << t;
                             umma_commit(smem_u32(&ctl->a_empty[sa]));   // frees the A stage once these MMAs have read it
 #ifdef SESSD_UMMA_TIMING
-                            if (warp == 4 && blockIdx.x < 2) {
+                            if (blockIdx.x < 1) ctl->t_commit[sa] = clock64();
+                            if (warp == 4 && blockIdx.x < 1) {
                                 tacc[10] += (unsigned long long)(clock64() - tm0);   // wait + issue + commit of one stage
                                 tacc[12] += 1;
                             }
@@ -581,7 +614,7 @@ conv_umma_kernel(const __half* __restrict__ in, __half* __restrict__ out, const 
             uint32_t rem = 0;
             while (ok && next_item<KG>(m, nstages, g, rem, t)) {
                 const uint32_t si = my_i % IDX_STAGES;
-                ok = mbar_wait<true>(smem_u32(&ctl->i_empty[si]), ((my_i / IDX_STAGES) & 1u) ^ 1u, abort_flag);
+                ok = mbar_wait<true>(smem_u32(&ctl->i_empty[si]), ((my_i / IDX_STAGES) & 1u) ^ 1u, abort_flag, 7 | (int)(my_i << 4));
                 if (!ok) break;
 #pragma unroll
                 for (int j = 0; j < KG; ++j) {
@@ -612,7 +645,7 @@ conv_umma_kernel(const __half* __restrict__ in, __half* __restrict__ out, const 
                     for (int t = 0; t < TILES; ++t) stage_any |= stage_active<KG>(m[t], g);
                     if (!stage_any) continue;
                     const uint32_t sb = my_b % B_STAGES;
-                    ok = mbar_wait<true>(smem_u32(&ctl->b_empty[sb]), ((my_b / B_STAGES) & 1u) ^ 1u, abort_flag);
+                    ok = mbar_wait<true>(smem_u32(&ctl->b_empty[sb]), ((my_b / B_STAGES) & 1u) ^ 1u, abort_flag, 8 | (int)(my_b << 4));
                     if (!ok) break;
                     const uint32_t bar = smem_u32(&ctl->b_full[sb]);
                     mbar_arrive_expect_tx(bar, B_BYTES);
@@ -630,15 +663,18 @@ conv_umma_kernel(const __half* __restrict__ in, __half* __restrict__ out, const 
     tc_fence_before();
     __syncthreads();
 #ifdef SESSD_UMMA_TIMING
-    if ((tid == 0 || tid == 128) && blockIdx.x < 2) {
-        unsigned long long* dbg = reinterpret_cast<unsigned long long*>(status) + 96 + blockIdx.x * 16;
+    if ((tid == 0 || tid == 128) && blockIdx.x < 1) {
+        unsigned long long* dbg = reinterpret_cast<unsigned long long*>(status) + 96;
         tacc[tid == 0 ? 8 : 13] = (unsigned long long)(clock64() - t_cta0);
 #pragma unroll
-        for (int i = 0; i < 16; ++i)
+        for (int i = 0; i < 32; ++i)
             if (tacc[i]) dbg[i] = tacc[i];
     }
 #endif
-    if (tid == 0 && *abort_flag) atomicOr(status, SESSD_STATUS_TIMEOUT);
+    if (tid == 0 && *abort_flag) {
+        atomicOr(status, SESSD_STATUS_TIMEOUT);
+        atomicCAS(status + 1, 0, ctl->abort_where);   // first report wins: which wait, at which ring position
+    }
     if (warp == 4) {
         tc_fence_after();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(TMEM_COLS) : "memory");
