@@ -185,6 +185,9 @@ struct SharedCtl {
     uint32_t tmem_base;
     int abort_flag;
     int abort_where;   // code of the first wait that ran out (role and ring position), for the status block
+    // per gather warp: the (stage << 2 | tile) pairs of the current group in ring order, so that a warp
+    // steps straight to the stages it owns
+    uint8_t stage_list[GATHER_WARPS][TILES * 32];
 #ifdef SESSD_UMMA_TIMING
     long long t_issue[A_STAGES_MAX];    // when the gathers of the stage were issued
     long long t_commit[A_STAGES_MAX];   // when the MMAs reading the stage were committed
@@ -230,7 +233,7 @@ __device__ __forceinline__ bool next_item(const uint32_t (&m)[TILES], int nstage
 // Register cap well below what two resident CTAs (the shared-memory limit) could take: the rest of the
 // register file is what lets blocks of other kernels (other streams) run beside them.
 template <int CIN, int COUT>
-__global__ void __maxnreg__(96)
+__global__ void __maxnreg__(104)
 conv_umma_kernel(const __half* __restrict__ in, __half* __restrict__ out, const int32_t* __restrict__ nbr,
                  const uint32_t* __restrict__ tile_mask, const int32_t* __restrict__ out_num,
                  const uint8_t* __restrict__ wtiles, const float* __restrict__ scale, const float* __restrict__ shift,
@@ -365,13 +368,28 @@ conv_umma_kernel(const __half* __restrict__ in, __half* __restrict__ out, const 
             if (tid == 0 && blockIdx.x < 1) tacc[9] += (unsigned long long)(tg1 - tg0);   // group set-up
 #endif
             bool ok = true;
-            int g = -1, t = 0;
-            uint32_t rem = 0;
-            while (ok && next_item<KG>(m, nstages, g, rem, t)) {
-                if ((my_a % GATHER_WARPS) != (uint32_t)warp) {   // another gather warp's stage
-                    ++my_a;
-                    continue;
+            // list of this group's (stage, tile) pairs: lane g holds stage g's tiles, a warp scan places them
+            uint8_t* list = ctl->stage_list[warp];
+            {
+                const uint32_t bits = lane < nstages ? active_tiles<KG>(m, lane) : 0u;
+                const int cnt_l = __popc(bits);
+                int incl = cnt_l;
+#pragma unroll
+                for (int d = 1; d < 32; d <<= 1) {
+                    const int v = __shfl_up_sync(0xFFFFFFFFu, incl, d);
+                    if (lane >= d) incl += v;
                 }
+                int at = incl - cnt_l;
+#pragma unroll
+                for (int tt = 0; tt < TILES; ++tt)
+                    if ((bits >> tt) & 1u) list[at++] = (uint8_t)((lane << 2) | tt);
+                __syncwarp();
+            }
+            const int first = (warp + GATHER_WARPS - (int)(a_it % GATHER_WARPS)) % GATHER_WARPS;
+            for (int e = first; e < n_a && ok; e += GATHER_WARPS) {
+                my_a = a_it + (uint32_t)e;
+                const int code = list[e];
+                const int g = code >> 2, t = code & 3;
                 const uint32_t s = my_a % A_STAGES, si = my_a % IDX_STAGES;
 #ifdef SESSD_UMMA_TIMING
                 long long tq0 = clock64();
@@ -413,7 +431,6 @@ conv_umma_kernel(const __half* __restrict__ in, __half* __restrict__ out, const 
                 mbar_arrive(smem_u32(&ctl->i_empty[si]));           // the index block has been read
                 // publishes the stage, when the copies land, to the issuer that owns row tile t
                 cp_async_arrive_noinc(smem_u32(&ctl->a_full[t & 1][s]));
-                ++my_a;
 #ifdef SESSD_UMMA_TIMING
                 if (tid == 0 && blockIdx.x < 1) {
                     long long tq5 = clock64();
