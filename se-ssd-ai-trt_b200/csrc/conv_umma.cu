@@ -13,11 +13,22 @@
 // accumulator with tcgen05.ld, applies the folded BatchNorm scale/shift and ReLU, and stores fp16
 // rows (and, for the last layer, scatters them into the dense BEV map).
 //
-// Warp roles (256 threads, two CTAs per SM): warps 0-3 gather A tiles with 16-byte cp.async and later run
-// the epilogue; warps 4 and 7 each issue the MMAs of every other row tile from one thread (warp 4 also
-// owns the tensor memory allocation); warp 5 streams the weight blocks; warp 6 copies the neighbour
-// indices of upcoming stages into a small ring ahead of the gathers. Stages hand over through mbarriers; every wait is bounded by a clock limit, after which the
-// CTA raises SESSD_STATUS_TIMEOUT, stops issuing work, frees its tensor memory and returns.
+// Warp roles (256 threads, two CTAs per SM, about 85 KB of shared memory and at most 104 registers per
+// thread, which leaves room for other streams' kernels on the same SM):
+//   warps 0-3  gather. The ring has one 16 KB slot per gather warp; ring position q lives in slot q % 4
+//              and is filled by warp q % 4 alone with 32 sixteen-byte cp.async per lane group. A warp's
+//              cp.async issue rate is bound by latency (about 46 cycles per instruction), so the warps
+//              work on four different stages at once rather than sharing one; the copies publish the
+//              stage themselves (cp.async mbarrier arrival). After the group's last stage the four warps
+//              run the epilogue (each can read its quarter of the tensor-memory lanes).
+//   warps 4, 7 issue the MMAs of the even / odd row tiles from one thread each (one issue costs the
+//              thread about 76 cycles, a commit about 156). Each issuer has its own "landed" barrier
+//              per slot: a parity wait is only safe for a waiter that has seen every earlier phase.
+//   warp 5     streams the weight blocks (cp.async.bulk), warp 6 prefetches the neighbour indices of
+//              upcoming stages into a small shared-memory ring.
+// A CTA walks an equal share of all occupied row tiles (row counts are read on the device). Every wait is
+// bounded by a clock limit, after which the CTA raises SESSD_STATUS_TIMEOUT (and reports which wait in
+// the status block), stops issuing work, frees its tensor memory and returns.
 #include <cstdlib>
 #include <string>
 #include <vector>
