@@ -712,12 +712,8 @@ conv_umma_kernel(const __half* __restrict__ in, __half* __restrict__ out, const 
 template <int CIN, int COUT>
 int launch_one(const ConvLaunch& c, cudaStream_t stream) {
     static const std::string name = "conv_umma<f16," + std::to_string(CIN) + "," + std::to_string(COUT) + ">";
-    // Tuning knob for experiments: SESSD_UMMA_CTAS_PER_SM=1 pads the request so that one CTA fits per SM.
-    static const int ctas_per_sm = [] {
-        const char* e = std::getenv("SESSD_UMMA_CTAS_PER_SM");
-        return (e && e[0] == '1') ? 1 : 2;
-    }();
-    const int smem = ctas_per_sm == 1 ? 120 * 1024 : umma_smem_bytes<CIN, COUT>();
+    constexpr int ctas_per_sm = 2;   // shared memory and registers are budgeted for two resident CTAs
+    const int smem = umma_smem_bytes<CIN, COUT>();
     static bool configured = false;
     if (!configured) {
         SESSD_CUDA(cudaFuncSetAttribute(conv_umma_kernel<CIN, COUT>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));

@@ -186,6 +186,36 @@ def test_round_trip_dense_to_sparse_at_sweep_size(gpu):
     bb.close()
 
 
+def test_sweep_size_batch_equals_single_frame_runs(gpu):
+    """Four 120k-point frames in one call: blocks of the tensor-core kernel then walk several row groups
+    across frame boundaries. Every frame's BEV map and final rows must be bit-identical to the frame run
+    alone, with a clean status word (a bounded wait that gives up shows there)."""
+    import torch
+
+    S = gpu.synth
+    w, sc, sh = gpu.random_weights()
+    bb = gpu.Backbone(200000, w, sc, sh, dtype=1)
+    frames = np.stack([S.sweep_frame(i) for i in range(4)])
+    pts = torch.from_numpy(frames).cuda()
+    sizes = torch.full((4,), frames.shape[1], dtype=torch.int32, device="cuda")
+    last = len(bb.layers) - 1
+    for rep in range(2):   # the second pass reuses the workspace the first one left behind
+        dense, ws = bb.run(pts, sizes)
+        torch.cuda.synchronize()
+        assert gpu.read_status(ws) == 0
+    feat, coors, num = [t.clone() for t in bb.layer_view(ws, 4, frames.shape[1], last)]
+    dense = dense.clone()
+    for b in (0, 3):
+        d1, ws1 = bb.run(pts[b:b + 1], sizes[b:b + 1])
+        torch.cuda.synchronize()
+        assert gpu.read_status(ws1) == 0
+        f1, c1, n1 = bb.layer_view(ws1, 1, frames.shape[1], last)
+        n = int(n1[0])
+        assert int(num[b]) == n and torch.equal(dense[b], d1[0])
+        assert torch.equal(feat[b, :n], f1[0, :n]) and torch.equal(coors[b, :n, 1:], c1[0, :n, 1:])
+    bb.close()
+
+
 @pytest.mark.parametrize("dtype", [0, 1])
 def test_sparse2dense_plugin_entry(gpu, oracle, dtype):
     import torch
