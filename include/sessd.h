@@ -313,6 +313,24 @@ int sessd_decode_filter_enqueue(const sessd_anchor_params* anchors, const sessd_
                                 const void* const* inputs, void* const* outputs, void* workspace,
                                 size_t workspace_bytes, void* stream);
 
+/* Rotated non-maximum suppression in the bird's-eye view: the host step after the score filter
+ * (nms_cpu and box_overlap, se-ssd-ai-trt.cpp:97-273, called at :1892 with NMS_THRESH = 0.01, params.h:373). */
+typedef struct sessd_nms_params {
+    int32_t max_box_num;   /* rows of the box table (<= 2048) */
+    float nms_thresh;      /* a box is dropped when an earlier kept box overlaps it with IoU >= nms_thresh */
+} sessd_nms_params;
+
+size_t sessd_rotated_nms_workspace_bytes(const sessd_nms_params* p, int batch);
+
+/* inputs = { box f32 [B][max_box][9] = (x, y, z, w, l, h, yaw, label, score), valid_line_num u32 [B] } (the first
+ * and last outputs of sessd_filter_boxes_enqueue), outputs = { kept f32 [B][max_box][9], kept_num u32 [B] }.
+ * Boxes are visited in descending score (equal scores: lower row first; the reference's std::sort leaves that
+ * open); kept boxes are written in that order, rows after kept_num[b] are zero. IoU by the reference's polygon
+ * rule in fp32. Replaces save_result + nms_cpu (se-ssd-ai-trt.cpp:1709-1721, :247-273) without the device-to-host
+ * copy of the box table. */
+int sessd_rotated_nms_enqueue(const sessd_nms_params* p, int batch, const void* const* inputs, void* const* outputs,
+                              void* workspace, size_t workspace_bytes, void* stream);
+
 /* Per-launch timing for benchmarks (takes the place of the reference's unused Tn::Profiler,
  * Utils.h:24-49). Between begin and end every kernel this library launches from the calling thread is
  * bracketed by CUDA events on its own stream. end synchronises the device, writes the kernel names

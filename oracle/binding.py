@@ -194,6 +194,24 @@ def filter_boxes(boxes, cls, iou, dirs, dir_num, max_box, threshold, dir_offset)
     return ob, oc, oi, od, int(valid[0]), int(passed)
 
 
+def rotated_nms(boxes, thresh):
+    """Greedy rotated NMS of [n, 9] boxes; returns (kept [count, 9], order [count] input rows)."""
+    boxes = np.ascontiguousarray(boxes, np.float32)
+    n = boxes.shape[0]
+    kept = np.zeros((max(n, 1), 9), np.float32)
+    order = np.zeros(max(n, 1), np.int32)
+    lib().oracle_rotated_nms.restype = C.c_int
+    cnt = lib().oracle_rotated_nms(_ptr(boxes, C.c_float), C.c_int(n), C.c_float(thresh), _ptr(kept, C.c_float),
+                                   _ptr(order, C.c_int32))
+    return kept[:cnt], order[:cnt]
+
+
+def bev_iou(a9, b9):
+    lib().oracle_bev_iou.restype = C.c_float
+    a9, b9 = np.ascontiguousarray(a9, np.float32), np.ascontiguousarray(b9, np.float32)
+    return float(lib().oracle_bev_iou(_ptr(a9, C.c_float), _ptr(b9, C.c_float)))
+
+
 def _vparams(point_range, voxel_size):
     xmin, ymin, zmin, xmax, ymax, zmax = point_range
     return np.asarray([xmin, xmax, ymin, ymax, zmin, zmax, *voxel_size, 0, 0, 0], np.float32)

@@ -495,6 +495,147 @@ int oracle_filter_boxes(const float* boxes, const float* cls, const float* iou, 
     return passed;
 }
 
+// ---------------------------------------------------------------------------------
+// Rotated non-maximum suppression in the bird's-eye view, the host step after the score filter.
+// Follows nms_cpu and box_overlap (se-ssd-ai-trt.cpp:97-273). A box is (x, y, z, w, l, h, yaw, label,
+// score); only x, y, w, l, yaw and the score take part. Overlap of two boxes = area of the polygon whose
+// vertices are the pairwise edge intersections plus the corners of either box that lie inside the other
+// (with a 1e-2 margin), sorted by angle around their mean and summed as a triangle fan. All arithmetic in
+// fp32 without contraction, trigonometry with the float functions.
+// ---------------------------------------------------------------------------------
+namespace {
+
+constexpr float kNmsEps = 1e-8f;      // ThresHold, se-ssd-ai-trt.cpp:66
+constexpr float kNmsMargin = 1e-2f;   // MARGIN, :103
+
+struct P2 {
+    float x, y;
+};
+
+inline float cross_at(P2 a, P2 b, P2 o) { return (a.x - o.x) * (b.y - o.y) - (b.x - o.x) * (a.y - o.y); }   // :98-100
+
+struct BevBox {
+    float x, y, w, l, yaw;
+    P2 corner[5];   // rotated corners, corner[4] == corner[0]
+};
+
+BevBox bev_box(const float* b9) {   // corner construction of box_overlap, :159-196
+    BevBox b;
+    b.x = b9[0], b.y = b9[1], b.w = b9[3], b.l = b9[4], b.yaw = b9[6];
+    const float hx = b.w / 2, hy = b.l / 2;
+    const float cs = std::cos(b.yaw), sn = std::sin(b.yaw);
+    const P2 local[4] = {{b.x - hx, b.y - hy}, {b.x + hx, b.y - hy}, {b.x + hx, b.y + hy}, {b.x - hx, b.y + hy}};
+    for (int k = 0; k < 4; ++k) {   // rotate_around_center, :150-155
+        const float dx = local[k].x - b.x, dy = local[k].y - b.y;
+        b.corner[k].x = dx * cs + dy * (-sn) + b.x;
+        b.corner[k].y = dx * sn + dy * cs + b.y;
+    }
+    b.corner[4] = b.corner[0];
+    return b;
+}
+
+bool inside_with_margin(const BevBox& b, P2 p) {   // check_box2d, :102-112
+    const float cs = std::cos(-b.yaw), sn = std::sin(-b.yaw);
+    const float rx = (p.x - b.x) * cs + (p.y - b.y) * (-sn);
+    const float ry = (p.x - b.x) * sn + (p.y - b.y) * cs;
+    return std::fabs(rx) < b.w / 2 + kNmsMargin && std::fabs(ry) < b.l / 2 + kNmsMargin;
+}
+
+// Intersection of segments p0-p1 and q0-q1 (:114-148): bounding boxes must meet, the end points of each
+// segment must lie strictly on opposite sides of the other, then the point follows from two cross products
+// (or from the line equations when those nearly coincide).
+bool segments_meet(P2 p1, P2 p0, P2 q1, P2 q0, P2* out) {
+    const bool boxes_meet = std::min(p0.x, p1.x) <= std::max(q0.x, q1.x) && std::min(q0.x, q1.x) <= std::max(p0.x, p1.x) &&
+                            std::min(p0.y, p1.y) <= std::max(q0.y, q1.y) && std::min(q0.y, q1.y) <= std::max(p0.y, p1.y);
+    if (!boxes_meet) return false;
+    const float s1 = cross_at(q0, p1, p0), s2 = cross_at(p1, q1, p0);
+    const float s3 = cross_at(p0, q1, q0), s4 = cross_at(q1, p1, q0);
+    if (!(s1 * s2 > 0 && s3 * s4 > 0)) return false;
+    const float s5 = cross_at(q1, p1, p0);
+    if (std::fabs(s5 - s1) > kNmsEps) {
+        out->x = (s5 * q0.x - s1 * q1.x) / (s5 - s1);
+        out->y = (s5 * q0.y - s1 * q1.y) / (s5 - s1);
+    } else {
+        const float a0 = p0.y - p1.y, b0 = p1.x - p0.x, c0 = p0.x * p1.y - p1.x * p0.y;
+        const float a1 = q0.y - q1.y, b1 = q1.x - q0.x, c1 = q0.x * q1.y - q1.x * q0.y;
+        const float det = a0 * b1 - a1 * b0;
+        out->x = (b0 * c1 - b1 * c0) / det;
+        out->y = (a1 * c0 - a0 * c1) / det;
+    }
+    return true;
+}
+
+float bev_overlap(const BevBox& a, const BevBox& b) {   // box_overlap, :157-245
+    P2 pts[16];
+    P2 mean = {0.f, 0.f};
+    int cnt = 0;
+    for (int i = 0; i < 4; ++i)
+        for (int j = 0; j < 4; ++j)
+            if (segments_meet(a.corner[i + 1], a.corner[i], b.corner[j + 1], b.corner[j], &pts[cnt])) {
+                mean.x += pts[cnt].x, mean.y += pts[cnt].y;
+                ++cnt;
+            }
+    for (int k = 0; k < 4; ++k) {
+        if (inside_with_margin(a, b.corner[k])) {
+            mean.x += b.corner[k].x, mean.y += b.corner[k].y;
+            pts[cnt++] = b.corner[k];
+        }
+        if (inside_with_margin(b, a.corner[k])) {
+            mean.x += a.corner[k].x, mean.y += a.corner[k].y;
+            pts[cnt++] = a.corner[k];
+        }
+    }
+    mean.x /= cnt, mean.y /= cnt;   // 0/0 when nothing was found; the loops below then do nothing
+    for (int j = 0; j < cnt - 1; ++j)   // bubble sort by angle around the mean, :222-233
+        for (int i = 0; i < cnt - j - 1; ++i)
+            if (std::atan2(pts[i].y - mean.y, pts[i].x - mean.x) > std::atan2(pts[i + 1].y - mean.y, pts[i + 1].x - mean.x))
+                std::swap(pts[i], pts[i + 1]);
+    float area = 0.f;
+    for (int k = 0; k < cnt - 1; ++k) {
+        const float ax = pts[k].x - pts[0].x, ay = pts[k].y - pts[0].y;
+        const float bx = pts[k + 1].x - pts[0].x, by = pts[k + 1].y - pts[0].y;
+        area += ax * by - ay * bx;
+    }
+    return std::fabs(area) / 2.0f;
+}
+
+float bev_iou(const float* a9, const BevBox& a, const float* b9, const BevBox& b) {   // nms_cpu, :262-265
+    const float sa = a9[3] * a9[4], sb = b9[3] * b9[4];
+    const float ov = bev_overlap(a, b);
+    return ov / std::fmax(sa + sb - ov, kNmsEps);
+}
+
+}  // namespace
+
+// boxes: [n][9]. Boxes are taken in descending score (column 8); the reference's std::sort leaves the order
+// of equal scores open, here the lower input row goes first. A box is kept unless an earlier kept box
+// overlaps it with IoU >= thresh. kept [n][9] receives the kept boxes in that order (rows after the count
+// are zero); returns the count. order (optional, [n]) receives the input row of every kept box.
+int oracle_rotated_nms(const float* boxes, int n, float thresh, float* kept, int32_t* order) {
+    std::vector<int> idx(n);
+    for (int i = 0; i < n; ++i) idx[i] = i;
+    std::stable_sort(idx.begin(), idx.end(), [&](int a, int b) { return boxes[a * 9 + 8] > boxes[b * 9 + 8]; });
+    std::vector<BevBox> bev(n);
+    for (int i = 0; i < n; ++i) bev[i] = bev_box(boxes + (size_t)idx[i] * 9);
+    std::vector<char> dead(n, 0);
+    std::memset(kept, 0, sizeof(float) * (size_t)n * 9);
+    int count = 0;
+    for (int i = 0; i < n; ++i) {
+        if (dead[i]) continue;
+        std::memcpy(kept + (size_t)count * 9, boxes + (size_t)idx[i] * 9, sizeof(float) * 9);
+        if (order) order[count] = idx[i];
+        ++count;
+        for (int j = i + 1; j < n; ++j) {
+            if (dead[j]) continue;
+            if (bev_iou(boxes + (size_t)idx[i] * 9, bev[i], boxes + (size_t)idx[j] * 9, bev[j]) >= thresh) dead[j] = 1;
+        }
+    }
+    return count;
+}
+
+// IoU of two boxes by the same rule (for tests that need the margin of a decision).
+float oracle_bev_iou(const float* a9, const float* b9) { return bev_iou(a9, bev_box(a9), b9, bev_box(b9)); }
+
 void oracle_round_half(float* x, size_t n) {
     for (size_t i = 0; i < n; ++i) x[i] = to_half_and_back(x[i]);
 }

@@ -32,7 +32,7 @@ EXPORTS = (
     "sessd_pipeline_run_device", "sessd_pipeline_dense", "sessd_pipeline_workspace", "sessd_launch_count",
     "sessd_profile_begin", "sessd_profile_end", "sessd_read_status", "sessd_last_cuda_error", "sessd_version",
     "sessd_anchor_decode_enqueue", "sessd_filter_boxes_workspace_bytes", "sessd_filter_boxes_enqueue",
-    "sessd_decode_filter_enqueue",
+    "sessd_decode_filter_enqueue", "sessd_rotated_nms_workspace_bytes", "sessd_rotated_nms_enqueue",
 )
 
 
@@ -77,6 +77,10 @@ class FilterParams(C.Structure):
                 ("score_threshold", C.c_float), ("direction_offset", C.c_float)]
 
 
+class NmsParams(C.Structure):
+    _fields_ = [("max_box_num", C.c_int32), ("nms_thresh", C.c_float)]
+
+
 class S2DParams(C.Structure):
     _fields_ = [("feature_map_size_x", C.c_int32), ("feature_map_size_y", C.c_int32),
                 ("feature_map_size_z", C.c_int32), ("feature_map_channel", C.c_int32)]
@@ -93,7 +97,7 @@ def lib():
             raise SessdError(f"{LIB_PATH} is missing: run build() (needs nvcc); there is no CPU fallback")
         L = C.CDLL(LIB_PATH)
         for name in ("sessd_voxelize_workspace_bytes", "sessd_conv_workspace_bytes", "sessd_backbone_workspace_bytes",
-                     "sessd_filter_boxes_workspace_bytes"):
+                     "sessd_filter_boxes_workspace_bytes", "sessd_rotated_nms_workspace_bytes"):
             getattr(L, name).restype = C.c_size_t
         for name in ("sessd_voxelize_num_points", "sessd_pipeline_dense", "sessd_pipeline_workspace"):
             getattr(L, name).restype = C.c_void_p
@@ -340,6 +344,22 @@ def filter_boxes(boxes, cls, iou, dirs, params: FilterParams, anchors: AnchorPar
                "sessd_decode_filter_enqueue")
     out["status"] = read_status(ws)
     return out
+
+
+def rotated_nms(boxes, valid, nms_thresh=schedule.NMS_THRESH):
+    """Greedy rotated NMS (the reference's host nms_cpu) of [B, M, 9] boxes with valid[b] rows each.
+    Returns (kept [B, M, 9], kept_num [B])."""
+    torch = _torch()
+    B, M = boxes.shape[0], boxes.shape[1]
+    p = NmsParams(M, nms_thresh)
+    kept = torch.empty_like(boxes)
+    kept_num = torch.empty((B,), dtype=torch.int32, device=boxes.device)
+    nbytes = lib().sessd_rotated_nms_workspace_bytes(C.byref(p), B)
+    ws = torch.empty((max(nbytes, 1),), dtype=torch.uint8, device=boxes.device)
+    _check(lib().sessd_rotated_nms_enqueue(C.byref(p), B, _vp(boxes, valid), _vp(kept, kept_num),
+                                           C.c_void_p(ws.data_ptr()), C.c_size_t(nbytes), _stream()),
+           "sessd_rotated_nms_enqueue")
+    return kept, kept_num
 
 
 class Backbone:

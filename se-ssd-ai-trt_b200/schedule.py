@@ -28,6 +28,7 @@ CAR_SIZE = (3.9, 1.6, 1.56)         # length, width, height
 MAX_BOX_NUM = 500
 SCORE_THRESHOLD = 0.45
 DIRECTION_OFFSET = 0.0
+NMS_THRESH = 0.01                    # params.h:373
 
 
 @dataclass(frozen=True)

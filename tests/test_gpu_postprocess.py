@@ -101,3 +101,77 @@ def test_filter_rejects_bad_arguments(gpu):
         gpu.filter_boxes(x, x, x, x, fp)
     with pytest.raises(gpu.SessdError):   # the two parameter blocks disagree on the feature map
         gpu.filter_boxes(x, x, x, x, gpu.filter_params(), anchors=gpu.anchor_params(height=100))
+
+
+# ---- rotated NMS ---------------------------------------------------------------------------------------
+
+def _random_boxes(rs, n, spread):
+    """Car-sized boxes scattered over `spread` metres, with clusters so that suppression happens."""
+    centres = rs.uniform(0, spread, (max(n // 4, 1), 2))
+    pick = rs.randint(0, len(centres), n)
+    b = np.zeros((n, 9), np.float32)
+    b[:, 0:2] = centres[pick] + rs.randn(n, 2) * 0.6
+    b[:, 2] = rs.uniform(-1.5, -0.5, n)
+    b[:, 3] = rs.uniform(1.4, 1.9, n)
+    b[:, 4] = rs.uniform(3.4, 4.5, n)
+    b[:, 5] = rs.uniform(1.4, 1.7, n)
+    b[:, 6] = rs.uniform(-3.2, 3.2, n)
+    b[:, 8] = np.round(rs.uniform(0.05, 1.0, n), 2)      # two decimals: plenty of equal scores
+    return b
+
+
+def _clear_of_threshold(oracle, boxes, thresh, eps=1e-4):
+    """True when no pair's IoU lies within eps of the threshold (then a last-place difference of the
+    device's trigonometric functions cannot flip a decision)."""
+    n = len(boxes)
+    for i in range(n):
+        for j in range(i + 1, n):
+            if abs(boxes[i, 0] - boxes[j, 0]) + abs(boxes[i, 1] - boxes[j, 1]) < 12:
+                if abs(oracle.bev_iou(boxes[i], boxes[j]) - thresh) < eps:
+                    return False
+    return True
+
+
+@pytest.mark.parametrize("thresh", [0.01, 0.3])
+def test_rotated_nms_matches_oracle(gpu, oracle, thresh):
+    import torch
+
+    rs = np.random.RandomState(31)
+    M = 500
+    counts = [500, 137, 0, 64]
+    boxes = np.zeros((len(counts), M, 9), np.float32)
+    for b, n in enumerate(counts):
+        for attempt in range(20):
+            cand = _random_boxes(rs, n, 60.0)
+            if _clear_of_threshold(oracle, cand, thresh):
+                break
+        else:
+            pytest.fail("could not draw boxes clear of the threshold")
+        boxes[b, :n] = cand
+        boxes[b, n:] = 7.0    # rows past the count must be ignored
+    valid = np.array(counts, np.int32)
+    kept, kept_num = gpu.rotated_nms(torch.from_numpy(boxes).cuda(), torch.from_numpy(valid).cuda(), thresh)
+    kept, kept_num = kept.cpu().numpy(), kept_num.cpu().numpy()
+    for b, n in enumerate(counts):
+        want, order = oracle.rotated_nms(boxes[b, :n], thresh)
+        assert int(kept_num[b]) == len(want)
+        np.testing.assert_array_equal(kept[b, :len(want)], want)     # same boxes, same order, copied bit for bit
+        assert not kept[b, len(want):].any()
+        if n > 100:
+            assert 0 < len(want) < n                                    # the case does suppress something
+
+
+def test_rotated_nms_after_score_filter(gpu, oracle):
+    """Score filter -> NMS on the device, the reference's post-processing chain (se-ssd-ai-trt.cpp:1868-1892)."""
+    S = gpu.schedule
+    box, cls, iou, dr = _head_outputs(gpu, 9, 2, S.FEATURE_MAP_HEIGHT, S.FEATURE_MAP_WIDTH, 2, logit_mean=-4.5)
+    r = gpu.filter_boxes(*_to_gpu(box, cls, iou, dr), gpu.filter_params(), anchors=gpu.anchor_params())
+    kept, kept_num = gpu.rotated_nms(r["box"], r["valid"], S.NMS_THRESH)
+    for b in range(2):
+        n = int(r["valid"][b])
+        src = r["box"][b, :n].cpu().numpy()
+        if not _clear_of_threshold(oracle, src, S.NMS_THRESH, 1e-5):
+            pytest.skip("a pair sits on the threshold for this seed")
+        want, _ = oracle.rotated_nms(src, S.NMS_THRESH)
+        assert int(kept_num[b]) == len(want) and len(want) > 0
+        np.testing.assert_array_equal(kept[b, :len(want)].cpu().numpy(), want)

@@ -264,3 +264,58 @@ def test_filter_boxes_against_numpy(oracle):
     flip = ((best == 1) & (yaw < 0)) | ((best == 0) & (yaw > 0))
     np.testing.assert_array_equal(ob[:valid, 6], np.where(flip, yaw + np.float32(3.1415926), yaw).astype(np.float32))
     assert not ob[valid:].any() and not oc[valid:].any()
+
+
+# ---- rotated NMS -------------------------------------------------------------------------------
+
+def _box(x, y, w, l, yaw, score, z=0.0, h=1.5, label=0.0):
+    return np.array([x, y, z, w, l, h, yaw, label, score], np.float32)
+
+
+def test_bev_iou_hand_cases(oracle):
+    a = _box(0, 0, 2, 4, 0.0, 0.9)
+    assert abs(oracle.bev_iou(a, a) - 1.0) < 1e-5
+    assert oracle.bev_iou(a, _box(10, 0, 2, 4, 0.0, 0.5)) == 0.0                 # disjoint
+    # shifted by half the width: overlap 1 x 4 = 4, union 8 + 8 - 4
+    assert abs(oracle.bev_iou(a, _box(1, 0, 2, 4, 0.0, 0.5)) - 4.0 / 12.0) < 1e-5
+    # the same box turned by 90 degrees: the 2 x 2 centre square is shared
+    assert abs(oracle.bev_iou(a, _box(0, 0, 2, 4, np.pi / 2, 0.5)) - 4.0 / 12.0) < 1e-4
+    # a small box inside a large one: no edge crossings, only contained corners
+    assert abs(oracle.bev_iou(_box(0, 0, 10, 10, 0.3, 0.9), _box(1, 1, 2, 2, 1.0, 0.5)) - 4.0 / 100.0) < 1e-4
+
+
+def test_bev_iou_against_rasterised_area(oracle):
+    """Independent check: area of the intersection counted on a fine grid."""
+    rs = np.random.RandomState(21)
+    g = (np.arange(600) + 0.5) / 600 * 12 - 6
+    gx, gy = np.meshgrid(g, g)
+
+    def inside(b):
+        c, s = np.cos(-b[6]), np.sin(-b[6])
+        rx, ry = (gx - b[0]) * c - (gy - b[1]) * s, (gx - b[0]) * s + (gy - b[1]) * c
+        return (np.abs(rx) < b[3] / 2) & (np.abs(ry) < b[4] / 2)
+
+    for _ in range(40):
+        a = _box(rs.uniform(-1, 1), rs.uniform(-1, 1), rs.uniform(1, 3), rs.uniform(2, 5), rs.uniform(-3, 3), 0.5)
+        b = _box(rs.uniform(-1, 1), rs.uniform(-1, 1), rs.uniform(1, 3), rs.uniform(2, 5), rs.uniform(-3, 3), 0.5)
+        ia, ib = inside(a), inside(b)
+        inter, union = (ia & ib).sum(), (ia | ib).sum()
+        assert abs(oracle.bev_iou(a, b) - inter / union) < 2e-2
+
+
+def test_rotated_nms_order_and_suppression(oracle):
+    boxes = np.stack([
+        _box(0, 0, 2, 4, 0.0, 0.50),        # 0: suppressed by 2 (same place, lower score)
+        _box(20, 0, 2, 4, 0.3, 0.90),       # 1: best, kept
+        _box(0.2, 0, 2, 4, 0.0, 0.80),      # 2: kept
+        _box(20.1, 0.1, 2, 4, 0.3, 0.85),   # 3: suppressed by 1
+        _box(-20, 5, 2, 4, 1.0, 0.10),      # 4: far away, kept last
+        _box(40, 40, 2, 4, 0.0, 0.80),      # 5: same score as 2, later row: after 2
+    ])
+    kept, order = oracle.rotated_nms(boxes, 0.01)
+    assert order.tolist() == [1, 2, 5, 4]
+    np.testing.assert_array_equal(kept, boxes[[1, 2, 5, 4]])
+    # touching corners only: IoU far below the 0.01 threshold, both kept
+    two = np.stack([_box(0, 0, 2, 2, 0.0, 0.9), _box(1.99, 1.99, 2, 2, 0.0, 0.8)])
+    assert oracle.rotated_nms(two, 0.01)[1].tolist() == [0, 1]
+    assert oracle.rotated_nms(np.zeros((0, 9), np.float32), 0.01)[1].tolist() == []
