@@ -134,7 +134,9 @@ def peaks():
 
 
 def layer_costs(pkg, rows_in, rows_out, pairs, esize=2):
-    """Algorithmic bytes and flops per conv layer for one frame set ('Roofline arithmetic')."""
+    """Algorithmic bytes and flops per conv layer for one frame set: bytes = input rows x Cin + output rows x Cout
+    + the weights (all fp16) + 16 B of coordinates per input row (and per output row of a strided layer);
+    flops = 2 x rulebook pairs x Cin x Cout."""
     out = []
     for l, ni, no, p in zip(pkg.schedule.LAYERS, rows_in, rows_out, pairs):
         b = ni * l.cin * esize + no * l.cout * esize + l.kvol * l.cin * l.cout * esize + 16 * ni
