@@ -126,6 +126,15 @@ template <int N>
 __device__ __forceinline__ void cp_async_wait() {
     asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
 }
+// 16-byte copy that writes zeros instead when index < 0 (the source address is then not touched).
+__device__ __forceinline__ void cp_async_16_or_zero(uint32_t dst, const void* src, int index) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.lt.s32 p, %2, 0;\n\t"
+        "cp.async.cg.shared.global [%0], [%1], 16, p;\n\t}" ::"r"(dst),
+        "l"(src), "r"(index)
+        : "memory");
+}
 // Arrival on `bar` that fires when all cp.async copies this thread has issued so far have landed
 // (the barrier's expected count must include it).
 __device__ __forceinline__ void cp_async_arrive_noinc(uint32_t bar) {
@@ -426,17 +435,33 @@ conv_umma_kernel(const __half* __restrict__ in, __half* __restrict__ out, const 
                 const int rows_left = n - (row0 + t * TILE_M + jrow);   // rows of this lane group inside the frame
                 const int32_t* ip = &s_idx[si * IDX_WORDS + koff * TILE_M + jrow];
                 const uint32_t a_base = smem_u32(sA + s * A_BYTES) + jrow * ROW_BYTES;
+                // Every instruction of this loop is on the critical path of the stage (the gather warps are bound
+                // by their own instruction latency, not by the copies), so the common case - all offsets of the
+                // stage exist and the whole tile lies inside the frame - takes three instructions per row: a
+                // predicate from the sign of the index, the address, and a copy that writes zeros when the
+                // predicate says the neighbour is missing.
+                const bool plain = g * KG + KG <= kvol && row0 + (t + 1) * TILE_M <= n;   // uniform over the warp
+                const __half* lane_base = in_b + csub;
 #pragma unroll
                 for (int q = 0; q < 4; ++q) {
                     const int4 v0 = *reinterpret_cast<const int4*>(ip + 8 * q);
                     const int4 v1 = *reinterpret_cast<const int4*>(ip + 8 * q + 4);
                     const int vv[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
+                    if (plain) {
 #pragma unroll
-                    for (int u = 0; u < 8; ++u) {
-                        const int p = 8 * q + u;
-                        const int id = (k_ok && p < rows_left) ? vv[u] : -1;
-                        const __half* src = in_b + (size_t)(id < 0 ? 0 : id) * CIN + csub;
-                        cp_async_16(a_base + p * ROW_BYTES + ((c ^ u) << 4), src, id < 0 ? 0u : 16u);
+                        for (int u = 0; u < 8; ++u) {
+                            const int p = 8 * q + u;
+                            cp_async_16_or_zero(a_base + p * ROW_BYTES + ((c ^ u) << 4),
+                                                lane_base + (ptrdiff_t)vv[u] * CIN, vv[u]);
+                        }
+                    } else {
+#pragma unroll
+                        for (int u = 0; u < 8; ++u) {
+                            const int p = 8 * q + u;
+                            const int id = (k_ok && p < rows_left) ? vv[u] : -1;
+                            const __half* src = in_b + (size_t)(id < 0 ? 0 : id) * CIN + csub;
+                            cp_async_16(a_base + p * ROW_BYTES + ((c ^ u) << 4), src, id < 0 ? 0u : 16u);
+                        }
                     }
                 }
                 mbar_arrive(smem_u32(&ctl->i_empty[si]));           // the index block has been read
