@@ -442,26 +442,24 @@ conv_umma_kernel(const __half* __restrict__ in, __half* __restrict__ out, const 
                 // predicate says the neighbour is missing.
                 const bool plain = g * KG + KG <= kvol && row0 + (t + 1) * TILE_M <= n;   // uniform over the warp
                 const __half* lane_base = in_b + csub;
+                // all 32 indices first (the copies below are compiler barriers, a load could not move above them)
+                int vv[32];
 #pragma unroll
-                for (int q = 0; q < 4; ++q) {
-                    const int4 v0 = *reinterpret_cast<const int4*>(ip + 8 * q);
-                    const int4 v1 = *reinterpret_cast<const int4*>(ip + 8 * q + 4);
-                    const int vv[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
-                    if (plain) {
+                for (int q = 0; q < 8; ++q) {
+                    const int4 v = *reinterpret_cast<const int4*>(ip + 4 * q);
+                    vv[4 * q] = v.x, vv[4 * q + 1] = v.y, vv[4 * q + 2] = v.z, vv[4 * q + 3] = v.w;
+                }
+                if (plain) {
 #pragma unroll
-                        for (int u = 0; u < 8; ++u) {
-                            const int p = 8 * q + u;
-                            cp_async_16_or_zero(a_base + p * ROW_BYTES + ((c ^ u) << 4),
-                                                lane_base + (ptrdiff_t)vv[u] * CIN, vv[u]);
-                        }
-                    } else {
+                    for (int p = 0; p < 32; ++p)
+                        cp_async_16_or_zero(a_base + p * ROW_BYTES + ((c ^ (p & 7)) << 4),
+                                            lane_base + (ptrdiff_t)vv[p] * CIN, vv[p]);
+                } else {
 #pragma unroll
-                        for (int u = 0; u < 8; ++u) {
-                            const int p = 8 * q + u;
-                            const int id = (k_ok && p < rows_left) ? vv[u] : -1;
-                            const __half* src = in_b + (size_t)(id < 0 ? 0 : id) * CIN + csub;
-                            cp_async_16(a_base + p * ROW_BYTES + ((c ^ u) << 4), src, id < 0 ? 0u : 16u);
-                        }
+                    for (int p = 0; p < 32; ++p) {
+                        const int id = (k_ok && p < rows_left) ? vv[p] : -1;
+                        const __half* src = in_b + (size_t)(id < 0 ? 0 : id) * CIN + csub;
+                        cp_async_16(a_base + p * ROW_BYTES + ((c ^ (p & 7)) << 4), src, id < 0 ? 0u : 16u);
                     }
                 }
                 mbar_arrive(smem_u32(&ctl->i_empty[si]));           // the index block has been read
