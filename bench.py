@@ -96,9 +96,11 @@ class ClockSampler:
 
     def _read(self):
         for line in self.proc.stdout:
-            self.lines.append(line.strip())
+            self.lines.append((time.perf_counter(), line.strip()))
 
-    def stop(self):
+    def stop(self, t_begin=None, t_end=None):
+        """Summary of the samples taken in [t_begin, t_end] (the timed region; nvidia-smi needs a second to
+        start, so the sampler is started before the warm-up passes)."""
         if not self.proc:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
         self.proc.terminate()
@@ -107,7 +109,8 @@ class ClockSampler:
         except subprocess.TimeoutExpired:
             self.proc.kill()
         sm, mx, reasons = [], [], set()
-        for ln in self.lines:
+        lines = [ln for ts, ln in self.lines if t_begin is None or t_begin <= ts <= t_end + 0.25]
+        for ln in lines:
             p = [t.strip() for t in ln.split(",")]
             if len(p) < 8:
                 continue
@@ -253,15 +256,16 @@ def main():
             dist.barrier()
         torch.cuda.synchronize()
 
+    sampler = ClockSampler(local)
+    sampler.start()
     for i in range(max(args.warmup, 3)):
         pipe.run_device(d_pts, d_sizes)
         if i == 0:   # fail fast if a kernel reported a bounded-wait timeout or a capacity problem
             bad = pipe.status_bits()
             if bad & ~pkg.STATUS_VOXEL_OVERFLOW:
+                sampler.stop()
                 raise SystemExit(f"device status {bad:#x} after the first pass: aborting the benchmark")
     barrier()
-    sampler = ClockSampler(local)
-    sampler.start()
     launches0 = pkg.launch_count()
     t0 = time.perf_counter()
     dev_ms = 0.0
@@ -270,7 +274,7 @@ def main():
     barrier()
     wall_ms = (time.perf_counter() - t0) * 1e3
     launches = pkg.launch_count() - launches0
-    clocks = sampler.stop()
+    clocks = sampler.stop(t0, time.perf_counter())
 
     # end to end through the host-buffer entry point: H2D of the points and D2H of counts + status inside
     for _ in range(2):
