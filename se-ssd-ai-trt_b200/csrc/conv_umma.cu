@@ -29,6 +29,7 @@
 // A CTA walks an equal share of all occupied row tiles (row counts are read on the device). Every wait is
 // bounded by a clock limit, after which the CTA raises SESSD_STATUS_TIMEOUT (and reports which wait in
 // the status block), stops issuing work, frees its tensor memory and returns.
+#include <atomic>
 #include <cstdlib>
 #include <string>
 #include <vector>
@@ -737,10 +738,15 @@ int launch_one(const ConvLaunch& c, cudaStream_t stream) {
     static const std::string name = "conv_umma<f16," + std::to_string(CIN) + "," + std::to_string(COUT) + ">";
     constexpr int ctas_per_sm = 2;   // shared memory and registers are budgeted for two resident CTAs
     const int smem = umma_smem_bytes<CIN, COUT>();
-    static bool configured = false;
-    if (!configured) {
+    // the attribute belongs to the device's context: set it once per device (repeating it is harmless, so a
+    // race between two host threads only costs a second call)
+    static std::atomic<uint64_t> configured{0};
+    int dev = 0;
+    SESSD_CUDA(cudaGetDevice(&dev));
+    const uint64_t bit = 1ull << (dev & 63);
+    if (!(configured.load(std::memory_order_acquire) & bit)) {
         SESSD_CUDA(cudaFuncSetAttribute(conv_umma_kernel<CIN, COUT>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-        configured = true;
+        configured.fetch_or(bit, std::memory_order_release);
     }
     SESSD_LAUNCH_NAMED(name.c_str(), (conv_umma_kernel<CIN, COUT>), persistent_grid(ctas_per_sm), UMMA_THREADS, smem, stream,
                        static_cast<const __half*>(c.in), static_cast<__half*>(c.out), c.nbr, c.tile_mask, c.out_num,
