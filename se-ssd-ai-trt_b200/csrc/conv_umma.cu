@@ -323,6 +323,7 @@ conv_umma_kernel(const __half* __restrict__ in, __half* __restrict__ out, const 
     const int tiles_per_frame = (max_voxels + TILE_M - 1) / TILE_M;
     uint32_t a_it = 0, b_it = 0, st_it = 0;   // ring positions; every role advances them identically
     uint32_t full_phase = 0;                  // MMA issuers: bit s = parity of the next phase of their a_full[.][s]
+    uint32_t b_issued = 0;                    // weight streamer: blocks whose bulk copy has been started
 
     // Balanced split: the occupied 128-row tiles of all frames, laid end to end, are cut into gridDim.x
     // equal contiguous ranges (row counts are read from the device, so no host round trip); a CTA walks
@@ -703,6 +704,7 @@ conv_umma_kernel(const __half* __restrict__ in, __half* __restrict__ out, const 
                     mbar_arrive_expect_tx(bar, B_BYTES);
                     bulk_load(smem_u32(sB + sb * B_BYTES), wtiles + (size_t)g * B_BYTES, B_BYTES, bar);
                     ++my_b;
+                    b_issued = my_b;
                 }
             }
             __syncwarp();
@@ -723,6 +725,20 @@ conv_umma_kernel(const __half* __restrict__ in, __half* __restrict__ out, const 
             if (tacc[i]) dbg[i] = tacc[i];
     }
 #endif
+    if (*abort_flag) {
+        // An aborting CTA must not return while its own copies are still writing shared memory: the gather
+        // warps wait for their cp.async copies, the weight streamer (bounded) for its last bulk copies.
+        if (warp < GATHER_WARPS) asm volatile("cp.async.wait_all;" ::: "memory");
+        if (warp == 5 && lane == 0) {
+            const uint32_t first = b_issued > (uint32_t)B_STAGES ? b_issued - B_STAGES : 0u;
+            for (uint32_t j = first; j < b_issued; ++j) {
+                const uint32_t bar = smem_u32(&ctl->b_full[j % B_STAGES]);
+                const long long t0 = clock64();
+                while (!mbar_try_wait(bar, (j / B_STAGES) & 1u) && clock64() - t0 < WAIT_LIMIT_CYCLES) {}
+            }
+        }
+    }
+    __syncthreads();
     if (tid == 0 && *abort_flag) {
         atomicOr(status, SESSD_STATUS_TIMEOUT);
         atomicCAS(status + 1, 0, ctl->abort_where);   // first report wins: which wait, at which ring position
