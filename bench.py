@@ -365,7 +365,12 @@ def main():
                     group_profile=dict(frames=B, total_ms=group_ms,
                                        gflop_per_frame=total_flops / B / 1e9,
                                        kernels={n: dict(launches=v[0], ms=round(v[1], 4)) for n, v in
-                                                sorted(per_kernel.items(), key=lambda kv: -kv[1][1])}))
+                                                sorted(per_kernel.items(), key=lambda kv: -kv[1][1])},
+                                       # per conv layer: launch time, algorithmic GB/s and TFLOP/s (pair flops)
+                                       layers=[dict(name=c["name"], kernel=k, ms=round(ms, 4),
+                                                    gbps=round(c["bytes"] / (ms / 1e3) / 1e9, 1),
+                                                    tflops=round(c["flops"] / (ms / 1e3) / 1e12, 2))
+                                               for c, k, ms in zip(costs, conv_launch_order, conv_ms)]))
         if world == 1 and not args.no_cpu_baseline:
             info, _, _ = cpu_baseline(pkg, wl, frames, sizes)
             line["cpu_baseline"] = info
