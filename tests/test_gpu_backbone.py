@@ -216,6 +216,44 @@ def test_sweep_size_batch_equals_single_frame_runs(gpu):
     bb.close()
 
 
+def test_backbone_enqueue_can_be_captured_in_a_cuda_graph(gpu):
+    """The enqueue call allocates nothing, synchronises nothing and reads its row counts on the device, so a
+    host can capture it once and replay it (the first call, which configures the kernels, stays outside)."""
+    import torch
+
+    case = mk.small_case(gpu)
+    bb = gpu.Backbone(case["max_voxels"], case["weights"], case["scale"], case["shift"], dtype=1,
+                      layers=case["layers"], point_range=case["range"], voxel_size=case["voxel"])
+    P = len(case["points"])
+    pts = torch.zeros((1, P, 4), device="cuda")
+    sizes = torch.zeros((1,), dtype=torch.int32, device="cuda")
+    pts[0] = torch.from_numpy(case["points"]).cuda()
+    sizes[0] = P
+    want, ws = bb.run(pts, sizes)          # plain call; also the warm-up
+    want = want.clone()
+    dense = torch.empty_like(want)
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.stream(side):
+        with torch.cuda.graph(graph, stream=side):
+            bb.run(pts, sizes, workspace=ws, dense=dense)
+    for half in (False, True):             # replay on new inputs written into the captured buffers
+        if half:
+            sizes[0] = P // 2
+        dense.fill_(7)
+        graph.replay()
+        torch.cuda.synchronize()
+        assert gpu.read_status(ws) == 0
+        if not half:
+            assert torch.equal(dense, want)
+        else:
+            ref, _ = bb.run(pts, sizes)
+            torch.cuda.synchronize()
+            assert torch.equal(dense, ref) and not torch.equal(dense, want)
+    bb.close()
+
+
 @pytest.mark.parametrize("dtype", [0, 1])
 def test_sparse2dense_plugin_entry(gpu, oracle, dtype):
     import torch
