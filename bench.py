@@ -213,6 +213,12 @@ def main():
     args = ap.parse_args()
     args.warmup = max(args.warmup, 0)
 
+    if args.gpus > 1 and "RANK" not in os.environ:
+        # started by hand without torchrun: start one rank per GPU of this node the way the launcher would
+        port = str(29500 + os.getpid() % 1000)
+        os.execv(sys.executable, [sys.executable, "-m", "torch.distributed.run", "--nnodes=1",
+                                  f"--nproc-per-node={args.gpus}", "--master-addr", "127.0.0.1", "--master-port", port,
+                                  os.path.abspath(__file__), *sys.argv[1:]])
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
