@@ -110,6 +110,10 @@ class ClockSampler:
             self.proc.kill()
         sm, mx, reasons = [], [], set()
         lines = [ln for ts, ln in self.lines if t_begin is None or t_begin <= ts <= t_end + 0.25]
+        if not lines and self.lines and t_begin is not None:
+            # a timed region shorter than the sampling period: take the two samples nearest to it
+            mid = 0.5 * (t_begin + t_end)
+            lines = [ln for _, ln in sorted(self.lines, key=lambda x: abs(x[0] - mid))[:2]]
         for ln in lines:
             p = [t.strip() for t in ln.split(",")]
             if len(p) < 8:
