@@ -213,6 +213,7 @@ def main():
     ap.add_argument("--frames", type=int, default=0, help="frames per GPU per step (default: the workload's)")
     ap.add_argument("--batch", type=int, default=0, help="frames per launch group")
     ap.add_argument("--streams", type=int, default=4, help="launch groups in flight per GPU")
+    ap.add_argument("--graphs", action="store_true", help="replay each launch group from a CUDA graph")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 0)
@@ -260,6 +261,8 @@ def main():
     w, sc, sh = pkg.random_weights()
     bb = pkg.Backbone(wl["max_voxels"], w, sc, sh, dtype=pkg.F16)
     pipe = pkg.Pipeline(bb, B, P, nstreams=args.streams)
+    if args.graphs:
+        pipe.use_graphs(True)
 
     def barrier():
         if world > 1:
@@ -364,7 +367,7 @@ def main():
                     warmup=max(args.warmup, 3), ms_per_step=dev_ms / args.steps, higher_is_better=True,
                     scaling="weak", vs_baseline=None, dtype="f16", data="synthetic",
                     config=dict(workload=args.workload, description=wl["desc"], points_per_frame=P,
-                                frames_per_gpu_per_step=F, frames_per_launch_group=B, streams=args.streams,
+                                frames_per_gpu_per_step=F, frames_per_launch_group=B, streams=args.streams, cuda_graphs=bool(args.graphs),
                                 max_voxels=wl["max_voxels"], layers=len(bb.layers),
                                 l2="inputs larger than L2 (points of one step: %.0f MB)" % (F * P * 16 / 1e6),
                                 parallelism=f"frames sharded over {world} GPU(s), no collective"),

@@ -257,6 +257,11 @@ int sessd_pipeline_run_host(sessd_pipeline* pl, const float* host_points, const 
  * stream event is returned in *elapsed_ms when it is non-null. */
 int sessd_pipeline_run_device(sessd_pipeline* pl, const void* points, const void* sizes, int nframes,
                               float* elapsed_ms);
+/* With enable != 0, every stream slot captures the launch sequence of one full group into a CUDA graph the second
+ * time it runs one and replays it from then on (partial last groups and profiled runs use plain launches).
+ * Device-resident inputs are then copied into the slot's staging buffers first. Off by default. No counterpart
+ * in the reference, which launches every kernel of every frame from the host. */
+int sessd_pipeline_use_graphs(sessd_pipeline* pl, int enable);
 /* Dense BEV buffer / workspace of stream `s` (device pointers; dense is [batch][C*D][H][W]). */
 void* sessd_pipeline_dense(sessd_pipeline* pl, int s);
 void* sessd_pipeline_workspace(sessd_pipeline* pl, int s);

@@ -29,7 +29,8 @@ EXPORTS = (
     "sessd_backbone_workspace_bytes", "sessd_backbone_enqueue", "sessd_backbone_pair_counts",
     "sessd_backbone_layer_view",
     "sessd_backbone_final_level", "sessd_pipeline_create", "sessd_pipeline_destroy", "sessd_pipeline_run_host",
-    "sessd_pipeline_run_device", "sessd_pipeline_dense", "sessd_pipeline_workspace", "sessd_launch_count",
+    "sessd_pipeline_run_device", "sessd_pipeline_dense", "sessd_pipeline_workspace", "sessd_pipeline_use_graphs",
+    "sessd_launch_count",
     "sessd_profile_begin", "sessd_profile_end", "sessd_read_status", "sessd_last_cuda_error", "sessd_version",
     "sessd_anchor_decode_enqueue", "sessd_filter_boxes_workspace_bytes", "sessd_filter_boxes_enqueue",
     "sessd_decode_filter_enqueue", "sessd_rotated_nms_workspace_bytes", "sessd_rotated_nms_enqueue",
@@ -463,6 +464,10 @@ class Pipeline:
         _check(lib().sessd_pipeline_create(backbone.handle, batch, max_points, nstreams, C.byref(self.handle)),
                "sessd_pipeline_create")
 
+    def use_graphs(self, enable=True):
+        """Replay the launch sequence of full groups from CUDA graphs (captured per stream slot on second use)."""
+        _check(lib().sessd_pipeline_use_graphs(self.handle, int(bool(enable))), "sessd_pipeline_use_graphs")
+
     def run_device(self, points, sizes) -> float:
         """points cuda f32 [F, P, 4], sizes cuda i32 [F]; returns device milliseconds."""
         ms = C.c_float(0)
@@ -477,6 +482,20 @@ class Pipeline:
                                              points.shape[0], C.c_void_p(voxel_num.data_ptr()),
                                              C.c_void_p(status.data_ptr()), C.byref(ms)), "sessd_pipeline_run_host")
         return float(ms.value)
+
+    def dense(self, s):
+        """The dense BEV buffer of stream slot `s` as a cuda tensor [batch, C*D, H, W] (a view, not a copy)."""
+        torch = _torch()
+        ptr = lib().sessd_pipeline_dense(self.handle, s)
+        if not ptr:
+            raise ValueError("no such stream slot")
+        shape = tuple(self.backbone.dense_shape(self.batch))
+        typestr = "<f4" if self.backbone.dtype == F32 else "<f2"
+
+        class _View:
+            __cuda_array_interface__ = {"shape": shape, "typestr": typestr, "data": (int(ptr), False), "version": 2}
+
+        return torch.as_tensor(_View(), device="cuda")
 
     def status_bits(self) -> int:
         """OR of the status words of all stream workspaces (synchronises the device)."""

@@ -820,6 +820,11 @@ struct sessd_pipeline {
     std::vector<int32_t*> sizes;
     std::vector<cudaEvent_t> done;
     cudaEvent_t start;
+    // optional: the launch sequence of one full group, captured once per stream slot and replayed
+    bool use_graphs;
+    std::vector<cudaGraphExec_t> graphs;
+    std::vector<char> warmed;   // slot has run one plain enqueue (kernels configured) before any capture
+    std::vector<uint64_t> graph_kernels;   // kernels in the slot's graph, for the launch counter
 };
 
 extern "C" {
@@ -831,6 +836,7 @@ void sessd_pipeline_destroy(sessd_pipeline* pl) {
     for (auto p : pl->dense) if (p) cudaFree(p);
     for (auto p : pl->pts) if (p) cudaFree(p);
     for (auto p : pl->sizes) if (p) cudaFree(p);
+    for (auto g : pl->graphs) if (g) cudaGraphExecDestroy(g);
     for (auto e : pl->done) if (e) cudaEventDestroy(e);
     if (pl->start) cudaEventDestroy(pl->start);
     for (auto s : pl->streams) if (s) cudaStreamDestroy(s);
@@ -860,6 +866,10 @@ int sessd_pipeline_create(const sessd_backbone* bb, int batch, int max_points, i
     pl->pts.assign(nstreams, nullptr);
     pl->sizes.assign(nstreams, nullptr);
     pl->done.assign(nstreams, nullptr);
+    pl->use_graphs = false;
+    pl->graphs.assign(nstreams, nullptr);
+    pl->warmed.assign(nstreams, 0);
+    pl->graph_kernels.assign(nstreams, 0);
     cudaError_t e = cudaEventCreate(&pl->start);
     for (int s = 0; s < nstreams && e == cudaSuccess; ++s) {
         e = cudaStreamCreateWithFlags(&pl->streams[s], cudaStreamNonBlocking);
@@ -875,6 +885,12 @@ int sessd_pipeline_create(const sessd_backbone* bb, int batch, int max_points, i
         return SESSD_ERR_CUDA;
     }
     *out = pl;
+    return SESSD_OK;
+}
+
+int sessd_pipeline_use_graphs(sessd_pipeline* pl, int enable) {
+    if (!pl) return SESSD_ERR_NULL;
+    pl->use_graphs = enable != 0;
     return SESSD_OK;
 }
 
@@ -914,8 +930,47 @@ static int pipeline_run(sessd_pipeline* pl, const void* points, const int32_t* s
             dpts = static_cast<const char*>(points) + (size_t)f0 * frame_bytes;
             dsizes = sizes + f0;
         }
-        int rc = sessd_backbone_enqueue(bb, nb, pl->max_points, dpts, dsizes, pl->dense[s], pl->ws[s], pl->ws_bytes, st);
-        if (rc) return rc;
+        int rc = SESSD_OK;
+        // Graph path: only full groups, only outside per-launch profiling (events recorded inside a capture
+        // cannot be timed), and only after the slot has run once plainly. The captured sequence reads the
+        // slot's own staging buffers, so device-resident inputs are copied there first (device to device).
+        if (pl->use_graphs && nb == pl->batch && !g_recorder && pl->warmed[s]) {
+            if (!host) {
+                SESSD_CUDA(cudaMemcpyAsync(pl->pts[s], dpts, (size_t)nb * frame_bytes, cudaMemcpyDeviceToDevice, st));
+                SESSD_CUDA(cudaMemcpyAsync(pl->sizes[s], dsizes, (size_t)nb * 4, cudaMemcpyDeviceToDevice, st));
+            }
+            if (!pl->graphs[s]) {
+                cudaGraph_t graph = nullptr;
+                const uint64_t launches_before = g_launches.load(std::memory_order_relaxed);
+                SESSD_CUDA(cudaStreamBeginCapture(st, cudaStreamCaptureModeThreadLocal));
+                rc = sessd_backbone_enqueue(bb, nb, pl->max_points, pl->pts[s], pl->sizes[s], pl->dense[s], pl->ws[s],
+                                            pl->ws_bytes, st);
+                const cudaError_t e_end = cudaStreamEndCapture(st, &graph);
+                // the captured launches were recorded, not run: they count when the graph is launched
+                pl->graph_kernels[s] = g_launches.load(std::memory_order_relaxed) - launches_before;
+                g_launches.fetch_sub(pl->graph_kernels[s], std::memory_order_relaxed);
+                if (rc) {
+                    if (graph) cudaGraphDestroy(graph);
+                    return rc;
+                }
+                if (e_end != cudaSuccess) {
+                    set_cuda_error(e_end, "cudaStreamEndCapture");
+                    return SESSD_ERR_CUDA;
+                }
+                const cudaError_t e_inst = cudaGraphInstantiate(&pl->graphs[s], graph, 0);
+                cudaGraphDestroy(graph);
+                if (e_inst != cudaSuccess) {
+                    set_cuda_error(e_inst, "cudaGraphInstantiate");
+                    return SESSD_ERR_CUDA;
+                }
+            }
+            SESSD_CUDA(cudaGraphLaunch(pl->graphs[s], st));
+            g_launches.fetch_add(pl->graph_kernels[s], std::memory_order_relaxed);
+        } else {
+            rc = sessd_backbone_enqueue(bb, nb, pl->max_points, dpts, dsizes, pl->dense[s], pl->ws[s], pl->ws_bytes, st);
+            if (rc) return rc;
+            if (nb == pl->batch) pl->warmed[s] = 1;
+        }
         if (host && (host_voxel_num || host_status)) {
             void *feat, *coors, *num;
             rc = sessd_backbone_layer_view(bb, nb, pl->max_points, pl->ws[s], last_layer, &feat, &coors, &num);
