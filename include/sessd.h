@@ -42,7 +42,8 @@ typedef enum sessd_error {
     SESSD_ERR_PARAM = -2,       /* a parameter is out of its supported range */
     SESSD_ERR_WORKSPACE = -3,   /* workspace_bytes is smaller than *_workspace_bytes() */
     SESSD_ERR_CUDA = -4,        /* a CUDA runtime call failed; see sessd_last_cuda_error() */
-    SESSD_ERR_UNSUPPORTED = -5  /* channel count / dtype combination has no kernel */
+    SESSD_ERR_UNSUPPORTED = -5, /* channel count / dtype combination has no kernel */
+    SESSD_ERR_IO = -6           /* a file could not be opened, read or written, or is malformed */
 } sessd_error;
 
 /* Bits of the device status word. */
@@ -352,6 +353,47 @@ int sessd_read_status(const void* workspace, void* stream);
 const char* sessd_last_cuda_error(void);
 /* Library version string. */
 const char* sessd_version(void);
+
+/* ------------------------------------------------------------------------------------------
+ * On-disk formats either side of the path (host code, no GPU needed).
+ * ---------------------------------------------------------------------------------------- */
+
+/* A parsed weight file. Replaces loadWeights (se-ssd-ai-trt.cpp:278-314) and its std::map<std::string, Weights>:
+ * first token = number of blobs, then per blob `name count` and `count` hexadecimal words, each the bit pattern
+ * of one fp32 value (written by tools/gen_wts.py:85-99). A malformed or truncated file gives SESSD_ERR_IO
+ * (the reference asserts or reads garbage); a name that occurs twice keeps its last blob, as the map does. */
+typedef struct sessd_wts sessd_wts;
+int sessd_wts_load(const char* path, sessd_wts** out);
+void sessd_wts_destroy(sessd_wts* w);
+int sessd_wts_count(const sessd_wts* w);   /* blobs in file order (duplicates included), or a negative error */
+/* Blob `index` in file order / the blob called `name` (SESSD_ERR_PARAM when absent; the reference's
+ * weightMap[name] silently creates an empty entry). The pointers stay valid until sessd_wts_destroy. */
+int sessd_wts_entry(const sessd_wts* w, int index, const char** name, const float** values, int64_t* count);
+int sessd_wts_find(const sessd_wts* w, const char* name, const float** values, int64_t* count);
+/* Writes a file the reference's loadWeights reads back bit for bit (the exporter's format, tools/gen_wts.py:85-99). */
+int sessd_wts_save(const char* path, int n, const char* const* names, const float* const* values,
+                   const int64_t* counts);
+
+/* scale = gamma / sqrt(var + eps), shift = beta - mean * gamma / sqrt(var + eps), in fp32: the numbers
+ * add_batchNorm1d_relu (se-ssd-ai-trt.cpp:808-826) hands to its IScaleLayer, ready for the `scale` / `shift`
+ * arguments of sessd_conv_weights_create. */
+int sessd_fold_batchnorm(const float* gamma, const float* beta, const float* mean, const float* var, int len,
+                         float eps, float* scale, float* shift);
+
+/* sessd_backbone_create from a weight file: layer l takes `<prefix>.<module_index[l]>.weight` (the flattened
+ * [k0][k1][k2][Cin][Cout] tensor) and folds the batch norm `<prefix>.<module_index[l] + 1>.{weight, bias,
+ * running_mean, running_var}` with `eps`, which is what se-ssd-ai-trt.cpp:1147-1249 wires with
+ * prefix "backbone.middle_conv", module indices 0, 3, ..., 39 and eps 1e-5. A missing blob or one of the wrong
+ * size gives SESSD_ERR_PARAM. */
+int sessd_backbone_create_from_wts(const sessd_voxel_params* vp, const sessd_conv_params* layers, int nlayers,
+                                   const int32_t* module_index, const sessd_wts* w, const char* prefix, float eps,
+                                   const sessd_s2d_params* s2d, int dtype, sessd_backbone** out);
+
+/* Reads one point cloud file (fp32 x, y, z, intensity records, the KITTI ".bin" layout) into
+ * points [max_points][4], zero-fills the rest and sets *points_size = bytes / 16. Replaces loadData
+ * (se-ssd-ai-trt.cpp:1515-1556) and the size computation at :1848; a file larger than the buffer gives
+ * SESSD_ERR_PARAM (the reference exits the process). */
+int sessd_points_load(const char* path, float* points, int max_points, int32_t* points_size);
 
 #ifdef __cplusplus
 }

@@ -12,7 +12,7 @@ import os
 
 import numpy as np
 
-from . import plugins, schedule, sharding, synth  # noqa: F401
+from . import formats, plugins, schedule, sharding, synth  # noqa: F401
 from .build import LIB_PATH, build
 
 F32, F16 = 0, 1
@@ -34,6 +34,8 @@ EXPORTS = (
     "sessd_profile_begin", "sessd_profile_end", "sessd_read_status", "sessd_last_cuda_error", "sessd_version",
     "sessd_anchor_decode_enqueue", "sessd_filter_boxes_workspace_bytes", "sessd_filter_boxes_enqueue",
     "sessd_decode_filter_enqueue", "sessd_rotated_nms_workspace_bytes", "sessd_rotated_nms_enqueue",
+    "sessd_wts_load", "sessd_wts_destroy", "sessd_wts_count", "sessd_wts_entry", "sessd_wts_find", "sessd_wts_save",
+    "sessd_fold_batchnorm", "sessd_backbone_create_from_wts", "sessd_points_load",
 )
 
 
@@ -112,7 +114,7 @@ def lib():
 def _check(rc: int, what: str):
     if rc != 0:
         names = {-1: "null pointer", -2: "bad parameter", -3: "workspace too small", -4: "CUDA error",
-                 -5: "unsupported configuration"}
+                 -5: "unsupported configuration", -6: "file missing, unreadable or malformed"}
         extra = lib().sessd_last_cuda_error().decode() if rc == -4 else ""
         raise SessdError(f"{what} failed: {names.get(rc, rc)} {extra}")
 
@@ -389,6 +391,30 @@ class Backbone:
         _check(lib().sessd_backbone_create(C.byref(self.vp), cps, n, wptr, scptr, shptr,
                                            C.byref(self.s2d) if with_dense else None, dtype, C.byref(self.handle)),
                "sessd_backbone_create")
+
+    @classmethod
+    def from_wts(cls, wts, max_voxels, dtype=F16, layers=schedule.LAYERS, module_index=None,
+                 prefix="backbone.middle_conv", eps=1e-5, point_range=synth.POINT_RANGE,
+                 voxel_size=synth.VOXEL_SIZE, with_dense=True):
+        """Backbone from a parsed weight file (formats.Wts): conv weights `<prefix>.<i>.weight`, batch norm
+        `<prefix>.<i+1>.*` folded with eps, i = module_index[l] (default: the digits of the layer's name)."""
+        _torch()
+        self = cls.__new__(cls)
+        self.layers, self.dtype, self.max_voxels = tuple(layers), dtype, max_voxels
+        self.vp = voxel_params(max_voxels, point_range, voxel_size)
+        n = len(self.layers)
+        if module_index is None:
+            module_index = [int("".join(ch for ch in l.name if ch.isdigit())) for l in self.layers]
+        cps = (ConvParams * n)(*[conv_params(l, max_voxels) for l in self.layers])
+        idx = (C.c_int32 * n)(*module_index)
+        last = self.layers[-1]
+        self.s2d = S2DParams(last.out_shape[2], last.out_shape[1], last.out_shape[0], last.cout) if with_dense else None
+        self._keep = []
+        self.handle = C.c_void_p()
+        _check(lib().sessd_backbone_create_from_wts(C.byref(self.vp), cps, n, idx, wts.handle, prefix.encode(),
+                                                    C.c_float(eps), C.byref(self.s2d) if with_dense else None,
+                                                    dtype, C.byref(self.handle)), "sessd_backbone_create_from_wts")
+        return self
 
     def workspace_bytes(self, batch, max_points) -> int:
         n = lib().sessd_backbone_workspace_bytes(self.handle, batch, max_points)

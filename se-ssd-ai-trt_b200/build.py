@@ -11,7 +11,7 @@ _CSRC = os.path.join(_HERE, "csrc")
 LIB_PATH = os.path.join(_HERE, "libsessd.so")
 
 SOURCES = ["capi.cu", "voxelize.cu", "rulebook.cu", "conv_simt.cu", "conv_umma.cu", "sparse2dense.cu", "voxelize_static.cu",
-           "postprocess.cu", "nms.cu", "plugins.cu"]
+           "postprocess.cu", "nms.cu", "plugins.cu", "formats.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "-Xcompiler", "-fPIC", "-shared",

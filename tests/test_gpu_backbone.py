@@ -254,6 +254,51 @@ def test_backbone_enqueue_can_be_captured_in_a_cuda_graph(gpu):
     bb.close()
 
 
+def test_backbone_from_weight_file_equals_backbone_from_arrays(gpu, tmp_path):
+    """A weight file in the exporter's format, with the state-dict names the reference's builder looks up
+    (conv `backbone.middle_conv.<i>.weight`, batch norm at <i+1>), gives the same BEV map as a backbone
+    created from the arrays with the batch norm folded by the oracle's restatement."""
+    import torch
+    from oracle import formats as oracle_formats
+
+    case = mk.small_case(gpu)
+    rng = np.random.default_rng(21)
+    blobs, scale, shift = [], [], []
+    for layer, w in zip(case["layers"], case["weights"]):
+        i = int("".join(ch for ch in layer.name if ch.isdigit()))
+        bn = [rng.uniform(0.5, 1.5, layer.cout), rng.standard_normal(layer.cout) * 0.1,
+              rng.standard_normal(layer.cout) * 0.1, rng.uniform(0.5, 2.0, layer.cout)]
+        bn = [a.astype(np.float32) for a in bn]
+        blobs.append((f"backbone.middle_conv.{i}.weight", w))
+        for suffix, a in zip(("weight", "bias", "running_mean", "running_var"), bn):
+            blobs.append((f"backbone.middle_conv.{i + 1}.{suffix}", a))
+        blobs.append((f"backbone.middle_conv.{i + 1}.num_batches_tracked", np.array([100.0], np.float32)))
+        sc, sh = oracle_formats.fold_batchnorm(*bn, 1e-5)
+        scale.append(sc)
+        shift.append(sh)
+    path = tmp_path / "model.wts"
+    oracle_formats.write_wts(path, blobs)
+    wts = gpu.formats.Wts(path)
+    kw = dict(dtype=1, layers=case["layers"], point_range=case["range"], voxel_size=case["voxel"])
+    from_file = gpu.Backbone.from_wts(wts, case["max_voxels"], **kw)
+    from_arrays = gpu.Backbone(case["max_voxels"], case["weights"], scale, shift, **kw)
+    pts = torch.from_numpy(case["points"]).cuda()[None]
+    sizes = torch.tensor([pts.shape[1]], dtype=torch.int32, device="cuda")
+    a, wsa = from_file.run(pts, sizes)
+    b, wsb = from_arrays.run(pts, sizes)
+    torch.cuda.synchronize()
+    assert gpu.read_status(wsa) == 0 and gpu.read_status(wsb) == 0
+    assert float(a.float().abs().sum()) > 0
+    # the folded scale may differ from the oracle's in the square root's last bit: 1e-2 relative is the fp16
+    # bar of the whole stack; in practice the maps are equal
+    assert rel_err(a.float().cpu().numpy(), b.float().cpu().numpy()) <= 1e-2
+    short = gpu.formats.Wts(path)
+    with pytest.raises(gpu.SessdError):              # a module index the file does not hold
+        gpu.Backbone.from_wts(short, case["max_voxels"], module_index=[100 + 3 * i for i in range(len(case["layers"]))], **kw)
+    from_file.close()
+    from_arrays.close()
+
+
 @pytest.mark.parametrize("graphs", [False, True])
 def test_pipeline_groups_equal_direct_backbone_runs(gpu, graphs):
     """Seven frames through a pipeline of groups of two on two stream slots (three full groups and a partial
