@@ -203,6 +203,81 @@ def run_reference(args, pkg, wl, rank, world):
     print(json.dumps(line), flush=True)
 
 
+def detect_latency(pkg, frames_n=24, warm=6):
+    """Frame -> kept boxes at batch 1 on 20,000-point frames (the reference's end-to-end configuration, random-init
+    weights): host points in pinned memory, H2D, front end, fp16 neck + head (torch convolutions), fused decode +
+    score filter, rotated NMS, D2H of the kept boxes, then a synchronisation, as in the reference's loop body."""
+    import torch
+
+    wl = WORKLOADS["single"]
+    frames, sizes = make_frames(pkg, wl, frames_n, 0)
+    P = wl["points"]
+    w, sc, sh = pkg.random_weights()
+    bb = pkg.Backbone(wl["max_voxels"], w, sc, sh, dtype=pkg.F16)
+    blobs = pkg.detector.random_neck_weights()
+    det = pkg.detector.Detector(bb, pkg.detector.Neck2D(blobs))
+    h_pts = torch.from_numpy(frames).pin_memory()
+    h_sizes = torch.from_numpy(sizes).pin_memory()
+    d_pts = torch.empty((1, P, 4), device="cuda")
+    d_sizes = torch.empty((1,), dtype=torch.int32, device="cuda")
+    d_pts.copy_(h_pts[:1])
+    d_sizes.copy_(h_sizes[:1])
+    # a classification bias that lets a few hundred anchors through, as a trained head would
+    logits = det(d_pts, d_sizes)["heads"]["cls"][0, :, 0].float().cpu().numpy()
+    thr = float(np.log(pkg.schedule.SCORE_THRESHOLD / (1 - pkg.schedule.SCORE_THRESHOLD)))
+    blobs["bbox_head.tasks.0.conv_cls.bias"] = blobs["bbox_head.tasks.0.conv_cls.bias"] + np.float32(thr - np.sort(logits)[-300])
+    det = pkg.detector.Detector(bb, pkg.detector.Neck2D(blobs))
+    ws = torch.empty(bb.workspace_bytes(1, P), dtype=torch.uint8, device="cuda")
+    bev = torch.empty(bb.dense_shape(1), dtype=torch.float16, device="cuda")
+    h_boxes = torch.empty((1, pkg.schedule.MAX_BOX_NUM, 9)).pin_memory()
+    h_num = torch.empty((1,), dtype=torch.int32).pin_memory()
+    ev = [torch.cuda.Event(enable_timing=True) for _ in range(5)]
+    stage_ms, wall, kept = np.zeros(4), [], []
+    for f in range(warm + frames_n):
+        i = f % frames_n
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        ev[0].record()
+        d_pts.copy_(h_pts[i:i + 1], non_blocking=True)
+        d_sizes.copy_(h_sizes[i:i + 1], non_blocking=True)
+        ev[1].record()
+        bb.run(d_pts, d_sizes, ws, bev)
+        ev[2].record()
+        heads = det.neck(bev)
+        ev[3].record()
+        flt = pkg.filter_boxes(heads["box"], heads["cls"], heads["iou"], heads["dir"], det.filter, anchors=det.anchors)
+        boxes, num = pkg.rotated_nms(flt["box"], flt["valid"], det.nms_thresh)
+        h_boxes.copy_(boxes, non_blocking=True)
+        h_num.copy_(num, non_blocking=True)
+        ev[4].record()
+        torch.cuda.synchronize()
+        if f >= warm:
+            wall.append((time.perf_counter() - t0) * 1e3)
+            stage_ms += [ev[j].elapsed_time(ev[j + 1]) for j in range(4)]
+            kept.append(int(h_num[0]))
+    # the same chain recorded once into a CUDA graph: H2D into its input buffers, one graph launch, D2H
+    det.capture(P)
+    gwall = []
+    for f in range(warm + frames_n):
+        i = f % frames_n
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        out = det.replay(h_pts[i:i + 1], h_sizes[i:i + 1], read_back_status=False)
+        h_boxes.copy_(out["boxes"], non_blocking=True)
+        h_num.copy_(out["num"], non_blocking=True)
+        torch.cuda.synchronize()
+        if f >= warm:
+            gwall.append((time.perf_counter() - t0) * 1e3)
+    bb.close()
+    stage_ms /= frames_n
+    return dict(workload="20,000-point frames, batch 1, random-init weights", frames=frames_n,
+                graph_latency_ms_median=float(np.median(gwall)), graph_latency_ms_mean=float(np.mean(gwall)),
+                latency_ms_median=float(np.median(wall)), latency_ms_mean=float(np.mean(wall)),
+                device_ms=dict(h2d=round(float(stage_ms[0]), 4), front_end=round(float(stage_ms[1]), 4),
+                               neck_head_torch=round(float(stage_ms[2]), 4), filter_nms_d2h=round(float(stage_ms[3]), 4)),
+                kept_boxes_mean=float(np.mean(kept)))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -215,6 +290,7 @@ def main():
     ap.add_argument("--streams", type=int, default=4, help="launch groups in flight per GPU")
     ap.add_argument("--graphs", action="store_true", help="replay each launch group from a CUDA graph")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--detect", action="store_true", help="also time frame -> boxes at batch 1 (adds a `detect` object)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 0)
 
@@ -391,6 +467,8 @@ def main():
             line["cpu_baseline"] = None
     pipe.close()
     bb.close()
+    if rank == 0 and world == 1 and args.detect:
+        line["detect"] = detect_latency(pkg)
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()

@@ -12,7 +12,7 @@ import os
 
 import numpy as np
 
-from . import formats, plugins, schedule, sharding, synth  # noqa: F401
+from . import detector, formats, plugins, schedule, sharding, synth  # noqa: F401
 from .build import LIB_PATH, build
 
 F32, F16 = 0, 1
@@ -326,9 +326,10 @@ def anchor_decode(box_preds, params: AnchorParams):
     return out
 
 
-def filter_boxes(boxes, cls, iou, dirs, params: FilterParams, anchors: AnchorParams = None):
+def filter_boxes(boxes, cls, iou, dirs, params: FilterParams, anchors: AnchorParams = None, read_back_status=True):
     """Score filter + ordered compaction (FilterBoxByScorePlugin). With `anchors`, `boxes` holds the regression
-    outputs and decoding is fused in. Returns dict(box, score, iou, direction, valid, status)."""
+    outputs and decoding is fused in. Returns dict(box, score, iou, direction, valid, status); with
+    read_back_status=False nothing synchronises (stream capture) and `workspace` is returned for read_status."""
     torch = _torch()
     B, M = boxes.shape[0], params.max_box_num
     f32 = dict(dtype=torch.float32, device=boxes.device)
@@ -345,7 +346,10 @@ def filter_boxes(boxes, cls, iou, dirs, params: FilterParams, anchors: AnchorPar
         _check(lib().sessd_decode_filter_enqueue(C.byref(anchors), C.byref(params), B, ins, outs,
                                                  C.c_void_p(ws.data_ptr()), C.c_size_t(nbytes), _stream()),
                "sessd_decode_filter_enqueue")
-    out["status"] = read_status(ws)
+    if read_back_status:
+        out["status"] = read_status(ws)
+    else:
+        out["workspace"] = ws
     return out
 
 

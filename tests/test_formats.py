@@ -127,3 +127,32 @@ def test_point_cloud_file(pkg, tmp_path):
     assert n == 0 and not got.any()
     with pytest.raises(pkg.SessdError):
         pkg.formats.load_points(tmp_path / "absent.bin", 4)
+
+
+def test_neck_blobs_survive_a_weight_file_and_drive_the_fp32_restatement(pkg, tmp_path):
+    """Random-init neck/head blobs under the reference's state-dict names: written and read back bit for bit,
+    and accepted by the CPU restatement of the layer graph, whose outputs have the plugin input layout."""
+    from oracle import neck as oracle_neck
+
+    blobs = pkg.detector.random_neck_weights()
+    assert len(blobs) == 14 * 5 + 4 * 2
+    path = tmp_path / "neck.wts"
+    pkg.formats.save_wts(path, blobs)
+    w = pkg.formats.Wts(path)
+    back = {}
+    for name, want in blobs.items():
+        got = w.find(name)
+        assert np.array_equal(_bits(got), _bits(want.reshape(-1)))
+        back[name] = got
+    rng = np.random.default_rng(2)
+    bev = np.zeros((1, 128, 202, 178), np.float32)
+    bev[:, :, 61:101, 41:91] = rng.random((1, 128, 40, 50), dtype=np.float32) * (rng.random((1, 1, 40, 50)) < 0.2)
+    out = oracle_neck.neck_and_head(bev, back)
+    assert out["features"].shape == (1, 128, 200, 176)
+    assert [out[k].shape for k in ("box", "cls", "iou", "dir")] == [(1, 70400, 7), (1, 70400, 1), (1, 70400, 1), (1, 70400, 2)]
+    # far from the occupied patch every pixel of the same parity (the stride-2 transposed convolutions) sees
+    # the same empty neighbourhood and gets the same numbers, which pins the (pixel, anchor) order of the reshape
+    box = out["box"].reshape(200, 176, 2, 7)
+    assert np.allclose(box[150, 150], box[150, 152], atol=1e-6) and np.allclose(box[150, 150], box[152, 150], atol=1e-6)
+    assert not np.allclose(box[150, 150, 0], box[150, 150, 1])
+    assert not np.allclose(box[80, 60], box[150, 150])
