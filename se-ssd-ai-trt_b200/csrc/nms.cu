@@ -5,10 +5,10 @@
 //   1. per frame: rank the boxes by descending score (equal scores: lower row first; the reference's
 //      std::sort leaves that open) and store every box's rotated corners and the cos/sin of -yaw once
 //      (the reference recomputes them for every pair);
-//   2. pairs: one thread per (box i, 64-box column block) computes the IoU with the later boxes of the block
-//      by the reference's polygon rule and packs "i suppresses j" bits;
-//   3. per frame: one warp walks the boxes in rank order, keeps the ones not yet suppressed, ORs their bit
-//      rows into the suppressed set, and writes the kept boxes in that order.
+//   2. pairs: one thread per (box i, later box j) computes the IoU by the reference's polygon rule; a warp
+//      covers 32 consecutive j and packs its "i suppresses j" bits with a ballot;
+//   3. per frame: one warp walks the boxes in rank order, 64 at a time, keeps the ones not yet suppressed,
+//      ORs their bit rows into the suppressed set, and writes the kept boxes in that order.
 // Arithmetic is fp32 with explicit round-to-nearest operations (no contraction), in the reference's order.
 #include "common.cuh"
 
@@ -175,66 +175,123 @@ nms_rank_kernel(NmsArgs a) {
 }
 
 // Kernel 2: bit j of mask[b][i][w] = ranked box i suppresses ranked box w*64 + j (only j > i matter).
-__global__ void __launch_bounds__(64)
+// One warp per (box i, 32-box column segment): lane = column, one IoU per thread, the 32 decisions packed
+// by a ballot into half of a 64-bit mask word. Segments from the word that holds i itself up to the last
+// word in use are always written (zeros where j <= i or j >= n), so the greedy pass never reads stale bits.
+constexpr int kMaskWarps = 8;
+__global__ void __launch_bounds__(kMaskWarps * 32)
 nms_mask_kernel(NmsArgs a) {
-    const int blocks_per_frame = a.words * a.words;
-    for (int it = blockIdx.x; it < a.batch * blocks_per_frame; it += gridDim.x) {
-        const int b = it / blocks_per_frame;
-        const int r = it - b * blocks_per_frame;
-        const int rb = r / a.words, cb = r - rb * a.words;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int segs = a.words * 2;
+    const int64_t per_frame = (int64_t)a.max_box * segs;
+    const int64_t items = (int64_t)a.batch * per_frame;
+    for (int64_t it = (int64_t)blockIdx.x * kMaskWarps + warp; it < items; it += (int64_t)gridDim.x * kMaskWarps) {
+        const int b = (int)(it / per_frame);
+        const int r = (int)(it - (int64_t)b * per_frame);
+        const int i = r / segs, seg = r - i * segs;
         const int n = frame_count(a, b);
-        const int i = rb * 64 + threadIdx.x;
-        if (cb < rb || rb * 64 >= n || cb * 64 >= n) continue;   // uniform over the block
-        unsigned long long bits = 0ull;
-        if (i < n) {
+        if (i >= n || seg < (i >> 6) * 2 || seg >= ((n + 63) >> 6) * 2) continue;   // uniform over the warp
+        const int j = seg * 32 + lane;
+        bool hit = false;
+        if (j > i && j < n) {
             const float* gb = a.geom + (size_t)b * a.max_box * kGeomFloats;
-            const BevBox bi = load_geom(gb + (size_t)i * kGeomFloats);
-            const float area_i = mul(bi.w, bi.l);
-            const float rad_i = sqrtf(add(mul(bi.w, bi.w), mul(bi.l, bi.l))) * 0.5f;
-            const int j_end = min(64, n - cb * 64);
-            for (int jj = 0; jj < j_end; ++jj) {
-                const int j = cb * 64 + jj;
-                if (j <= i) continue;
-                const float* gj = gb + (size_t)j * kGeomFloats;
-                // boxes whose centres are farther apart than their half diagonals (plus the corner margin)
-                // cannot touch: overlap 0, IoU 0, which is below any positive threshold
-                const float dx = gj[0] - bi.x, dy = gj[1] - bi.y;
-                const float rad_j = sqrtf(gj[2] * gj[2] + gj[3] * gj[3]) * 0.5f;
-                const float reach = rad_i + rad_j + 0.1f;
-                float iou = 0.f;
-                if (!(a.thresh > 0.f) || dx * dx + dy * dy <= reach * reach) {
-                    const BevBox bj = load_geom(gj);
-                    const float ov = bev_overlap(bi, bj);
-                    iou = dvd(ov, fmaxf(sub(add(area_i, mul(bj.w, bj.l)), ov), kEps));   // nms_cpu, :262-265
-                }
-                if (iou >= a.thresh) bits |= 1ull << jj;
+            const float* gi = gb + (size_t)i * kGeomFloats;
+            const float* gj = gb + (size_t)j * kGeomFloats;
+            // boxes whose centres are farther apart than their half diagonals (plus the corner margin)
+            // cannot touch: overlap 0, IoU 0, which is below any positive threshold
+            const float dx = gj[0] - gi[0], dy = gj[1] - gi[1];
+            const float rad_i = sqrtf(add(mul(gi[2], gi[2]), mul(gi[3], gi[3]))) * 0.5f;
+            const float rad_j = sqrtf(gj[2] * gj[2] + gj[3] * gj[3]) * 0.5f;
+            const float reach = rad_i + rad_j + 0.1f;
+            float iou = 0.f;
+            if (!(a.thresh > 0.f) || dx * dx + dy * dy <= reach * reach) {
+                const BevBox bi = load_geom(gi);
+                const BevBox bj = load_geom(gj);
+                const float ov = bev_overlap(bi, bj);
+                iou = dvd(ov, fmaxf(sub(add(mul(bi.w, bi.l), mul(bj.w, bj.l)), ov), kEps));   // nms_cpu, :262-265
             }
+            hit = iou >= a.thresh;
         }
-        if (i < n) a.mask[((size_t)b * a.max_box + i) * a.words + cb] = bits;
+        const uint32_t bits = __ballot_sync(0xFFFFFFFFu, hit);
+        if (lane == 0)   // little-endian halves of the 64-bit word: even segment = low half
+            reinterpret_cast<uint32_t*>(a.mask + ((size_t)b * a.max_box + i) * a.words)[seg] = bits;
     }
 }
 
 // Kernel 3: greedy pass in rank order by one warp per frame; lane w holds word w of the suppressed set.
+// The boxes are walked 64 at a time: the 64 x 64 diagonal block of the mask is fetched with one load per
+// lane and resolved with shuffles (no memory access between dependent steps), then the full mask rows of the
+// boxes kept in the block are ORed into the suppressed set with independent loads.
 __global__ void __launch_bounds__(32)
 nms_reduce_kernel(NmsArgs a) {
     const int lane = threadIdx.x;
     for (int b = blockIdx.x; b < a.batch; b += gridDim.x) {
         const int n = frame_count(a, b);
+        const int words_n = (n + 63) >> 6;
         const float* bx = a.boxes + (size_t)b * a.max_box * 9;
         float* out = a.kept + (size_t)b * a.max_box * 9;
-        unsigned long long removed = 0ull;
-        int count = 0;
-        for (int i = 0; i < n; ++i) {
-            const unsigned long long word = __shfl_sync(0xFFFFFFFFu, removed, i >> 6);
-            if ((word >> (i & 63)) & 1ull) continue;   // uniform over the warp
-            const int src = a.order[(size_t)b * a.max_box + i];
-            if (lane < 9) out[(size_t)count * 9 + lane] = bx[(size_t)src * 9 + lane];
-            ++count;
-            const int rb = i >> 6;
-            if (lane < (n + 63) / 64 && lane >= rb) removed |= a.mask[((size_t)b * a.max_box + i) * a.words + lane];
+        const unsigned long long* mask = a.mask + (size_t)b * a.max_box * a.words;
+        unsigned long long removed = 0ull, keepw = 0ull;
+        for (int c = 0; c < words_n; ++c) {
+            const int i0 = c * 64 + lane, i1 = i0 + 32;
+            const unsigned long long d0 = i0 < n ? mask[(size_t)i0 * a.words + c] : 0ull;
+            const unsigned long long d1 = i1 < n ? mask[(size_t)i1 * a.words + c] : 0ull;
+            unsigned long long rem = __shfl_sync(0xFFFFFFFFu, removed, c);
+            unsigned long long keep = 0ull;
+            const int rows = min(64, n - c * 64);
+            for (int r = 0; r < rows; ++r) {           // every quantity here is uniform over the warp
+                const unsigned long long row = __shfl_sync(0xFFFFFFFFu, r < 32 ? d0 : d1, r & 31);
+                if (!((rem >> r) & 1ull)) {
+                    keep |= 1ull << r;
+                    rem |= row;
+                }
+            }
+            if (lane == c) keepw = keep;
+            // eight rows per round, so that eight loads are in flight before the first OR waits for one
+            unsigned long long acc = 0ull;
+            const bool mine = lane > c && lane < words_n;
+            for (unsigned long long kk = keep; kk;) {
+                unsigned long long v[8];
+#pragma unroll
+                for (int u = 0; u < 8; ++u) {
+                    v[u] = 0ull;
+                    if (kk) {
+                        const int r = __ffsll((long long)kk) - 1;
+                        kk &= kk - 1ull;
+                        if (mine) v[u] = mask[(size_t)(c * 64 + r) * a.words + lane];
+                    }
+                }
+#pragma unroll
+                for (int u = 0; u < 8; ++u) acc |= v[u];
+            }
+            removed |= acc;
         }
-        for (int e = count * 9 + lane; e < a.max_box * 9; e += 32) out[e] = 0.f;   // rows after the count are zero
-        if (lane == 0) a.kept_num[b] = (uint32_t)count;
+        // output rows: kept boxes in rank order
+        const int cnt = __popcll(keepw);
+        int incl = cnt;
+#pragma unroll
+        for (int d = 1; d < 32; d <<= 1) {
+            const int v = __shfl_up_sync(0xFFFFFFFFu, incl, d);
+            if (lane >= d) incl += v;
+        }
+        const int total = __shfl_sync(0xFFFFFFFFu, incl, 31);
+        const int base = incl - cnt;
+        for (int c = 0; c < words_n; ++c) {
+            const unsigned long long kw = __shfl_sync(0xFFFFFFFFu, keepw, c);
+            const int bw = __shfl_sync(0xFFFFFFFFu, base, c);
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                const int r = lane + 32 * h;
+                if ((kw >> r) & 1ull) {
+                    const int pos = bw + __popcll(kw & ((1ull << r) - 1ull));
+                    const int src = a.order[(size_t)b * a.max_box + c * 64 + r];
+#pragma unroll
+                    for (int e = 0; e < 9; ++e) out[(size_t)pos * 9 + e] = bx[(size_t)src * 9 + e];
+                }
+            }
+        }
+        for (int e = total * 9 + lane; e < a.max_box * 9; e += 32) out[e] = 0.f;   // rows after the count are zero
+        if (lane == 0) a.kept_num[b] = (uint32_t)total;
     }
 }
 
@@ -286,9 +343,9 @@ int sessd_rotated_nms_enqueue(const sessd_nms_params* p, int batch, const void* 
     SESSD_CUDA(cudaMemsetAsync(workspace, 0, kStatusBytes, stream));
     const int frames_grid = batch < persistent_grid(8) ? batch : persistent_grid(8);
     SESSD_LAUNCH(nms_rank_kernel, frames_grid, kThreads, 0, stream, a);
-    const int64_t pair_blocks = (int64_t)batch * words * words;
-    const int pair_grid = (int)(pair_blocks < persistent_grid(16) ? pair_blocks : persistent_grid(16));
-    SESSD_LAUNCH(nms_mask_kernel, pair_grid, 64, 0, stream, a);
+    const int64_t pair_blocks = ((int64_t)batch * M * words * 2 + kMaskWarps - 1) / kMaskWarps;
+    const int pair_grid = (int)(pair_blocks < persistent_grid(8) ? pair_blocks : persistent_grid(8));
+    SESSD_LAUNCH(nms_mask_kernel, pair_grid, kMaskWarps * 32, 0, stream, a);
     SESSD_LAUNCH(nms_reduce_kernel, frames_grid, 32, 0, stream, a);
     return SESSD_OK;
 }
