@@ -218,80 +218,99 @@ nms_mask_kernel(NmsArgs a) {
     }
 }
 
-// Kernel 3: greedy pass in rank order by one warp per frame; lane w holds word w of the suppressed set.
-// The boxes are walked 64 at a time: the 64 x 64 diagonal block of the mask is fetched with one load per
+// Kernel 3: greedy pass in rank order, one block per frame. When the frame's part of the mask fits the
+// block's shared memory all threads stage it there first; warp 0 then walks the boxes 64 at a time (lane w
+// holds word w of the suppressed set): the 64 x 64 diagonal block of the mask is fetched with one load per
 // lane and resolved with shuffles (no memory access between dependent steps), then the full mask rows of the
-// boxes kept in the block are ORed into the suppressed set with independent loads.
-__global__ void __launch_bounds__(32)
-nms_reduce_kernel(NmsArgs a) {
-    const int lane = threadIdx.x;
+// boxes kept in the block are ORed into the suppressed set with independent loads. All threads write the
+// kept boxes in rank order.
+constexpr int kReduceThreads = 256;
+__global__ void __launch_bounds__(kReduceThreads)
+nms_reduce_kernel(NmsArgs a, int smem_words) {
+    extern __shared__ unsigned long long s_mask[];
+    __shared__ unsigned long long s_keep[32];
+    __shared__ int s_base[33];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     for (int b = blockIdx.x; b < a.batch; b += gridDim.x) {
         const int n = frame_count(a, b);
         const int words_n = (n + 63) >> 6;
         const float* bx = a.boxes + (size_t)b * a.max_box * 9;
         float* out = a.kept + (size_t)b * a.max_box * 9;
         const unsigned long long* mask = a.mask + (size_t)b * a.max_box * a.words;
-        unsigned long long removed = 0ull, keepw = 0ull;
-        for (int c = 0; c < words_n; ++c) {
-            const int i0 = c * 64 + lane, i1 = i0 + 32;
-            const unsigned long long d0 = i0 < n ? mask[(size_t)i0 * a.words + c] : 0ull;
-            const unsigned long long d1 = i1 < n ? mask[(size_t)i1 * a.words + c] : 0ull;
-            unsigned long long rem = __shfl_sync(0xFFFFFFFFu, removed, c);
-            unsigned long long keep = 0ull;
-            const int rows = min(64, n - c * 64);
-            for (int r = 0; r < rows; ++r) {           // every quantity here is uniform over the warp
-                const unsigned long long row = __shfl_sync(0xFFFFFFFFu, r < 32 ? d0 : d1, r & 31);
-                if (!((rem >> r) & 1ull)) {
-                    keep |= 1ull << r;
-                    rem |= row;
-                }
+        int stride = a.words;
+        __syncthreads();   // the previous frame is done with the shared arrays
+        if (n * words_n <= smem_words) {
+            // only words from the one that holds the row itself onward are ever written or read
+            for (int e = threadIdx.x; e < n * words_n; e += kReduceThreads) {
+                const int i = e / words_n, w = e - i * words_n;
+                s_mask[e] = w >= (i >> 6) ? mask[(size_t)i * a.words + w] : 0ull;
             }
-            if (lane == c) keepw = keep;
-            // eight rows per round, so that eight loads are in flight before the first OR waits for one
-            unsigned long long acc = 0ull;
-            const bool mine = lane > c && lane < words_n;
-            for (unsigned long long kk = keep; kk;) {
-                unsigned long long v[8];
-#pragma unroll
-                for (int u = 0; u < 8; ++u) {
-                    v[u] = 0ull;
-                    if (kk) {
-                        const int r = __ffsll((long long)kk) - 1;
-                        kk &= kk - 1ull;
-                        if (mine) v[u] = mask[(size_t)(c * 64 + r) * a.words + lane];
+            mask = s_mask;
+            stride = words_n;
+        }
+        __syncthreads();
+        if (warp == 0) {
+            unsigned long long removed = 0ull, keepw = 0ull;
+            for (int c = 0; c < words_n; ++c) {
+                const int i0 = c * 64 + lane, i1 = i0 + 32;
+                const unsigned long long d0 = i0 < n ? mask[(size_t)i0 * stride + c] : 0ull;
+                const unsigned long long d1 = i1 < n ? mask[(size_t)i1 * stride + c] : 0ull;
+                unsigned long long rem = __shfl_sync(0xFFFFFFFFu, removed, c);
+                unsigned long long keep = 0ull;
+                const int rows = min(64, n - c * 64);
+                for (int r = 0; r < rows; ++r) {           // every quantity here is uniform over the warp
+                    const unsigned long long row = __shfl_sync(0xFFFFFFFFu, r < 32 ? d0 : d1, r & 31);
+                    if (!((rem >> r) & 1ull)) {
+                        keep |= 1ull << r;
+                        rem |= row;
                     }
                 }
+                if (lane == c) keepw = keep;
+                // eight rows per round, so that eight loads are in flight before the first OR waits for one
+                unsigned long long acc = 0ull;
+                const bool mine = lane > c && lane < words_n;
+                for (unsigned long long kk = keep; kk;) {
+                    unsigned long long v[8];
 #pragma unroll
-                for (int u = 0; u < 8; ++u) acc |= v[u];
-            }
-            removed |= acc;
-        }
-        // output rows: kept boxes in rank order
-        const int cnt = __popcll(keepw);
-        int incl = cnt;
+                    for (int u = 0; u < 8; ++u) {
+                        v[u] = 0ull;
+                        if (kk) {
+                            const int r = __ffsll((long long)kk) - 1;
+                            kk &= kk - 1ull;
+                            if (mine) v[u] = mask[(size_t)(c * 64 + r) * stride + lane];
+                        }
+                    }
 #pragma unroll
-        for (int d = 1; d < 32; d <<= 1) {
-            const int v = __shfl_up_sync(0xFFFFFFFFu, incl, d);
-            if (lane >= d) incl += v;
-        }
-        const int total = __shfl_sync(0xFFFFFFFFu, incl, 31);
-        const int base = incl - cnt;
-        for (int c = 0; c < words_n; ++c) {
-            const unsigned long long kw = __shfl_sync(0xFFFFFFFFu, keepw, c);
-            const int bw = __shfl_sync(0xFFFFFFFFu, base, c);
-#pragma unroll
-            for (int h = 0; h < 2; ++h) {
-                const int r = lane + 32 * h;
-                if ((kw >> r) & 1ull) {
-                    const int pos = bw + __popcll(kw & ((1ull << r) - 1ull));
-                    const int src = a.order[(size_t)b * a.max_box + c * 64 + r];
-#pragma unroll
-                    for (int e = 0; e < 9; ++e) out[(size_t)pos * 9 + e] = bx[(size_t)src * 9 + e];
+                    for (int u = 0; u < 8; ++u) acc |= v[u];
                 }
+                removed |= acc;
+            }
+            const int cnt = __popcll(keepw);
+            int incl = cnt;
+#pragma unroll
+            for (int d = 1; d < 32; d <<= 1) {
+                const int v = __shfl_up_sync(0xFFFFFFFFu, incl, d);
+                if (lane >= d) incl += v;
+            }
+            s_keep[lane] = keepw;
+            s_base[lane] = incl - cnt;
+            if (lane == 31) s_base[32] = incl;
+        }
+        __syncthreads();
+        // output rows: kept boxes in rank order
+        const int total = s_base[32];
+        for (int i = threadIdx.x; i < n; i += kReduceThreads) {
+            const int c = i >> 6, r = i & 63;
+            const unsigned long long kw = s_keep[c];
+            if ((kw >> r) & 1ull) {
+                const int pos = s_base[c] + __popcll(kw & ((1ull << r) - 1ull));
+                const int src = a.order[(size_t)b * a.max_box + i];
+#pragma unroll
+                for (int e = 0; e < 9; ++e) out[(size_t)pos * 9 + e] = bx[(size_t)src * 9 + e];
             }
         }
-        for (int e = total * 9 + lane; e < a.max_box * 9; e += 32) out[e] = 0.f;   // rows after the count are zero
-        if (lane == 0) a.kept_num[b] = (uint32_t)total;
+        for (int e = total * 9 + threadIdx.x; e < a.max_box * 9; e += kReduceThreads) out[e] = 0.f;   // rows after the count
+        if (threadIdx.x == 0) a.kept_num[b] = (uint32_t)total;
     }
 }
 
@@ -346,7 +365,11 @@ int sessd_rotated_nms_enqueue(const sessd_nms_params* p, int batch, const void* 
     const int64_t pair_blocks = ((int64_t)batch * M * words * 2 + kMaskWarps - 1) / kMaskWarps;
     const int pair_grid = (int)(pair_blocks < persistent_grid(8) ? pair_blocks : persistent_grid(8));
     SESSD_LAUNCH(nms_mask_kernel, pair_grid, kMaskWarps * 32, 0, stream, a);
-    SESSD_LAUNCH(nms_reduce_kernel, frames_grid, 32, 0, stream, a);
+    // the staged copy of a frame's mask must fit the 48 KB a block gets without opting in; larger tables are read in place
+    const size_t stage_bytes = M * words * sizeof(unsigned long long);
+    const int smem_words = stage_bytes <= 40 * 1024 ? (int)(M * words) : 0;
+    SESSD_LAUNCH(nms_reduce_kernel, frames_grid, kReduceThreads, (size_t)smem_words * sizeof(unsigned long long), stream, a,
+                 smem_words);
     return SESSD_OK;
 }
 

@@ -161,6 +161,32 @@ def test_rotated_nms_matches_oracle(gpu, oracle, thresh):
             assert 0 < len(want) < n                                    # the case does suppress something
 
 
+def test_rotated_nms_table_larger_than_the_staged_copy(gpu, oracle):
+    """A 1,200-row box table: its suppression mask (1,200 x 19 words) does not fit the block's staging buffer,
+    so the greedy pass reads the mask in place; same answer as the oracle."""
+    import torch
+
+    rs = np.random.RandomState(77)
+    M, counts = 1200, [700, 1200]
+    boxes = np.zeros((len(counts), M, 9), np.float32)
+    for b, n in enumerate(counts):
+        for attempt in range(20):
+            cand = _random_boxes(rs, n, 150.0)
+            if _clear_of_threshold(oracle, cand, 0.1):
+                break
+        else:
+            pytest.fail("could not draw boxes clear of the threshold")
+        boxes[b, :n] = cand
+    valid = np.array(counts, np.int32)
+    kept, kept_num = gpu.rotated_nms(torch.from_numpy(boxes).cuda(), torch.from_numpy(valid).cuda(), 0.1)
+    kept, kept_num = kept.cpu().numpy(), kept_num.cpu().numpy()
+    for b, n in enumerate(counts):
+        want, _ = oracle.rotated_nms(boxes[b, :n], 0.1)
+        assert int(kept_num[b]) == len(want) and 0 < len(want) < n
+        np.testing.assert_array_equal(kept[b, :len(want)], want)
+        assert not kept[b, len(want):].any()
+
+
 def test_rotated_nms_after_score_filter(gpu, oracle):
     """Score filter -> NMS on the device, the reference's post-processing chain (se-ssd-ai-trt.cpp:1868-1892)."""
     S = gpu.schedule
