@@ -6,7 +6,10 @@ import pytest
 
 from conftest import canonical_rulebook
 
-KITTI0 = "/root/reference/data/kitti_training_velodyne_reduced/000000.bin"
+# the reference checkout, when it sits beside this repository (or where SESSD_REFERENCE_ROOT points)
+_REFERENCE = os.environ.get("SESSD_REFERENCE_ROOT",
+                            os.path.join(os.path.dirname(os.path.abspath(__file__)), "..", "..", "reference"))
+KITTI0 = os.path.join(_REFERENCE, "data", "kitti_training_velodyne_reduced", "000000.bin")
 GOLDEN = os.path.join(os.path.dirname(__file__), "golden")
 
 
