@@ -31,6 +31,23 @@ def main():
                         layer_pairs=r["layer_pairs"], coors=r["coors"], feat=r["feat"], dense_nz=nz,
                         dense_val=r["dense"].ravel()[nz])
     print("rows", r["layer_rows"], "pairs", r["layer_pairs"], "final", r["num"])
+    # a small weight file in the exporter's text format (tools/gen_wts.py:85-99), written by the pure-Python
+    # restatement of that loop; tests/test_formats.py reads it with the library and compares bit patterns
+    from oracle import formats as oracle_formats
+
+    oracle_formats.write_wts(os.path.join(HERE, "tiny.wts"), tiny_wts_blobs())
+
+
+def tiny_wts_blobs():
+    """Blobs of tests/golden/tiny.wts: seeded values plus the special bit patterns a reader can get wrong."""
+    rng = np.random.default_rng(12345)
+    return [
+        ("backbone.middle_conv.0.weight", rng.standard_normal((3, 2, 4)).astype(np.float32)),
+        ("backbone.middle_conv.1.running_var", rng.uniform(0.5, 2.0, 4).astype(np.float32)),
+        ("special", np.array([0x00000000, 0x80000000, 0x7F800000, 0xFF800000, 0x7FC00001, 0x00000001, 0x7F7FFFFF],
+                             np.uint32).view(np.float32)),
+        ("empty", np.zeros((0,), np.float32)),
+    ]
 
 
 if __name__ == "__main__":

@@ -156,3 +156,23 @@ def test_neck_blobs_survive_a_weight_file_and_drive_the_fp32_restatement(pkg, tm
     assert np.allclose(box[150, 150], box[150, 152], atol=1e-6) and np.allclose(box[150, 150], box[152, 150], atol=1e-6)
     assert not np.allclose(box[150, 150, 0], box[150, 150, 1])
     assert not np.allclose(box[80, 60], box[150, 150])
+
+
+def test_committed_weight_file_fixture(pkg):
+    """tests/golden/tiny.wts was written by the restated exporter loop (tests/golden/make_golden.py); the
+    library's reader must return the bit patterns the generator put in, and re-saving must give the file back."""
+    import os
+    import sys
+
+    golden = os.path.join(os.path.dirname(__file__), "golden")
+    sys.path.insert(0, golden)
+    import make_golden
+
+    path = os.path.join(golden, "tiny.wts")
+    w = pkg.formats.Wts(path)
+    blobs = make_golden.tiny_wts_blobs()
+    assert len(w) == len(blobs)
+    for i, (name, want) in enumerate(blobs):
+        got_name, got = w.entry(i)
+        assert got_name == name and np.array_equal(_bits(got), _bits(want.reshape(-1)))
+    assert open(path, "rb").read().startswith(b"4\nbackbone.middle_conv.0.weight 24  ")
