@@ -100,6 +100,9 @@ conv_simt_kernel(const T* __restrict__ in, T* __restrict__ out, const int32_t* _
                  T* __restrict__ dense, const int4* __restrict__ out_coors, int D, int H, int W) {
     constexpr int TPR = COUT / CO_T;          // threads per output row
     constexpr int ROWS = kThreads / TPR;      // rows per block iteration
+    constexpr int KVOL_MAX = 27;              // 3 x 3 x 3 is the largest kernel the geometry code accepts
+    constexpr bool COMPACT = CIN <= 16;
+    __shared__ int32_t s_idx[COMPACT ? KVOL_MAX : 1][kThreads];
     const int chunks = (max_voxels + ROWS - 1) / ROWS;
     const int items = batch * chunks;
     const int cg = threadIdx.x % TPR;
@@ -114,11 +117,8 @@ conv_simt_kernel(const T* __restrict__ in, T* __restrict__ out, const int32_t* _
         for (int c = 0; c < CO_T; ++c) acc[c] = 0.f;
         const int32_t* nb = nbr + (size_t)b * kvol * max_voxels + o;
         const T* in_b = in + (size_t)b * max_voxels * CIN;
-        for (int k = 0; k < kvol; ++k) {
-            const int idx = __ldg(nb + (size_t)k * max_voxels);
-            if (idx < 0) continue;
-            float x[CIN];
-            RowLoader<T, CIN>::load(in_b + (size_t)idx * CIN, x);
+        // one neighbour: s = sum_ci x[ci] * W[k][ci][:] as a fused chain, then acc += s
+        auto add_neighbour = [&](int k, const float (&x)[CIN]) {
             float s[CO_T];
 #pragma unroll
             for (int c = 0; c < CO_T; ++c) s[c] = 0.f;
@@ -132,6 +132,41 @@ conv_simt_kernel(const T* __restrict__ in, T* __restrict__ out, const int32_t* _
             }
 #pragma unroll
             for (int c = 0; c < CO_T; ++c) acc[c] = __fadd_rn(acc[c], s[c]);
+        };
+        if constexpr (COMPACT) {
+            // Narrow rows (the full-resolution layers, where a row has 5 of its 27 neighbours on average): all
+            // slots are read first, then every thread walks its own present neighbours in ascending k (two
+            // row loads in flight for the 4-channel input). A warp then runs as many steps as its fullest row has
+            // neighbour pairs, instead of one step for every offset any of its 32 rows has. Same order of additions as below.
+            uint32_t present = 0;
+#pragma unroll
+            for (int k = 0; k < KVOL_MAX; ++k) {
+                const int idx = k < kvol ? __ldg(nb + (size_t)k * max_voxels) : -1;
+                s_idx[k][threadIdx.x] = idx;          // read back by this thread only
+                present |= (idx >= 0 ? 1u : 0u) << k;
+            }
+            constexpr int NP = CIN <= 4 ? 2 : 1;      // row loads in flight per thread (four measured no faster than two)
+            while (present) {
+                int ks[NP];
+                float x[NP][CIN];
+#pragma unroll
+                for (int u = 0; u < NP; ++u) {
+                    ks[u] = present ? __ffs((int)present) - 1 : -1;
+                    present &= present - 1u;          // no-op when nothing is left
+                    if (ks[u] >= 0) RowLoader<T, CIN>::load(in_b + (size_t)s_idx[ks[u]][threadIdx.x] * CIN, x[u]);
+                }
+#pragma unroll
+                for (int u = 0; u < NP; ++u)
+                    if (ks[u] >= 0) add_neighbour(ks[u], x[u]);
+            }
+        } else {
+            for (int k = 0; k < kvol; ++k) {
+                const int idx = __ldg(nb + (size_t)k * max_voxels);
+                if (idx < 0) continue;
+                float x[CIN];
+                RowLoader<T, CIN>::load(in_b + (size_t)idx * CIN, x);
+                add_neighbour(k, x);
+            }
         }
 #pragma unroll
         for (int c = 0; c < CO_T; ++c) {
