@@ -353,6 +353,11 @@ int sessd_read_status(const void* workspace, void* stream);
 const char* sessd_last_cuda_error(void);
 /* Library version string. */
 const char* sessd_version(void);
+/* Test hook for the time-out path, process-wide, off by default: while on, the tensor-core convolution kernel's
+ * weight streamer stays silent, so the kernel's bounded waits run out (about 0.1 s), every block leaves through
+ * its abort path, the call returns SESSD_OK and the status word carries SESSD_STATUS_TIMEOUT with the code of
+ * the wait in the second status word. Nothing faults or hangs; the next call with the hook off is normal. */
+int sessd_debug_withhold_weights(int on);
 
 /* ------------------------------------------------------------------------------------------
  * On-disk formats either side of the path (host code, no GPU needed).

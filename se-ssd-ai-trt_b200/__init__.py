@@ -35,7 +35,7 @@ EXPORTS = (
     "sessd_anchor_decode_enqueue", "sessd_filter_boxes_workspace_bytes", "sessd_filter_boxes_enqueue",
     "sessd_decode_filter_enqueue", "sessd_rotated_nms_workspace_bytes", "sessd_rotated_nms_enqueue",
     "sessd_wts_load", "sessd_wts_destroy", "sessd_wts_count", "sessd_wts_entry", "sessd_wts_find", "sessd_wts_save",
-    "sessd_fold_batchnorm", "sessd_backbone_create_from_wts", "sessd_points_load",
+    "sessd_fold_batchnorm", "sessd_backbone_create_from_wts", "sessd_points_load", "sessd_debug_withhold_weights",
 )
 
 

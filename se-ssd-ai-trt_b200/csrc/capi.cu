@@ -133,7 +133,11 @@ bool conv_params_ok(const sessd_conv_params* p, int batch) {
 
 size_t esize(int dtype) { return dtype == SESSD_F32 ? 4 : 2; }
 
-int choose_conv(const ConvLaunch& c, cudaStream_t stream) {
+std::atomic<int> g_withhold_weights{0};   // sessd_debug_withhold_weights
+
+int choose_conv(const ConvLaunch& c_in, cudaStream_t stream) {
+    ConvLaunch c = c_in;
+    c.debug_withhold_weights = g_withhold_weights.load(std::memory_order_relaxed);
     if (c.dtype == SESSD_F16 && conv_umma_supported(c.cin, c.cout) && c.umma_weights) return launch_conv_umma(c, stream);
     return launch_conv_simt(c, stream);
 }
@@ -261,6 +265,11 @@ void backbone_layout(Bump& bump, const sessd_backbone* bb, int batch, int max_po
 extern "C" {
 
 const char* sessd_version(void) { return "sessd-b200 0.1 (sm_100a)"; }
+
+int sessd_debug_withhold_weights(int on) {
+    g_withhold_weights.store(on ? 1 : 0, std::memory_order_relaxed);
+    return SESSD_OK;
+}
 const char* sessd_last_cuda_error(void) { return t_last_error.c_str(); }
 uint64_t sessd_launch_count(void) { return g_launches.load(); }
 

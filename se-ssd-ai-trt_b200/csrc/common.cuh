@@ -256,6 +256,7 @@ struct ConvLaunch {
     const int32_t* out_coors;
     int D, H, W;
     int32_t* status;       // device status word (tensor-core path reports wait timeouts there)
+    int debug_withhold_weights;   // tests only: the tensor-core kernel's weight streamer stays silent (waits run out)
 };
 int launch_conv_simt(const ConvLaunch& c, cudaStream_t stream);
 bool conv_simt_supported(int cin, int cout);

@@ -203,6 +203,7 @@ struct SharedCtl {
     unsigned long long i_empty[IDX_STAGES];
     unsigned long long acc_full;
     unsigned long long acc_empty;
+    unsigned long long mma_drain;   // aborting CTA only: completes when the issuers' outstanding MMAs have finished
     uint32_t tmem_base;
     int abort_flag;
     int abort_where;   // code of the first wait that ran out (role and ring position), for the status block
@@ -259,7 +260,9 @@ conv_umma_kernel(const __half* __restrict__ in, __half* __restrict__ out, const 
                  const uint32_t* __restrict__ tile_mask, const int32_t* __restrict__ out_num,
                  const uint8_t* __restrict__ wtiles, const float* __restrict__ scale, const float* __restrict__ shift,
                  int relu, int batch, int max_voxels, int kvol, __half* __restrict__ dense,
-                 const int4* __restrict__ out_coors, int D, int H, int W, int32_t* status) {
+                 const int4* __restrict__ out_coors, int D, int H, int W, int32_t* status, int withhold_weights) {
+    // withhold_weights (tests of the time-out path only): the weight streamer stays silent, so the MMA issuers'
+    // bounded wait for the first weight block runs out and every CTA with work leaves through the abort path.
     constexpr int KG = 64 / CIN;            // kernel offsets sharing one 128-byte A row
     constexpr int CPO = CIN / 8;            // 16-byte chunks per offset
     constexpr int B_BYTES = COUT * ROW_BYTES;
@@ -296,6 +299,7 @@ conv_umma_kernel(const __half* __restrict__ in, __half* __restrict__ out, const 
         }
         mbar_init(smem_u32(&ctl->acc_full), MMA_WARPS);        // every MMA issuer reports its tiles
         mbar_init(smem_u32(&ctl->acc_empty), TILE_M);
+        mbar_init(smem_u32(&ctl->mma_drain), MMA_WARPS);
         ctl->abort_flag = 0;
         ctl->abort_where = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -689,7 +693,7 @@ conv_umma_kernel(const __half* __restrict__ in, __half* __restrict__ out, const 
             }
         } else {
             // ---------------- weight streamer ----------------
-            if (lane == 0) {
+            if (lane == 0 && !withhold_weights) {
                 uint32_t my_b = b_it;
                 bool ok = true;
                 for (int g = 0; g < nstages && ok; ++g) {
@@ -726,9 +730,12 @@ conv_umma_kernel(const __half* __restrict__ in, __half* __restrict__ out, const 
     }
 #endif
     if (*abort_flag) {
-        // An aborting CTA must not return while its own copies are still writing shared memory: the gather
-        // warps wait for their cp.async copies, the weight streamer (bounded) for its last bulk copies.
-        if (warp < GATHER_WARPS) asm volatile("cp.async.wait_all;" ::: "memory");
+        // An aborting CTA must not return while its own copies are still writing shared memory or its MMAs tensor
+        // memory: the gather and index warps wait for their cp.async copies, the issuers commit to a barrier that
+        // warp 4 waits on (bounded) before it frees the tensor memory, the weight streamer waits (bounded) for
+        // its last bulk copies.
+        if (warp < GATHER_WARPS || warp == 6) asm volatile("cp.async.wait_all;" ::: "memory");   // rows and indices
+        if ((warp == 4 || warp == 7) && lane == 0) umma_commit(smem_u32(&ctl->mma_drain));
         if (warp == 5 && lane == 0) {
             const uint32_t first = b_issued > (uint32_t)B_STAGES ? b_issued - B_STAGES : 0u;
             for (uint32_t j = first; j < b_issued; ++j) {
@@ -744,6 +751,12 @@ conv_umma_kernel(const __half* __restrict__ in, __half* __restrict__ out, const 
         atomicCAS(status + 1, 0, ctl->abort_where);   // first report wins: which wait, at which ring position
     }
     if (warp == 4) {
+        if (*abort_flag && lane == 0) {
+            // the tensor memory is given back only when no MMA of this CTA can still write to it
+            const long long t0 = clock64();
+            while (!mbar_try_wait(smem_u32(&ctl->mma_drain), 0u) && clock64() - t0 < WAIT_LIMIT_CYCLES) {}
+        }
+        __syncwarp();
         tc_fence_after();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(TMEM_COLS) : "memory");
     }
@@ -768,7 +781,7 @@ int launch_one(const ConvLaunch& c, cudaStream_t stream) {
                        static_cast<const __half*>(c.in), static_cast<__half*>(c.out), c.nbr, c.tile_mask, c.out_num,
                        static_cast<const uint8_t*>(c.umma_weights), c.scale, c.shift, c.relu, c.batch, c.max_voxels,
                        c.kvol, static_cast<__half*>(c.dense), reinterpret_cast<const int4*>(c.out_coors), c.D, c.H, c.W,
-                       c.status);
+                       c.status, c.debug_withhold_weights);
     return SESSD_OK;
 }
 

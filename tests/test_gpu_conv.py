@@ -210,3 +210,40 @@ def test_more_row_groups_than_resident_blocks_fp16(gpu, oracle, cin, cout):
     W = (rs.randn(27, cin, cout) / np.sqrt(5 * cin)).astype(np.float32)
     layer = _layer(gpu, True, cin, cout, (3, 3, 3), (1, 1, 1), (1, 1, 1), shape)
     _check_layer(gpu, oracle, layer, frames, W, dtype=gpu.F16, maxV=45056)
+
+
+def test_bounded_waits_run_out_report_and_leave_the_context_usable(gpu):
+    """Time-out path of the tensor-core kernel, made on the host: with the library's test hook on, the kernel's
+    weight streamer stays silent, the MMA issuers' bounded wait for the first weight block runs out, every block
+    leaves through its abort path and the call reports SESSD_STATUS_TIMEOUT with the code of that wait. Nothing
+    faults; the same call with the hook off then gives the result it gave before."""
+    import torch
+
+    rs = np.random.RandomState(5)
+    shape, cin, cout, n, maxV = (10, 60, 60), 32, 32, 3000, 4096
+    c = _random_coords(rs, n, shape)
+    layer = _layer(gpu, True, cin, cout, (3, 3, 3), (1, 1, 1), (1, 1, 1), shape)
+    feat = np.zeros((1, maxV, cin), np.float16)
+    coors = np.zeros((1, maxV, 4), np.int32)
+    feat[0, :len(c)] = rs.randn(len(c), cin).astype(np.float16)
+    coors[0, :len(c)] = c
+    coors[0, :, 0] = 0
+    W = (rs.randn(27, cin, cout) / np.sqrt(5 * cin)).astype(np.float32)
+    p = gpu.conv_params(layer, maxV)
+    w = gpu.ConvWeights(p, W, None, None, False, gpu.F16)
+    tf, tc = torch.from_numpy(feat).cuda(), torch.from_numpy(coors).cuda()
+    tn = torch.tensor([len(c)], dtype=torch.int32, device="cuda")
+    good = gpu.subm_conv(tf, tc, tn, p, w)
+    assert good["status"] == 0
+    want = good["features"].clone()
+    gpu.lib().sessd_debug_withhold_weights(1)
+    try:
+        r = gpu.subm_conv(tf, tc, tn, p, w, keep_workspace=True)
+    finally:
+        gpu.lib().sessd_debug_withhold_weights(0)
+    assert r["status"] & gpu.STATUS_TIMEOUT
+    where = int(r["workspace"][4:8].view(torch.int32)[0])
+    assert where & 15 == 5                    # an MMA issuer waiting for a weight block
+    again = gpu.subm_conv(tf, tc, tn, p, w)
+    assert again["status"] == 0 and torch.equal(again["features"], want)
+    w.close()
