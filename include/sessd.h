@@ -24,7 +24,9 @@
  *     the int32 status word that occupies the first 4 bytes of the caller's workspace (the first
  *     1024 bytes of every workspace are reserved for it and for counters); it is
  *     cleared at the start of every *_enqueue and may be read after the stream has been
- *     synchronised (sessd_read_status does the copy).
+ *     synchronised (sessd_read_status does the copy);
+ *   - a workspace must start on a 256-byte boundary (cudaMalloc and TensorRT workspaces do); an *_enqueue
+ *     given one that does not returns SESSD_ERR_PARAM.
  */
 #ifndef SESSD_H_
 #define SESSD_H_

@@ -355,6 +355,7 @@ int sessd_voxelize_enqueue(const sessd_voxel_params* p, int batch, int max_point
     VoxelWorkspace w;
     voxel_workspace_layout(bump, p, batch, max_points, &w);
     if (bump.total() > workspace_bytes) return SESSD_ERR_WORKSPACE;
+    if (!workspace_aligned(workspace)) return SESSD_ERR_PARAM;
     w.status = status;
     SESSD_CUDA(cudaMemsetAsync(status, 0, kStatusInts * sizeof(int32_t), stream));
     return voxelize_run(p, batch, max_points, out_dtype, static_cast<const float*>(inputs[0]),
@@ -454,6 +455,7 @@ static int conv_enqueue_common(const sessd_conv_params* p, const sessd_conv_weig
     ConvWorkspace ws;
     conv_workspace_layout(bump, p, g, batch, &ws);
     if (bump.total() > workspace_bytes) return SESSD_ERR_WORKSPACE;
+    if (!workspace_aligned(workspace)) return SESSD_ERR_PARAM;
     const int maxV = p->max_voxels;
     const int32_t* in_coors = static_cast<const int32_t*>(inputs[1]);
     const int32_t* in_num = static_cast<const int32_t*>(inputs[2]);
@@ -683,6 +685,7 @@ static int backbone_enqueue_impl(const sessd_backbone* bb, int batch, int max_po
     BackboneWorkspace w;
     backbone_layout(bump, bb, batch, max_points, &w);
     if (bump.total() > workspace_bytes) return SESSD_ERR_WORKSPACE;
+    if (!workspace_aligned(workspace)) return SESSD_ERR_PARAM;
     const int maxV = bb->max_voxels;
     SESSD_CUDA(cudaMemsetAsync(w.status, 0, kStatusInts * sizeof(int32_t), stream));
     int rc = launch_fill_ones(w.ones_base, w.ones_bytes, stream);

@@ -60,6 +60,10 @@ int sm_count();
 inline int persistent_grid(int per_sm) { return sm_count() * per_sm; }
 
 // Two-pass workspace layout: with base == nullptr it only measures.
+// A caller's workspace must start on a kAlign boundary (cudaMalloc and TensorRT workspaces do): the kernels use
+// 16- and 32-byte vector accesses relative to it.
+inline bool workspace_aligned(const void* p) { return reinterpret_cast<uintptr_t>(p) % kAlign == 0; }
+
 struct Bump {
     char* base;
     size_t off;

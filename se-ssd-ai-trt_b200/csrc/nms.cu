@@ -343,6 +343,7 @@ int sessd_rotated_nms_enqueue(const sessd_nms_params* p, int batch, const void* 
         return SESSD_ERR_NULL;
     if (!nms_params_ok(p, batch)) return SESSD_ERR_PARAM;
     if (workspace_bytes < sessd_rotated_nms_workspace_bytes(p, batch)) return SESSD_ERR_WORKSPACE;
+    if (!workspace_aligned(workspace)) return SESSD_ERR_PARAM;
     cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
     const size_t M = (size_t)p->max_box_num, words = (M + 63) / 64;
     Bump bump(workspace);

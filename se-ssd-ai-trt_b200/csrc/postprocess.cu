@@ -208,6 +208,7 @@ int run_filter(const sessd_anchor_params* ap, const sessd_filter_params* p, int 
             return SESSD_ERR_PARAM;
     }
     if (workspace_bytes < sessd_filter_boxes_workspace_bytes(p, batch)) return SESSD_ERR_WORKSPACE;
+    if (!workspace_aligned(workspace)) return SESSD_ERR_PARAM;
     cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
     FilterArgs a{};
     a.boxes = static_cast<const float*>(inputs[0]);

@@ -372,3 +372,25 @@ def test_sparse2dense_plugin_entry(gpu, oracle, dtype):
     want = oracle.sparse2dense(src, coors[0], 300, Cc, D, H, W, batch=1)
     np.testing.assert_array_equal(dense[0].float().cpu().numpy(), want[0])
     assert not dense[1].any()
+
+
+def test_misaligned_workspace_is_refused(gpu):
+    """A workspace that does not start on a 256-byte boundary is refused before any kernel runs (the kernels
+    use 16- and 32-byte vector accesses relative to it)."""
+    import torch
+
+    case = mk.small_case(gpu)
+    bb = gpu.Backbone(case["max_voxels"], case["weights"], case["scale"], case["shift"], dtype=1,
+                      layers=case["layers"], point_range=case["range"], voxel_size=case["voxel"])
+    pts = torch.from_numpy(case["points"]).cuda()[None]
+    sizes = torch.tensor([pts.shape[1]], dtype=torch.int32, device="cuda")
+    nbytes = bb.workspace_bytes(1, pts.shape[1])
+    raw = torch.empty(nbytes + 512, dtype=torch.uint8, device="cuda")
+    launches = gpu.launch_count()
+    with pytest.raises(gpu.SessdError):
+        bb.run(pts, sizes, workspace=raw[16:16 + nbytes])
+    assert gpu.launch_count() == launches
+    dense, ws = bb.run(pts, sizes, workspace=raw[256:256 + nbytes])
+    torch.cuda.synchronize()
+    assert gpu.read_status(ws) == 0
+    bb.close()
