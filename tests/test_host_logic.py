@@ -96,3 +96,27 @@ def test_two_ranks_shard_frames_and_reduce_time_over_gloo():
         assert value == pytest.approx(12 / 0.015)
         flat = [s for seeds in gathered for s in seeds]
         assert len(set(flat)) == 6
+
+
+def test_reference_arm_prints_the_contract_line():
+    """`bench.py --impl reference` needs no GPU: one JSON line with the metric of the main arm, the CPU
+    baseline that produced it and an end-to-end object that repeats the value with no device copies."""
+    import json
+    import os
+    import subprocess
+    import sys
+
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    out = subprocess.run([sys.executable, os.path.join(root, "bench.py"), "--impl", "reference", "--workload", "single",
+                          "--frames", "4", "--steps", "1", "--warmup", "0"], capture_output=True, text=True, timeout=600)
+    assert out.returncode == 0, out.stderr[-2000:]
+    line = json.loads(out.stdout.strip().splitlines()[-1])
+    for key in ("metric", "value", "unit", "n_gpus", "steps", "warmup", "ms_per_step", "higher_is_better", "scaling",
+                "vs_baseline", "dtype", "data", "config", "cpu_baseline", "e2e", "impl"):
+        assert key in line, key
+    assert line["impl"] == "reference" and line["unit"] == "frames/s" and line["value"] > 0
+    assert line["vs_baseline"] is None and line["higher_is_better"] is True and line["data"] == "synthetic"
+    assert line["config"]["workload"] == "single"
+    base = line["cpu_baseline"]
+    assert base["kind"] == "port" and base["cores"] >= 1 and base["value"] == line["value"] and base["sample"]
+    assert line["e2e"] == dict(value=line["value"], unit=line["unit"], h2d_bytes_per_step=0, d2h_bytes_per_step=0)
