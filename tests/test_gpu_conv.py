@@ -72,7 +72,8 @@ def _check_layer(gpu, oracle, layer, frames, W, scale=None, shift=None, relu=Fal
         n = len(c)
         assert g["status"] == 0
         if layer.subm:
-            pairs, pnum, st = oracle.subm_rulebook(c, n, layer.out_shape, maxV)
+            pairs, pnum, st = oracle.subm_rulebook(c, n, layer.out_shape, maxV, ksize=layer.ksize[0],
+                                                   padding=layer.padding[0])
             oc, on = c, n
         else:
             oc, on, pairs, pnum, st = oracle.spconv_rulebook(c, n, layer.ksize, layer.stride, layer.padding,
@@ -122,6 +123,21 @@ def test_subm_all_channel_pairs(gpu, oracle, cin, cout, dtype):
     layer = _layer(gpu, True, cin, cout, (3, 3, 3), (1, 1, 1), (1, 1, 1), shape)
     _check_layer(gpu, oracle, layer, frames, W, dtype=dtype)
     _check_layer(gpu, oracle, layer, frames, W, sc, sh, True, dtype=dtype)
+
+
+@pytest.mark.parametrize("ksize,pad,cin,cout,dtype", [(1, 0, 16, 16, 0), (1, 0, 32, 32, 1), (3, 0, 16, 16, 0),
+                                                      (2, 0, 16, 32, 1)])
+def test_subm_other_kernel_sizes_take_the_generic_map_path(gpu, oracle, ksize, pad, cin, cout, dtype):
+    """Submanifold layers whose kernel is not 3x3x3 / padding 1 build their neighbour map from a flat coordinate
+    table (one look-up per offset and output row) and their tile masks in a pass of their own; the reference's
+    plugin accepts any cubic kernel (submConv3dlayer.cu:271-358 takes ksize and padding as run-time values)."""
+    rs = np.random.RandomState(40 + ksize * 7 + cin)
+    shape = (6, 20, 24)
+    frames = [(_random_coords(rs, n, shape), None) for n in (800, 130)]
+    frames = [(c, rs.randn(len(c), cin).astype(np.float32)) for c, _ in frames]
+    W = (rs.randn(ksize ** 3, cin, cout) / np.sqrt(2 * cin)).astype(np.float32)
+    layer = _layer(gpu, True, cin, cout, (ksize,) * 3, (1, 1, 1), (pad,) * 3, shape)
+    _check_layer(gpu, oracle, layer, frames, W, dtype=dtype)
 
 
 STRIDED = [

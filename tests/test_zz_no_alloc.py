@@ -3,9 +3,9 @@
 Hosts whose device memory is fixed before the library runs (a pre-sized plugin arena, a real-time loop
 that must stay away from the allocator) cannot provide a workspace; this entry point keeps its scratch
 in a device array inside the library. The test calls it through the C ABI twice in a row, with different
-inputs, and requires outputs identical to those of the regular entry point (the array keeps the first
-call's contents, so the second call proves that everything that must start clean is reset). The file is
-named so that pytest collects it last.
+inputs, and requires outputs identical to those of the regular entry point and to those of the CPU oracle
+(the array keeps the first call's contents, so the second call proves that everything that must start
+clean is reset). The file is named so that pytest collects it last.
 """
 import ctypes as C
 
@@ -31,7 +31,7 @@ def _call_static(gpu, params, pts, sizes, out_dtype=0):
     return rc, voxels.cpu().numpy(), coors.cpu().numpy(), num.cpu().numpy()
 
 
-def test_static_scratch_voxeliser_matches_regular_entry_point_twice(gpu):
+def test_static_scratch_voxeliser_matches_regular_entry_point_twice(gpu, oracle):
     import torch
 
     params = gpu.voxel_params(20000)
@@ -49,6 +49,13 @@ def test_static_scratch_voxeliser_matches_regular_entry_point_twice(gpu):
         np.testing.assert_array_equal(coors, ref["coors"].cpu().numpy())
         np.testing.assert_allclose(voxels, ref["voxels"].cpu().numpy(), rtol=1e-5, atol=0)
         assert int(num[0]) > 10000
+        # and directly against the CPU oracle (voxelGenerator.cu:348-451, :255-321 restated): same rows in the
+        # same order, same means
+        ovox, ocoors, _, on, ost = oracle.voxelize(f, gpu.synth.POINT_RANGE, gpu.synth.VOXEL_SIZE, params.max_voxels)
+        assert ost == 0 and int(num[0]) == on
+        np.testing.assert_array_equal(coors[0, :on], ocoors[:on])
+        np.testing.assert_allclose(voxels[0, :on], ovox[:on], rtol=1e-5, atol=0)
+        assert not coors[0, on:].any() and not voxels[0, on:].any()
 
 
 def test_static_scratch_rejects_requests_beyond_its_size(gpu):
