@@ -80,13 +80,12 @@ struct ConvWorkspace {
     void* ones_base;      // tables: every word 0xFFFFFFFF before use
     size_t ones_bytes;
     Buckets buckets;      // submanifold 3x3x3: x-grouped table of the input coordinates
-    Table in_table;       // other submanifold geometries: flat table of the input coordinates
-    Table out_table;      // strided: flat table of the output coordinates (keys, rank, vals)
-    uint32_t* tile_mask;  // [B][tiles], zero before use
-    size_t tile_mask_bytes;
-    int32_t* slot_of;
+    Table in_table;       // every other layer: flat table of the input coordinates
+    BitGrid out_bits;     // strided: occupancy grid of the output level
+    void* zero_base;      // occupancy grid + tile masks: zero before use
+    size_t zero_bytes;
+    uint32_t* tile_mask;  // [B][tiles]
     int32_t* chunk_counts;
-    int chunks;
     int32_t* nbr;
 };
 
@@ -107,19 +106,22 @@ void conv_workspace_layout(Bump& bump, const sessd_conv_params* p, const ConvGeo
         w->ones_base = block;
         w->ones_bytes = per * 2 * sizeof(uint32_t);
     } else {
-        uint32_t* block = bump.take<uint32_t>(per * 3);
-        // 64-bit slots (key << 32 | rank) followed by the row ids
-        w->out_table = Table{block ? block + 1 : nullptr, block, reinterpret_cast<int32_t*>(block ? block + 2 * per : nullptr),
-                             cap, shift, 2, 2};
+        uint32_t* block = bump.take<uint32_t>(per * 2);
+        w->in_table = Table{block, nullptr, reinterpret_cast<int32_t*>(block ? block + per : nullptr), cap, shift, 1, 1};
         w->ones_base = block;
-        w->ones_bytes = per * 3 * sizeof(uint32_t);
-        w->slot_of = bump.take<int32_t>((size_t)batch * p->max_voxels * g.ncand);
-        w->chunks = spconv_chunks_per_frame(p->max_voxels, g);
-        w->chunk_counts = bump.take<int32_t>((size_t)batch * w->chunks);
+        w->ones_bytes = per * 2 * sizeof(uint32_t);
+        w->out_bits = bitgrid_shape(g.out_shape);
+        w->chunk_counts = bump.take<int32_t>((size_t)batch * w->out_bits.chunks);
     }
+    // occupancy grid (strided layers) and tile masks in one block, reset to zero by a single fill
     const size_t tiles = (size_t)(p->max_voxels + 127) / 128;
-    w->tile_mask_bytes = (batch * tiles * sizeof(uint32_t) + 15) / 16 * 16;
-    w->tile_mask = bump.take<uint32_t>(w->tile_mask_bytes / sizeof(uint32_t));
+    const size_t mask_bytes = (batch * tiles * sizeof(uint32_t) + 15) / 16 * 16;
+    const size_t grid_bytes = p->subm ? 0 : (size_t)batch * w->out_bits.words * sizeof(uint4);
+    char* zero = bump.take<char>(grid_bytes + mask_bytes);
+    w->zero_base = zero;
+    w->zero_bytes = grid_bytes + mask_bytes;
+    w->out_bits.rec = reinterpret_cast<uint4*>(zero);
+    w->tile_mask = reinterpret_cast<uint32_t*>(zero ? zero + grid_bytes : nullptr);
     w->nbr = bump.take<int32_t>((size_t)batch * g.kvol * p->max_voxels);
 }
 
@@ -178,8 +180,8 @@ struct BackboneWorkspace {
     VoxelWorkspace vox;
     void* voxel_feat;
     std::vector<int32_t*> coors, num;
-    std::vector<Table> tables;       // flat output tables of the derived levels (index 0 unused)
-    std::vector<Buckets> buckets;    // x-grouped tables of the levels that feed submanifold layers
+    std::vector<BitGrid> bits;       // occupancy grids of the derived levels (index 0 unused)
+    Buckets buckets0;                // x-grouped table of the voxeliser's rows (level 0)
     void* ones_base;
     size_t ones_bytes;
     std::vector<int32_t*> nbr_subm;
@@ -188,9 +190,7 @@ struct BackboneWorkspace {
     void* zero_base;
     size_t zero_bytes;
     int32_t* nbr_strided;
-    int32_t* slot_of;
     int32_t* chunk_counts;
-    int chunks;
     std::vector<void*> feat;
 };
 
@@ -202,8 +202,7 @@ void backbone_layout(Bump& bump, const sessd_backbone* bb, int batch, int max_po
     w->voxel_feat = bump.take<char>((size_t)batch * maxV * 4 * esize(bb->dtype));
     w->coors.assign(bb->nlevels, nullptr);
     w->num.assign(bb->nlevels, nullptr);
-    w->tables.assign(bb->nlevels, Table{});
-    w->buckets.assign(bb->nlevels, Buckets{});
+    w->bits.assign(bb->nlevels, BitGrid{});
     w->nbr_subm.assign(bb->nlevels, nullptr);
     w->mask_subm.assign(bb->nlevels, nullptr);
     w->mask_layer.assign(bb->layers.size(), nullptr);
@@ -211,39 +210,35 @@ void backbone_layout(Bump& bump, const sessd_backbone* bb, int batch, int max_po
         w->coors[l] = bump.take<int32_t>((size_t)batch * maxV * 4);
         w->num[l] = bump.take<int32_t>(batch);
     }
-    // one contiguous block of tables, reset to 0xFF by a single fill
-    const uint32_t cap = pow2_at_least(2ull * (uint64_t)maxV);
+    // the x-grouped table of level 0, reset to 0xFF by one fill (the voxeliser resets its own table)
     const uint32_t capb = pow2_at_least((uint64_t)maxV);
-    const size_t per = (size_t)batch * cap, perb = (size_t)batch * capb * 8;
-    size_t words = 0;
-    for (int l = 1; l < bb->nlevels; ++l) words += per * 3;
-    for (int l = 0; l < bb->nlevels; ++l)
-        if (bb->level_has_subm[l]) words += perb;
-    uint32_t* block = bump.take<uint32_t>(words + 4);
+    const size_t perb = (size_t)batch * capb * 8;
+    uint32_t* block = bump.take<uint32_t>(perb + 4);
+    w->buckets0 = Buckets{block, capb, 32 - ilog2(capb)};
     w->ones_base = block;
-    w->ones_bytes = words * sizeof(uint32_t);
-    size_t off = 0;
-    for (int l = 1; l < bb->nlevels; ++l) {
-        uint32_t* base = block ? block + off : nullptr;
-        // 64-bit slots (key << 32 | rank) followed by the row ids
-        w->tables[l] = Table{base ? base + 1 : nullptr, base, reinterpret_cast<int32_t*>(base ? base + 2 * per : nullptr),
-                             cap, 32 - ilog2(cap), 2, 2};
-        off += per * 3;
-    }
-    for (int l = 0; l < bb->nlevels; ++l)
-        if (bb->level_has_subm[l]) {
-            w->buckets[l] = Buckets{block ? block + off : nullptr, capb, 32 - ilog2(capb)};
-            off += perb;
-        }
-    // tile masks, reset to zero by a single fill
+    w->ones_bytes = perb * sizeof(uint32_t);
+    // occupancy grids of the derived levels and all tile masks in one block, reset to zero by one fill
     const size_t tiles = (size_t)(maxV + 127) / 128;
     const size_t mask_words = (batch * tiles + 3) / 4 * 4;
     size_t nmasks = 0;
     for (int l = 0; l < bb->nlevels; ++l) nmasks += bb->level_has_subm[l] ? 1 : 0;
     for (auto& L : bb->layers) nmasks += L.p.subm ? 0 : 1;
-    uint32_t* masks = bump.take<uint32_t>(mask_words * nmasks + 4);
-    w->zero_base = masks;
-    w->zero_bytes = mask_words * nmasks * sizeof(uint32_t);
+    size_t grid_recs = 0;
+    int chunks_max = 1;
+    for (int l = 1; l < bb->nlevels; ++l) {
+        w->bits[l] = bitgrid_shape(&bb->level_shape[3 * l]);
+        grid_recs += (size_t)batch * w->bits[l].words;
+        if (w->bits[l].chunks > chunks_max) chunks_max = w->bits[l].chunks;
+    }
+    char* zero = bump.take<char>(grid_recs * sizeof(uint4) + mask_words * nmasks * sizeof(uint32_t) + 16);
+    w->zero_base = zero;
+    w->zero_bytes = grid_recs * sizeof(uint4) + mask_words * nmasks * sizeof(uint32_t);
+    size_t off = 0;
+    for (int l = 1; l < bb->nlevels; ++l) {
+        w->bits[l].rec = reinterpret_cast<uint4*>(zero ? zero + off : nullptr);
+        off += (size_t)batch * w->bits[l].words * sizeof(uint4);
+    }
+    uint32_t* masks = reinterpret_cast<uint32_t*>(zero ? zero + off : nullptr);
     size_t mi = 0;
     for (int l = 0; l < bb->nlevels; ++l)
         if (bb->level_has_subm[l]) w->mask_subm[l] = masks ? masks + mask_words * mi++ : (mi++, nullptr);
@@ -252,9 +247,7 @@ void backbone_layout(Bump& bump, const sessd_backbone* bb, int batch, int max_po
     for (int l = 0; l < bb->nlevels; ++l)
         if (bb->level_has_subm[l]) w->nbr_subm[l] = bump.take<int32_t>((size_t)batch * 27 * maxV);
     w->nbr_strided = bump.take<int32_t>((size_t)batch * (bb->kvol_strided_max > 0 ? bb->kvol_strided_max : 1) * maxV);
-    w->slot_of = bump.take<int32_t>((size_t)batch * maxV * (bb->ncand_max > 0 ? bb->ncand_max : 1));
-    w->chunks = (int)(((int64_t)maxV * (bb->ncand_max > 0 ? bb->ncand_max : 1) + kChunk - 1) / kChunk);
-    w->chunk_counts = bump.take<int32_t>((size_t)batch * w->chunks);
+    w->chunk_counts = bump.take<int32_t>((size_t)batch * chunks_max);
     w->feat.assign(bb->layers.size(), nullptr);
     for (size_t i = 0; i < bb->layers.size(); ++i)
         w->feat[i] = bump.take<char>((size_t)batch * maxV * bb->layers[i].p.out_channel * esize(bb->dtype));
@@ -462,7 +455,7 @@ static int conv_enqueue_common(const sessd_conv_params* p, const sessd_conv_weig
     SESSD_CUDA(cudaMemsetAsync(ws.status, 0, kStatusInts * sizeof(int32_t), stream));
     rc = launch_fill_ones(ws.ones_base, ws.ones_bytes, stream);
     if (rc) return rc;
-    rc = launch_fill_zero(ws.tile_mask, ws.tile_mask_bytes, stream);
+    rc = launch_fill_zero(ws.zero_base, ws.zero_bytes, stream);
     if (rc) return rc;
     const int32_t* out_num = in_num;
     if (subm && is_subm_333(g)) {
@@ -478,13 +471,20 @@ static int conv_enqueue_common(const sessd_conv_params* p, const sessd_conv_weig
         rc = launch_tile_mask(ws.nbr, in_num, batch, maxV, g.kvol, ws.tile_mask, stream);
         if (rc) return rc;
     } else {
-        rc = launch_spconv_outputs(in_coors, in_num, batch, maxV, g, ws.out_table, ws.slot_of, ws.chunk_counts,
-                                   ws.chunks, static_cast<int32_t*>(outputs[1]), static_cast<int32_t*>(outputs[2]),
-                                   ws.status, stream);
+        // the caller's input rows come in any order: a flat table turns coordinates back into rows
+        rc = launch_table_build(in_coors, in_num, batch, maxV, g.in_shape, ws.in_table, ws.status, stream);
+        if (rc) return rc;
+        rc = launch_mark_outputs(in_coors, in_num, batch, maxV, g, ws.out_bits, stream);
+        if (rc) return rc;
+        rc = launch_number_outputs(ws.out_bits, batch, maxV, ws.chunk_counts, static_cast<int32_t*>(outputs[1]),
+                                   static_cast<int32_t*>(outputs[2]), ws.status, stream);
         if (rc) return rc;
         out_num = static_cast<const int32_t*>(outputs[2]);
-        rc = launch_nbr_scatter_strided(in_coors, in_num, out_num, batch, maxV, g, ws.out_table, ws.slot_of, ws.nbr,
-                                        ws.tile_mask, stream);
+        InputIndex idx{};
+        idx.kind = 2;
+        idx.table = ws.in_table;
+        rc = launch_map_rows(static_cast<const int32_t*>(outputs[1]), out_num, batch, maxV, g, idx, ws.nbr, ws.tile_mask,
+                             stream);
         if (rc) return rc;
     }
     ConvLaunch c{};
@@ -707,32 +707,53 @@ static int backbone_enqueue_impl(const sessd_backbone* bb, int batch, int max_po
                       /*zero_tail=*/false, stream);
     if (rc) return rc;
     std::vector<char> nbr_ready(bb->nlevels, 0);
+    bool buckets0_ready = false;
+    // how the rows of a level are found from coordinates: level 0 through the x-grouped table of the
+    // voxeliser's rows, every derived level through the occupancy grid that numbered it
+    auto input_index = [&](int level, InputIndex* idx) -> int {
+        *idx = InputIndex{};
+        if (level > 0) {
+            idx->kind = 0;
+            idx->bits = w.bits[level];
+            return SESSD_OK;
+        }
+        idx->kind = 1;
+        idx->buckets = w.buckets0;
+        if (buckets0_ready) return SESSD_OK;
+        buckets0_ready = true;
+        return launch_bucket_build(w.coors[0], w.num[0], batch, maxV, &bb->level_shape[0], w.buckets0, w.status, stream);
+    };
     const void* cur = w.voxel_feat;
     for (size_t i = 0; i < bb->layers.size(); ++i) {
         const sessd_backbone::Layer& L = bb->layers[i];
         const int32_t* nbr;
         const uint32_t* tile_mask;
+        InputIndex idx;
         if (L.p.subm) {
             if (!nbr_ready[L.level_in]) {
-                rc = launch_bucket_build(w.coors[L.level_in], w.num[L.level_in], batch, maxV, L.g.in_shape,
-                                         w.buckets[L.level_in], w.status, stream);
+                rc = input_index(L.level_in, &idx);
                 if (rc) return rc;
-                rc = launch_nbr_build_subm(w.coors[L.level_in], w.num[L.level_in], batch, maxV, L.g.in_shape,
-                                           w.buckets[L.level_in], w.nbr_subm[L.level_in], w.mask_subm[L.level_in],
-                                           stream);
+                if (L.level_in == 0)
+                    rc = launch_nbr_build_subm(w.coors[0], w.num[0], batch, maxV, L.g.in_shape, w.buckets0, w.nbr_subm[0],
+                                               w.mask_subm[0], stream);
+                else
+                    rc = launch_map_rows(w.coors[L.level_in], w.num[L.level_in], batch, maxV, L.g, idx,
+                                         w.nbr_subm[L.level_in], w.mask_subm[L.level_in], stream);
                 if (rc) return rc;
                 nbr_ready[L.level_in] = 1;
             }
             nbr = w.nbr_subm[L.level_in];
             tile_mask = w.mask_subm[L.level_in];
         } else {
-            rc = launch_spconv_outputs(w.coors[L.level_in], w.num[L.level_in], batch, maxV, L.g, w.tables[L.level_out],
-                                       w.slot_of, w.chunk_counts, w.chunks, w.coors[L.level_out], w.num[L.level_out],
-                                       w.status, stream);
+            rc = launch_mark_outputs(w.coors[L.level_in], w.num[L.level_in], batch, maxV, L.g, w.bits[L.level_out], stream);
             if (rc) return rc;
-            rc = launch_nbr_scatter_strided(w.coors[L.level_in], w.num[L.level_in], w.num[L.level_out], batch, maxV,
-                                            L.g, w.tables[L.level_out], w.slot_of, w.nbr_strided, w.mask_layer[i],
-                                            stream);
+            rc = launch_number_outputs(w.bits[L.level_out], batch, maxV, w.chunk_counts, w.coors[L.level_out],
+                                       w.num[L.level_out], w.status, stream);
+            if (rc) return rc;
+            rc = input_index(L.level_in, &idx);
+            if (rc) return rc;
+            rc = launch_map_rows(w.coors[L.level_out], w.num[L.level_out], batch, maxV, L.g, idx, w.nbr_strided,
+                                 w.mask_layer[i], stream);
             if (rc) return rc;
             nbr = w.nbr_strided;
             tile_mask = w.mask_layer[i];

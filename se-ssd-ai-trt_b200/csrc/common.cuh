@@ -117,6 +117,25 @@ struct Buckets {
     int shift;      // 32 - log2(cap)
 };
 
+// Occupancy grid of one resolution level: frame b owns records [b*words, (b+1)*words); record w covers the 64 cells
+// x = 64*(w % xw) .. +63 of line (z, y) = w / xw and holds {bits lo, bits hi, rows before this word, unused}.
+// Rows are numbered in record order, i.e. in (z, y, x) order.
+struct BitGrid {
+    uint4* rec;
+    int Z, Y, X;
+    int xw;      // records per x line
+    int words;   // records per frame
+    int chunks;  // 1024-record chunks per frame
+};
+inline BitGrid bitgrid_shape(const int shape[3]) {
+    BitGrid g{};
+    g.Z = shape[0], g.Y = shape[1], g.X = shape[2];
+    g.xw = (g.X + 63) / 64;
+    g.words = g.Z * g.Y * g.xw;
+    g.chunks = (g.words + kChunk - 1) / kChunk;
+    return g;
+}
+
 // Geometry of one sparse convolution (z, y, x order everywhere).
 struct ConvGeom {
     int K[3], S[3], P[3];
@@ -223,24 +242,29 @@ int launch_table_build(const int32_t* coors, const int32_t* voxel_num, int batch
                        const Table& t, int32_t* status, cudaStream_t stream);
 int launch_nbr_build(const int32_t* out_coors, const int32_t* out_num, int batch, int max_voxels, const ConvGeom& g,
                      const Table& in_table, int32_t* nbr, cudaStream_t stream);
-int launch_spconv_outputs(const int32_t* in_coors, const int32_t* in_num, int batch, int max_voxels, const ConvGeom& g,
-                          const Table& out_table, int32_t* slot_of, int32_t* chunk_counts, int chunks_per_frame,
-                          int32_t* out_coors, int32_t* out_num, int32_t* status, cudaStream_t stream);
+// Strided layers: set the bit of every candidate output, then number the set bits in (z, y, x) order.
+int launch_mark_outputs(const int32_t* in_coors, const int32_t* in_num, int batch, int max_voxels, const ConvGeom& g,
+                        const BitGrid& out, cudaStream_t stream);
+int launch_number_outputs(const BitGrid& out, int batch, int max_voxels, int32_t* chunk_counts, int32_t* out_coors,
+                          int32_t* out_num, int32_t* status, cudaStream_t stream);
+// How the rows of a layer's input level are found from coordinates: 0 = occupancy grid, 1 = x-grouped table,
+// 2 = flat table.
+struct InputIndex {
+    int kind;
+    BitGrid bits;
+    Buckets buckets;
+    Table table;
+};
+// Neighbour map + tile masks of a layer (any kernel up to 3x3x3, any stride) from its output rows.
+int launch_map_rows(const int32_t* out_coors, const int32_t* out_num, int batch, int max_voxels, const ConvGeom& g,
+                    const InputIndex& in, int32_t* nbr, uint32_t* tile_mask, cudaStream_t stream);
 int launch_bucket_build(const int32_t* coors, const int32_t* voxel_num, int batch, int max_voxels, const int shape[3],
                         const Buckets& t, int32_t* status, cudaStream_t stream);
 // 3x3x3 / stride 1 / pad 1 neighbour map from a bucket table, plus the per-128-row-tile offset masks.
 int launch_nbr_build_subm(const int32_t* coors, const int32_t* voxel_num, int batch, int max_voxels, const int shape[3],
                           const Buckets& t, int32_t* nbr, uint32_t* tile_mask, cudaStream_t stream);
-// Neighbour map of a strided layer from the candidate entries left by launch_spconv_outputs.
-int launch_nbr_scatter_strided(const int32_t* in_coors, const int32_t* in_num, const int32_t* out_num, int batch,
-                               int max_voxels, const ConvGeom& g, const Table& out_table, const int32_t* slot_of,
-                               int32_t* nbr, uint32_t* tile_mask, cudaStream_t stream);
 int launch_tile_mask(const int32_t* nbr, const int32_t* out_num, int batch, int max_voxels, int kvol,
                      uint32_t* tile_mask, cudaStream_t stream);
-inline int spconv_chunks_per_frame(int max_voxels, const ConvGeom& g) {
-    return (int)(((int64_t)max_voxels * g.ncand + kChunk - 1) / kChunk);
-}
-
 // conv_simt.cu
 struct ConvLaunch {
     const void* in;        // [B][max_voxels][Cin]

@@ -1,34 +1,35 @@
 // Sparse convolution as an implicit GEMM on the 5th-generation tensor cores (tcgen05 + TMEM).
 //
 // Replaces, for fp16 features and 16/32/64 channels, the reference's per-offset scalar kernel
-// (submConv3dlayer.cu:479-518, launched kvol times per layer, :632-638). One CTA owns a tile of 128
-// output rows. For every group of kernel offsets it gathers the 128 neighbour rows into shared
-// memory as a K-major, 128-byte-swizzled A operand (one 128-byte row per output row: 64/Cin offsets
-// side by side, missing neighbours zero-filled), streams the matching pre-tiled weight block as the B
-// operand with a bulk asynchronous copy, and issues tcgen05.mma (M=128, N=Cout, K=16 x 4) into one
-// fp32 accumulator in tensor memory that stays resident across all offsets. A CTA iteration covers
-// four such tiles (512 rows, four accumulators) with the offset loop outermost, so that a weight block
-// is fetched once per four tiles; (tile, offset group) pairs without any neighbour are skipped using
-// the per-tile offset masks the rulebook kernels produce. The epilogue reads the
-// accumulator with tcgen05.ld, applies the folded BatchNorm scale/shift and ReLU, and stores fp16
-// rows (and, for the last layer, scatters them into the dense BEV map).
+// (submConv3dlayer.cu:479-518, launched kvol times per layer, :632-638). A tile is 128 output rows. For
+// every group of kernel offsets ("stage": 64/Cin offsets side by side) the 128 neighbour rows are gathered
+// into shared memory as a K-major, 128-byte-swizzled A operand (one 128-byte row per output row, missing
+// neighbours zero-filled), the matching pre-tiled weight block is streamed in as the B operand with a bulk
+// asynchronous copy, and tcgen05.mma (M = 128, N = Cout, K = 16 x 4) accumulates into an fp32 accumulator in
+// tensor memory that stays resident across all offsets. A CTA iteration ("group") covers four tiles with
+// the offset loop outermost, so that a weight block is fetched once per four tiles; (tile, stage) pairs
+// without any neighbour are skipped using the per-tile offset masks the rulebook kernels produce. The
+// epilogue reads the accumulator with tcgen05.ld, applies the folded BatchNorm scale/shift and ReLU, and
+// stores fp16 rows (and, for the last layer, scatters them into the dense BEV map).
 //
-// Warp roles (256 threads, two CTAs per SM, about 85 KB of shared memory and at most 104 registers per
-// thread, which leaves room for other streams' kernels on the same SM):
-//   warps 0-3  gather. The ring has one 16 KB slot per gather warp; ring position q lives in slot q % 4
-//              and is filled by warp q % 4 alone with 32 sixteen-byte cp.async per lane group. A warp's
-//              cp.async issue rate is bound by latency (about 46 cycles per instruction), so the warps
-//              work on four different stages at once rather than sharing one; the copies publish the
-//              stage themselves (cp.async mbarrier arrival). After the group's last stage the four warps
-//              run the epilogue (each can read its quarter of the tensor-memory lanes).
-//   warps 4, 7 issue the MMAs of the even / odd row tiles from one thread each (one issue costs the
-//              thread about 76 cycles, a commit about 156). Each issuer has its own "landed" barrier
-//              per slot: a parity wait is only safe for a waiter that has seen every earlier phase.
-//   warp 5     streams the weight blocks (cp.async.bulk), warp 6 prefetches the neighbour indices of
-//              upcoming stages into a small shared-memory ring.
+// One persistent CTA per SM; every role has warps of its own and walks the same sequence of groups:
+//   warps 0-3    epilogue (warp w reads tensor-memory lanes 32w .. 32w+31). The accumulators are double
+//                buffered (2 sets x 4 tiles x Cout columns), so the epilogue of one group runs while the
+//                other roles are already working on the next group.
+//   warps 4-7    MMA issuers, one thread each; issuer t owns tile t of every group. Issuing costs the
+//                thread on the order of a hundred cycles per tcgen05.mma / commit, so four threads share it.
+//   warp  8      streams the weight blocks (cp.async.bulk) into a two-slot ring.
+//   warp  9      prefetches the neighbour indices of upcoming (tile, stage) items into shared memory.
+//   warps 10..   gather. The A ring has one 16 KB slot per gather warp: item q (the q-th (tile, stage) pair
+//                of the CTA's life) lives in slot q % NSLOT and is filled by warp q % NSLOT alone with
+//                sixteen-byte cp.async copies that publish the slot themselves (mbarrier arrival of the
+//                copies). With 11-12 slots in flight the latency chain of one slot (issue, landing, MMA,
+//                commit) is covered and no barrier is shared between gather warps.
+// Every barrier has one waiting role that sees each of its phases in order (a parity wait is only safe
+// then): a_full exists per (issuer, slot), index blocks are tied to the A slot of the same gather warp.
 // A CTA walks an equal share of all occupied row tiles (row counts are read on the device). Every wait is
-// bounded by a clock limit, after which the CTA raises SESSD_STATUS_TIMEOUT (and reports which wait in
-// the status block), stops issuing work, frees its tensor memory and returns.
+// bounded by a clock limit, after which the CTA raises SESSD_STATUS_TIMEOUT (and reports which wait in the
+// status block), stops issuing work, waits for its own copies and MMAs, frees its tensor memory and returns.
 #include <atomic>
 #include <cstdlib>
 #include <string>
@@ -41,25 +42,29 @@ namespace sessd {
 namespace {
 
 constexpr int TILE_M = 128;
-constexpr int MMA_WARPS_MAX = 2;
-constexpr int TILES = 4;                     // row tiles per CTA iteration; they share each weight block
-constexpr int GATHER_WARPS = 4;               // warps 0-3: gather, later epilogue
-constexpr int A_STAGES_MAX = GATHER_WARPS;
+constexpr int TILES = 4;                     // row tiles per group; they share each weight block
+constexpr int EPI_WARPS = 4;                 // warps 0-3
+constexpr int MMA_WARPS = TILES;             // warps 4-7: issuer t owns tile t
+constexpr int WEIGHT_WARP = EPI_WARPS + MMA_WARPS;
+constexpr int INDEX_WARP = WEIGHT_WARP + 1;
+constexpr int FIRST_GATHER_WARP = INDEX_WARP + 1;
+constexpr int NSLOT_MAX = 12;
+constexpr int NIDX_MAX = 36;
 constexpr int B_STAGES = 2;
-// One gather stage (16 KB) per gather warp: ring position q lives in slot q % 4 and is filled by warp q % 4, so
-// every barrier of a slot has one producer warp that uses it in order. With the weight ring (2 x Cout x 128 B),
-// the index ring and the control block a CTA takes about 85 KB of shared memory; two CTAs fit one SM.
-constexpr int IDX_STAGES = 6;                // ring of neighbour-index blocks, filled ahead by the index warp
-template <int CIN, int COUT>
-struct RingCfg {
-    static constexpr int A_STAGES = GATHER_WARPS;
-};
 constexpr int ROW_BYTES = 128;               // 64 halves per A/B row
 constexpr int A_BYTES = TILE_M * ROW_BYTES;  // 16 KB
-constexpr int UMMA_THREADS = 256;
-constexpr int MMA_WARPS = 2;                 // MMA issuer warps (4 and 7); one takes the even row tiles, the other the odd ones
 constexpr int KVOL_MAX = 27;
 constexpr long long WAIT_LIMIT_CYCLES = 200000000LL;   // about a tenth of a second; real waits are microseconds
+
+// Gather slots (= gather warps): as many as fit beside the weight ring and the index blocks.
+// The index ring is deeper than the A ring (index rows come from DRAM, several microseconds away under load):
+// block j = q % NIDX, with NIDX a multiple of NSLOT so that block j is always read by gather warp j % NSLOT.
+template <int CIN>
+struct Ring {
+    static constexpr int NSLOT = CIN == 64 ? 11 : 10;
+    static constexpr int NIDX = (CIN == 16 ? 2 : 3) * NSLOT;
+    static constexpr int THREADS = (FIRST_GATHER_WARP + NSLOT) * 32;
+};
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
@@ -98,13 +103,14 @@ __device__ __forceinline__ bool mbar_try_wait_parked(uint32_t bar, uint32_t pari
 }
 // Bounded wait: false when the phase did not complete within the clock limit or the CTA is aborting.
 // The polling loop is kept to a handful of instructions (abort flag and clock are looked at every 32
-// polls): the role warps spend most of their life here and must not take the issue slots of the warps
-// that feed the pipeline. RELAXED waits (roles with slack: weight and index prefetch) also sleep
-// between polls.
-template <bool RELAXED = false>
+// polls). RELAXED waits (roles with slack: weight and index prefetch) also sleep between polls. The MMA
+// issuers use the plain limit, every other role one and a half times that: when something upstream is
+// missing, the wait closest to the cause is the one that gets reported.
+template <bool RELAXED = false, bool ISSUER = false>
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int where = 0) {
     if (mbar_try_wait(bar, parity)) return true;
     const long long t0 = clock64();
+    const long long limit = ISSUER ? WAIT_LIMIT_CYCLES : WAIT_LIMIT_CYCLES + WAIT_LIMIT_CYCLES / 2;
     for (;;) {
 #pragma unroll 1
         for (int i = 0; i < 32; ++i) {
@@ -112,7 +118,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
             if (mbar_try_wait_parked(bar, parity, 1000u)) return true;
         }
         if (*abort_flag) return false;
-        if (clock64() - t0 > WAIT_LIMIT_CYCLES) {
+        if (clock64() - t0 > limit) {
             if (*abort_flag == 0) abort_flag[1] = where;   // abort_where follows abort_flag in SharedCtl
             *abort_flag = 1;
             return false;
@@ -122,10 +128,6 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
 
 __device__ __forceinline__ void cp_async_16(uint32_t dst, const void* src, uint32_t src_bytes) {
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
-}
-template <int N>
-__device__ __forceinline__ void cp_async_wait() {
-    asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
 }
 // 16-byte copy that writes zeros instead when index < 0 (the source address is then not touched).
 __device__ __forceinline__ void cp_async_16_or_zero(uint32_t dst, const void* src, int index) {
@@ -153,7 +155,8 @@ __device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_
 
 // Shared-memory matrix descriptor, K-major, 128-byte swizzle: rows of 128 bytes, groups of 8 rows 1024
 // bytes apart (stride byte offset), leading byte offset unused by swizzled K-major layouts (set to 1),
-// descriptor version 1, layout type 2 (SWIZZLE_128B).
+// descriptor version 1, layout type 2 (SWIZZLE_128B). The start address sits in the low 14 bits in units
+// of 16 bytes, so stepping 32 bytes along K adds 2 to the descriptor.
 __device__ __forceinline__ uint64_t umma_desc(uint32_t saddr) {
     uint64_t d = 0;
     d |= (uint64_t)((saddr & 0x3FFFFu) >> 4);
@@ -181,6 +184,16 @@ __device__ __forceinline__ void umma_commit(uint32_t bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
 
+__device__ __forceinline__ bool elect_one() {
+    uint32_t pred;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "elect.sync _|p, 0xffffffff;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(pred));
+    return pred != 0;
+}
+
 __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
     asm volatile(
         "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
@@ -192,34 +205,33 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
 struct SharedCtl {
-    // a_full[i][s]: stage s has landed, for MMA issuer i (the issuer that owns the stage's row tile). One
-    // barrier per (issuer, slot) keeps a single consumer per barrier: parity waits are only safe when the
-    // waiter has itself seen every earlier phase complete.
-    unsigned long long a_full[MMA_WARPS_MAX][A_STAGES_MAX];
-    unsigned long long a_empty[A_STAGES_MAX];
+    // a_full[t][s]: slot s has landed, for the issuer of tile t. One barrier per (issuer, slot) keeps a single
+    // waiter per barrier: parity waits are only safe when the waiter has itself seen every earlier phase.
+    unsigned long long a_full[MMA_WARPS][NSLOT_MAX];
+    unsigned long long a_empty[NSLOT_MAX];   // the MMAs that read slot s have completed (commit of its issuer)
+    unsigned long long i_full[NIDX_MAX];     // index block j has landed
+    unsigned long long i_empty[NIDX_MAX];    // gather warp j % NSLOT has read index block j
     unsigned long long b_full[B_STAGES];
-    unsigned long long b_empty[B_STAGES];
-    unsigned long long i_full[IDX_STAGES];
-    unsigned long long i_empty[IDX_STAGES];
-    unsigned long long acc_full;
-    unsigned long long acc_empty;
-    unsigned long long mma_drain;   // aborting CTA only: completes when the issuers' outstanding MMAs have finished
+    unsigned long long b_empty[B_STAGES];    // every issuer has released the block (commit of its MMAs, or a plain arrival)
+    unsigned long long acc_full[2];          // every issuer has committed its tile of the group (per accumulator set)
+    unsigned long long acc_empty[2];         // the epilogue has read the set
+    unsigned long long mma_drain;            // aborting CTA only: completes when the issuers' outstanding MMAs have finished
     uint32_t tmem_base;
     int abort_flag;
     int abort_where;   // code of the first wait that ran out (role and ring position), for the status block
-    // per gather warp: the (stage << 2 | tile) pairs of the current group in ring order, so that a warp
-    // steps straight to the stages it owns
-    uint8_t stage_list[GATHER_WARPS][TILES * 32];
-#ifdef SESSD_UMMA_TIMING
-    long long t_issue[A_STAGES_MAX];    // when the gathers of the stage were issued
-    long long t_commit[A_STAGES_MAX];   // when the MMAs reading the stage were committed
-#endif
+    // per gather warp: the (stage << 2 | tile) codes of the current group's items in ring order, so that a warp
+    // steps straight to the items it owns
+    uint8_t stage_list[NSLOT_MAX][TILES * 32];
+    uint8_t idx_list[TILES * 32];            // the same list for the index warp
+    uint32_t scan_warp[32];                  // work split: per-warp totals of the block scan
+    int range_lo, range_hi;                  // work split: this CTA's tiles
+    uint32_t idx_uses[NIDX_MAX];             // bulk copies issued into index block j so far (for the abort path)
 };
 
 template <int CIN, int COUT>
 constexpr int umma_smem_bytes() {
-    return 1024 /*alignment slack*/ + RingCfg<CIN, COUT>::A_STAGES * A_BYTES + B_STAGES * COUT * ROW_BYTES +
-           IDX_STAGES * (64 / CIN) * TILE_M * 4 + 2 * COUT * 4 + (int)sizeof(SharedCtl);
+    return 1024 /*alignment slack*/ + Ring<CIN>::NSLOT * A_BYTES + B_STAGES * COUT * ROW_BYTES +
+           Ring<CIN>::NIDX * (64 / CIN) * TILE_M * 4 + 2 * COUT * 4 + (int)sizeof(SharedCtl);
 }
 
 // Offsets g*KG .. g*KG+KG-1 of a tile's 27-bit offset mask.
@@ -229,8 +241,7 @@ __device__ __forceinline__ bool stage_active(uint32_t kmask, int g) {
 }
 
 // Bit t set when row tile t has a neighbour under the offsets of stage g. The masks are only ever indexed
-// with compile-time constants, so they stay in registers (local memory would miss in the small L1 that
-// is left beside 200 KB of shared memory).
+// with compile-time constants, so they stay in registers.
 template <int KG>
 __device__ __forceinline__ uint32_t active_tiles(const uint32_t (&m)[TILES], int g) {
     uint32_t bits = 0;
@@ -239,7 +250,7 @@ __device__ __forceinline__ uint32_t active_tiles(const uint32_t (&m)[TILES], int
     return bits;
 }
 
-// Advances to the next (stage g, tile t) pair with work, in the order stage-major, tile-minor; `rem` holds
+// Advances to the next (stage g, tile t) item with work, in the order stage-major, tile-minor; `rem` holds
 // the tiles of stage g not yet visited. Start with g = -1, rem = 0.
 template <int KG>
 __device__ __forceinline__ bool next_item(const uint32_t (&m)[TILES], int nstages, int& g, uint32_t& rem, int& t) {
@@ -252,10 +263,16 @@ __device__ __forceinline__ bool next_item(const uint32_t (&m)[TILES], int nstage
     return true;
 }
 
-// Register cap well below what two resident CTAs (the shared-memory limit) could take: the rest of the
-// register file is what lets blocks of other kernels (other streams) run beside them.
+#ifdef SESSD_UMMA_TIMING
+#define TCLK() clock64()
+#define TADD(i, v) do { if (blockIdx.x == 0) tacc[i] += (unsigned long long)(v); } while (0)
+#else
+#define TCLK() 0LL
+#define TADD(i, v) do { } while (0)
+#endif
+
 template <int CIN, int COUT>
-__global__ void __maxnreg__(104)
+__global__ void __launch_bounds__(Ring<CIN>::THREADS, 1)
 conv_umma_kernel(const __half* __restrict__ in, __half* __restrict__ out, const int32_t* __restrict__ nbr,
                  const uint32_t* __restrict__ tile_mask, const int32_t* __restrict__ out_num,
                  const uint8_t* __restrict__ wtiles, const float* __restrict__ scale, const float* __restrict__ shift,
@@ -266,49 +283,58 @@ conv_umma_kernel(const __half* __restrict__ in, __half* __restrict__ out, const 
     constexpr int KG = 64 / CIN;            // kernel offsets sharing one 128-byte A row
     constexpr int CPO = CIN / 8;            // 16-byte chunks per offset
     constexpr int B_BYTES = COUT * ROW_BYTES;
-    constexpr int A_STAGES = RingCfg<CIN, COUT>::A_STAGES;
+    constexpr int NSLOT = Ring<CIN>::NSLOT;
+    constexpr int NIDX = Ring<CIN>::NIDX;
+    constexpr int THREADS = Ring<CIN>::THREADS;
     constexpr int IDX_WORDS = KG * TILE_M;  // one index block: KG offsets x 128 rows
-    constexpr int TMEM_COLS = TILES * COUT < 32 ? 32 : TILES * COUT;
+    constexpr int IDX_BATCH = 16;           // items the index warp handles side by side (must stay below NIDX)
+    constexpr int SET_COLS = TILES * COUT;  // accumulator columns of one set
+    constexpr int TMEM_COLS = 2 * SET_COLS < 32 ? 32 : 2 * SET_COLS;
     constexpr uint32_t IDESC = umma_idesc(COUT);
 
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint8_t* sA = smem;
-    uint8_t* sB = sA + A_STAGES * A_BYTES;
+    uint8_t* sB = sA + NSLOT * A_BYTES;
     int32_t* s_idx = reinterpret_cast<int32_t*>(sB + B_STAGES * B_BYTES);
-    float* s_scale = reinterpret_cast<float*>(s_idx + IDX_STAGES * IDX_WORDS);
+    float* s_scale = reinterpret_cast<float*>(s_idx + NIDX * IDX_WORDS);
     float* s_shift = s_scale + COUT;
     SharedCtl* ctl = reinterpret_cast<SharedCtl*>(s_shift + COUT);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int nstages = (kvol + KG - 1) / KG;
+    const bool idx_bulk = (max_voxels & 3) == 0;   // bulk copies need 16-byte aligned map rows
 
     if (tid == 0) {
-        for (int s = 0; s < A_STAGES; ++s) {
-            for (int i = 0; i < MMA_WARPS_MAX; ++i)
-                mbar_init(smem_u32(&ctl->a_full[i][s]), 32);   // the lanes of the gather warp that owns the stage
+        for (int s = 0; s < NSLOT; ++s) {
+            for (int i = 0; i < MMA_WARPS; ++i)
+                mbar_init(smem_u32(&ctl->a_full[i][s]), 32);   // the lanes of the gather warp that owns the slot
             mbar_init(smem_u32(&ctl->a_empty[s]), 1);
+        }
+        for (int j = 0; j < NIDX; ++j) {
+            ctl->idx_uses[j] = 0;
+            mbar_init(smem_u32(&ctl->i_full[j]), idx_bulk ? 1 : 32);   // the issuing lane / the lanes of the index warp
+            mbar_init(smem_u32(&ctl->i_empty[j]), 32);         // the lanes of the gather warp
         }
         for (int s = 0; s < B_STAGES; ++s) {
             mbar_init(smem_u32(&ctl->b_full[s]), 1);
-            mbar_init(smem_u32(&ctl->b_empty[s]), MMA_WARPS);   // every MMA issuer releases the weight block
+            mbar_init(smem_u32(&ctl->b_empty[s]), MMA_WARPS);
         }
-        for (int s = 0; s < IDX_STAGES; ++s) {
-            mbar_init(smem_u32(&ctl->i_full[s]), 32);
-            mbar_init(smem_u32(&ctl->i_empty[s]), 32);
+        for (int s = 0; s < 2; ++s) {
+            mbar_init(smem_u32(&ctl->acc_full[s]), MMA_WARPS);          // every MMA issuer reports its tile
+            mbar_init(smem_u32(&ctl->acc_empty[s]), EPI_WARPS * 32);    // every epilogue thread
         }
-        mbar_init(smem_u32(&ctl->acc_full), MMA_WARPS);        // every MMA issuer reports its tiles
-        mbar_init(smem_u32(&ctl->acc_empty), TILE_M);
         mbar_init(smem_u32(&ctl->mma_drain), MMA_WARPS);
         ctl->abort_flag = 0;
         ctl->abort_where = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    for (int c = tid; c < COUT; c += UMMA_THREADS) {
+    for (int c = tid; c < COUT; c += THREADS) {
         s_scale[c] = scale ? scale[c] : 1.f;
         s_shift[c] = (scale && shift) ? shift[c] : 0.f;
     }
-    if (warp == 4) {
+    const int tiles_per_frame = (max_voxels + TILE_M - 1) / TILE_M;
+    if (warp == EPI_WARPS) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&ctl->tmem_base)),
                      "r"(TMEM_COLS)
                      : "memory");
@@ -321,25 +347,87 @@ conv_umma_kernel(const __half* __restrict__ in, __half* __restrict__ out, const 
     volatile int* abort_flag = &ctl->abort_flag;
 #ifdef SESSD_UMMA_TIMING
     const long long t_cta0 = clock64();
-    unsigned long long tacc[32] = {};   // cycle counters kept in registers, written once at the end
+    unsigned long long tacc[8] = {};
 #endif
 
-    const int tiles_per_frame = (max_voxels + TILE_M - 1) / TILE_M;
-    uint32_t a_it = 0, b_it = 0, st_it = 0;   // ring positions; every role advances them identically
-    uint32_t full_phase = 0;                  // MMA issuers: bit s = parity of the next phase of their a_full[.][s]
+    uint32_t a_it = 0, b_it = 0, acc_it = 0;  // items, weight blocks and accumulator sets used so far; every role advances them identically
+    uint32_t full_phase = 0;                  // MMA issuers: bit s = parity of the next phase of their a_full[t][s]
     uint32_t b_issued = 0;                    // weight streamer: blocks whose bulk copy has been started
 
     // Balanced split: the occupied 128-row tiles of all frames, laid end to end, are cut into gridDim.x
-    // equal contiguous ranges (row counts are read from the device, so no host round trip); a CTA walks
-    // its range in groups of up to TILES tiles of one frame.
+    // contiguous ranges of equal work (row counts and tile masks are read from the device, so no host round
+    // trip); a CTA walks its range in groups of up to TILES tiles of one frame. The work of a tile is the number
+    // of its (tile, stage) items plus a constant for its epilogue: rows numbered in spatial order make
+    // neighbouring tiles alike, so dense and sparse regions would otherwise load the CTAs unevenly.
+    // Every CTA computes the same cut points from the same masks: thread t sums the weights of its slice of the
+    // tile sequence, a block scan turns the sums into running totals, and the threads whose slice holds cut
+    // point blockIdx.x or blockIdx.x + 1 walk the slice to the tile where the running total passes the target.
     auto frame_rows = [&](int f) {
         const int v = __ldg(out_num + f);
         return v > max_voxels ? max_voxels : (v < 0 ? 0 : v);
     };
-    long long total_tiles = 0;
+    int total_tiles = 0;
     for (int f = 0; f < batch; ++f) total_tiles += (frame_rows(f) + TILE_M - 1) / TILE_M;
-    const int range_lo = (int)(total_tiles * blockIdx.x / gridDim.x);
-    const int range_hi = (int)(total_tiles * (blockIdx.x + 1) / gridDim.x);
+    {
+        const int per = (total_tiles + THREADS - 1) / THREADS;
+        const int first = tid * per, last = first + per < total_tiles ? first + per : total_tiles;
+        auto tile_weight = [&](uint32_t mask) {
+            int items = 0;
+            for (int g = 0; g < nstages; ++g) items += stage_active<KG>(mask, g) ? 1 : 0;
+            return (uint32_t)(items + 2);
+        };
+        int f = 0, f_first = 0, f_tiles = batch > 0 ? (frame_rows(0) + TILE_M - 1) / TILE_M : 0;
+        auto seek = [&](int tile) {   // frame of a tile of the sequence (tiles are visited in ascending order)
+            while (f < batch && tile >= f_first + f_tiles) {
+                f_first += f_tiles;
+                ++f;
+                f_tiles = f < batch ? (frame_rows(f) + TILE_M - 1) / TILE_M : 0;
+            }
+        };
+        uint32_t mine = 0;
+        for (int i = first; i < last; ++i) {
+            seek(i);
+            mine += tile_weight(__ldg(tile_mask + (size_t)f * tiles_per_frame + (i - f_first)));
+        }
+        uint32_t incl = mine;   // inclusive block scan of `mine`
+#pragma unroll
+        for (int d = 1; d < 32; d <<= 1) {
+            const uint32_t v = __shfl_up_sync(0xFFFFFFFFu, incl, d);
+            if (lane >= d) incl += v;
+        }
+        if (lane == 31) ctl->scan_warp[warp] = incl;
+        if (tid == 0) ctl->range_lo = 0, ctl->range_hi = total_tiles;
+        __syncthreads();
+        uint32_t before = 0, grand = 0;
+        for (int w = 0; w < THREADS / 32; ++w) {
+            const uint32_t v = ctl->scan_warp[w];
+            if (w < warp) before += v;
+            grand += v;
+        }
+        const uint32_t excl = before + incl - mine;   // weight of all tiles before this thread's slice
+        // cut point c: the first tile whose running total (inclusive) exceeds grand * c / gridDim.x
+        for (int side = 0; side < 2; ++side) {
+            const unsigned long long c = blockIdx.x + side;
+            if (c == 0 || c >= gridDim.x) continue;   // 0 and total_tiles are preset
+            const uint32_t target = (uint32_t)((unsigned long long)grand * c / gridDim.x);
+            if (mine == 0 || target < excl || target >= excl + mine) continue;
+            f = 0, f_first = 0, f_tiles = batch > 0 ? (frame_rows(0) + TILE_M - 1) / TILE_M : 0;
+            uint32_t run = excl;
+            int cut = last;
+            for (int i = first; i < last; ++i) {
+                seek(i);
+                run += tile_weight(__ldg(tile_mask + (size_t)f * tiles_per_frame + (i - f_first)));
+                if (run > target) {
+                    cut = i;
+                    break;
+                }
+            }
+            if (side == 0) ctl->range_lo = cut;
+            else ctl->range_hi = cut;
+        }
+    }
+    __syncthreads();
+    const int range_lo = ctl->range_lo, range_hi = ctl->range_hi;
     int b = 0, frame_first = 0;                 // frame of the cursor and the global index of its first tile
     int n = batch > 0 ? frame_rows(0) : 0;
     int frame_tiles = (n + TILE_M - 1) / TILE_M;
@@ -351,15 +439,13 @@ conv_umma_kernel(const __half* __restrict__ in, __half* __restrict__ out, const 
             n = frame_rows(b);
             frame_tiles = (n + TILE_M - 1) / TILE_M;
         }
+        const long long tg0 = TCLK();
         const int tile0 = cur - frame_first;
         int cnt = range_hi - cur;
         cnt = cnt > TILES ? TILES : cnt;
         cnt = cnt > frame_tiles - tile0 ? frame_tiles - tile0 : cnt;
         cur += cnt;
         const int row0 = tile0 * TILE_M;
-#ifdef SESSD_UMMA_TIMING
-        const long long tg0 = clock64();
-#endif
         if (*abort_flag) break;
         uint32_t m[TILES];
         uint32_t any = 0;
@@ -368,34 +454,30 @@ conv_umma_kernel(const __half* __restrict__ in, __half* __restrict__ out, const 
             m[t] = t < cnt ? __ldg(tile_mask + (size_t)b * tiles_per_frame + tile0 + t) : 0u;
             any |= m[t];
         }
-        int n_a = 0, n_b = 0;   // A and B stages this super-tile consumes
+        int n_a = 0, n_b = 0;   // items and weight blocks this group consumes
         for (int g = 0; g < nstages; ++g) {
-            int act = 0;
-#pragma unroll
-            for (int t = 0; t < TILES; ++t) act += stage_active<KG>(m[t], g) ? 1 : 0;
+            const int act = __popc(active_tiles<KG>(m, g));
             n_a += act;
             n_b += act ? 1 : 0;
         }
+        const uint32_t set = acc_it & 1u;           // accumulator set of this group (groups without work use none)
+        const uint32_t set_phase = (acc_it >> 1) & 1u;
 
-        if (warp < 4) {
+        TADD(6, TCLK() - tg0);
+        if (warp >= FIRST_GATHER_WARP) {
             // ---------------- gather producers ----------------
-            // Each of the four gather warps owns every fourth stage and issues all of its copies: while one
-            // warp sits in the latency of its barrier hand-offs the other three keep the copy pipe busy.
+            // Gather warp s fills slot s with every NSLOT-th item and issues all of its copies: while one warp
+            // sits in the latency of its barrier hand-offs the others keep the copy pipe busy.
             // Lane = (row group j, 16-byte chunk c): the eight lanes j*8..j*8+7 copy rows 32j..32j+31 of the
-            // stage, one row per step, chunk c of the row landing at chunk c ^ (row & 7) (128-byte swizzle).
+            // item, one row per step, chunk c of the row landing at chunk c ^ (row & 7) (128-byte swizzle).
+            const int s = warp - FIRST_GATHER_WARP;
             const int c = lane & 7;                // 16-byte chunk of the 128-byte row
             const int jrow = (lane >> 3) * 32;     // first row of this lane group
             const int koff = c / CPO;              // offset of the stage's group this chunk belongs to
             const int csub = (c % CPO) * 8;        // first channel of the chunk
             const __half* in_b = in + (size_t)b * max_voxels * CIN;
-            uint32_t my_a = a_it;
-#ifdef SESSD_UMMA_TIMING
-            const long long tg1 = clock64();
-            if (tid == 0 && blockIdx.x < 1) tacc[9] += (unsigned long long)(tg1 - tg0);   // group set-up
-#endif
-            bool ok = true;
-            // list of this group's (stage, tile) pairs: lane g holds stage g's tiles, a warp scan places them
-            uint8_t* list = ctl->stage_list[warp];
+            // list of this group's items: lane g holds stage g's tiles, a warp scan places them
+            uint8_t* list = ctl->stage_list[s];
             {
                 const uint32_t bits = lane < nstages ? active_tiles<KG>(m, lane) : 0u;
                 const int cnt_l = __popc(bits);
@@ -411,50 +493,43 @@ conv_umma_kernel(const __half* __restrict__ in, __half* __restrict__ out, const 
                     if ((bits >> tt) & 1u) list[at++] = (uint8_t)((lane << 2) | tt);
                 __syncwarp();
             }
-            const int first = (warp + GATHER_WARPS - (int)(a_it % GATHER_WARPS)) % GATHER_WARPS;
-            for (int e = first; e < n_a && ok; e += GATHER_WARPS) {
-                my_a = a_it + (uint32_t)e;
+            const int first = (s + NSLOT - (int)(a_it % NSLOT)) % NSLOT;
+            const uint32_t idx_lane = smem_u32(&s_idx[koff * TILE_M + jrow]);
+            const uint32_t a_base = smem_u32(sA + s * A_BYTES) + jrow * ROW_BYTES;
+            for (int e = first; e < n_a; e += NSLOT) {
+                const uint32_t q = a_it + (uint32_t)e;
+                const uint32_t use = (q / NSLOT) & 1u;   // parity of this use of the slot
+                const uint32_t ji = q % NIDX;            // index block of the item
+                const uint32_t iuse = (q / NIDX) & 1u;
+                const uint32_t idx_base = idx_lane + ji * (IDX_WORDS * 4);
                 const int code = list[e];
                 const int g = code >> 2, t = code & 3;
-                const uint32_t s = my_a % A_STAGES, si = my_a % IDX_STAGES;
-#ifdef SESSD_UMMA_TIMING
-                long long tq0 = clock64();
-#endif
-                // row indices of this stage, fetched ahead of time by the index warp
-                ok = mbar_wait(smem_u32(&ctl->i_full[si]), (my_a / IDX_STAGES) & 1u, abort_flag, 1 | (int)(my_a << 4));
-                if (!ok) break;
-#ifdef SESSD_UMMA_TIMING
-                long long tq1 = clock64();
-                long long tq2 = tq1;
-#endif
-                ok = mbar_wait(smem_u32(&ctl->a_empty[s]), ((my_a / A_STAGES) & 1u) ^ 1u, abort_flag, 2 | (int)(my_a << 4));
-                if (!ok) break;
-#ifdef SESSD_UMMA_TIMING
-                long long tq3 = clock64();
-                if (tid == 0 && blockIdx.x < 1 && my_a >= (uint32_t)A_STAGES) {
-                    tacc[16] += (unsigned long long)(tq3 - ctl->t_commit[s]);   // commit issued -> stage seen free
-                    tacc[17] += 1;
-                    if (tq3 - tq2 < 100) tacc[18] += 1;                         // free already when asked
-                }
-#endif
-                const bool k_ok = g * KG + koff < kvol;
-                const int rows_left = n - (row0 + t * TILE_M + jrow);   // rows of this lane group inside the frame
-                const int32_t* ip = &s_idx[si * IDX_WORDS + koff * TILE_M + jrow];
-                const uint32_t a_base = smem_u32(sA + s * A_BYTES) + jrow * ROW_BYTES;
-                // Every instruction of this loop is on the critical path of the stage (the gather warps are bound
-                // by their own instruction latency, not by the copies), so the common case - all offsets of the
-                // stage exist and the whole tile lies inside the frame - takes three instructions per row: a
-                // predicate from the sign of the index, the address, and a copy that writes zeros when the
-                // predicate says the neighbour is missing.
-                const bool plain = g * KG + KG <= kvol && row0 + (t + 1) * TILE_M <= n;   // uniform over the warp
-                const __half* lane_base = in_b + csub;
+                // row indices of this item, fetched ahead of time by the index warp
+                const long long tq0 = TCLK();
+                if (!mbar_wait(smem_u32(&ctl->i_full[ji]), iuse, abort_flag, 1 | (int)(q << 4))) break;
+                const long long tq1 = TCLK();
+
                 // all 32 indices first (the copies below are compiler barriers, a load could not move above them)
                 int vv[32];
 #pragma unroll
-                for (int q = 0; q < 8; ++q) {
-                    const int4 v = *reinterpret_cast<const int4*>(ip + 4 * q);
-                    vv[4 * q] = v.x, vv[4 * q + 1] = v.y, vv[4 * q + 2] = v.z, vv[4 * q + 3] = v.w;
+                for (int w4 = 0; w4 < 8; ++w4) {
+                    int4 v;
+                    asm volatile("ld.shared.v4.s32 {%0,%1,%2,%3}, [%4];"
+                                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                                 : "r"(idx_base + 16 * w4));
+                    vv[4 * w4] = v.x, vv[4 * w4 + 1] = v.y, vv[4 * w4 + 2] = v.z, vv[4 * w4 + 3] = v.w;
                 }
+                const long long tq2 = TCLK();
+                if (!mbar_wait(smem_u32(&ctl->a_empty[s]), use ^ 1u, abort_flag, 2 | (int)(q << 4))) break;
+                const long long tq3 = TCLK();
+                const bool k_ok = g * KG + koff < kvol;
+                const int rows_left = n - (row0 + t * TILE_M + jrow);   // rows of this lane group inside the frame
+                // Every instruction of this loop is on the critical path of the item, so the common case - all
+                // offsets of the stage exist and the whole tile lies inside the frame - takes three instructions
+                // per row: a predicate from the sign of the index, the address, and a copy that writes zeros when
+                // the predicate says the neighbour is missing.
+                const bool plain = g * KG + KG <= kvol && row0 + (t + 1) * TILE_M <= n;   // uniform over the warp
+                const __half* lane_base = in_b + csub;
                 if (plain) {
 #pragma unroll
                     for (int p = 0; p < 32; ++p)
@@ -468,39 +543,30 @@ conv_umma_kernel(const __half* __restrict__ in, __half* __restrict__ out, const 
                         cp_async_16(a_base + p * ROW_BYTES + ((c ^ (p & 7)) << 4), src, id < 0 ? 0u : 16u);
                     }
                 }
-                mbar_arrive(smem_u32(&ctl->i_empty[si]));           // the index block has been read
-                // publishes the stage, when the copies land, to the issuer that owns row tile t
-                cp_async_arrive_noinc(smem_u32(&ctl->a_full[t & 1][s]));
-#ifdef SESSD_UMMA_TIMING
-                if (tid == 0 && blockIdx.x < 1) {
-                    long long tq5 = clock64();
-                    ctl->t_issue[s] = tq5;
-                    tacc[0] += (unsigned long long)(tq1 - tq0);  // wait index block
-                    tacc[1] += (unsigned long long)(tq3 - tq2);  // wait free A stage
-                    tacc[3] += (unsigned long long)(tq5 - tq0);  // whole iteration
-                    tacc[4] += 1;
-                }
-#endif
+                // The index block may be refilled now: every index has been consumed by a copy above (the arrival
+                // sits behind the copies so that it depends on the registers the index loads wrote; released
+                // earlier, right after the loads were issued, the last of them were seen to return the next
+                // item's indices). The ring is three slot cycles deep, so nothing waits for this.
+                mbar_arrive(smem_u32(&ctl->i_empty[ji]));
+                // publishes the slot, when the copies land, to the issuer that owns row tile t
+                cp_async_arrive_noinc(smem_u32(&ctl->a_full[t][s]));
+                TADD(0, tq1 - tq0);
+                TADD(1, tq3 - tq2);
+                TADD(2, TCLK() - tq3);
+                TADD(3, 1);
+                TADD(4, tq2 - tq1);
             }
-#ifdef SESSD_UMMA_TIMING
-            if (tid == 0 && blockIdx.x < 1) tacc[14] += (unsigned long long)(clock64() - tg1);   // whole gather loop of the group
-#endif
-
+        } else if (warp < EPI_WARPS) {
             // ---------------- epilogue ----------------
-#ifdef SESSD_UMMA_TIMING
-            long long te0 = clock64();
-#endif
             bool got = true;
+            const long long te0 = TCLK();
             if (any) {
-                got = ok && mbar_wait(smem_u32(&ctl->acc_full), st_it & 1u, abort_flag, 3 | (int)(st_it << 4));
+                got = mbar_wait<true>(smem_u32(&ctl->acc_full[set]), set_phase, abort_flag, 3 | (int)(acc_it << 4));
                 got = __all_sync(0xFFFFFFFFu, got);
                 if (got) tc_fence_after();
             }
-#ifdef SESSD_UMMA_TIMING
-            long long te1 = clock64();
-#endif
-            // Column blocks of CB channels keep the register footprint small enough for other kernels'
-            // blocks to share the SM with the two resident CTAs of this one.
+            const long long te1 = TCLK();
+            // Column blocks of CB channels keep the register footprint small.
             constexpr int CB = COUT < 32 ? COUT : 32;
 #pragma unroll 1
             for (int t2 = 0; t2 < cnt; ++t2) {
@@ -522,7 +588,7 @@ conv_umma_kernel(const __half* __restrict__ in, __half* __restrict__ out, const 
 #pragma unroll
                         for (int c0 = 0; c0 < CB; c0 += 16) {
                             uint32_t r16[16];
-                            tmem_ld16(tmem + ((uint32_t)(warp * 32) << 16) + t2 * COUT + cb + c0, r16);
+                            tmem_ld16(tmem + ((uint32_t)(warp * 32) << 16) + set * SET_COLS + t2 * COUT + cb + c0, r16);
 #pragma unroll
                             for (int j = 0; j < 16; ++j) acc[c0 + j] = __uint_as_float(r16[j]);
                         }
@@ -561,149 +627,165 @@ conv_umma_kernel(const __half* __restrict__ in, __half* __restrict__ out, const 
                     }
                 }
             }
-            if (any) {
+            if (any && got) {
                 tc_fence_before();
-                mbar_arrive(smem_u32(&ctl->acc_empty));   // the accumulators may be overwritten
+                mbar_arrive(smem_u32(&ctl->acc_empty[set]));   // the set may be overwritten
             }
-#ifdef SESSD_UMMA_TIMING
-            if (tid == 0 && blockIdx.x < 1) {
-                tacc[5] += (unsigned long long)(te1 - te0);          // wait for the accumulators
-                tacc[6] += (unsigned long long)(clock64() - te1);    // epilogue proper
-                tacc[7] += 1;
-            }
-#endif
-        } else if (warp == 4 || warp == 7) {
+            TADD(0, te1 - te0);
+            TADD(1, TCLK() - te1);
+            TADD(2, 1);
+        } else if (warp < WEIGHT_WARP) {
             // ---------------- MMA issuers ----------------
-            // Issuing a tcgen05.mma or commit costs the issuing thread on the order of a hundred cycles, so
-            // two threads issue: warp 4 owns the even row tiles, warp 7 the odd ones (disjoint accumulators;
-            // the split stays even when a group holds fewer than TILES tiles).
+            // Issuer t owns tile t: its accumulator, the items (t, g) and their slots. All four wait for every
+            // weight block and release it, also one with nothing to do for the stage: each of its waits and
+            // arrivals must count for this use of the weight slot, not for an earlier one (a slot refilled while
+            // an issuer has not yet tested its previous use would leave that issuer waiting on the wrong phase).
             if (lane == 0 && any) {
-                const int parity = warp == 4 ? 0 : 1;
+                const int t = warp - EPI_WARPS;
                 uint32_t my_a = a_it, my_b = b_it;
-                bool ok = true;
-                if (st_it > 0) ok = mbar_wait(smem_u32(&ctl->acc_empty), (st_it - 1u) & 1u, abort_flag, 4 | (int)(st_it << 4));
+                // the epilogue must have read this set's previous contents (two groups back)
+                const long long tm0 = TCLK();
+                bool ok = mbar_wait<false, true>(smem_u32(&ctl->acc_empty[set]), set_phase ^ 1u, abort_flag,
+                                                 4 | (int)(acc_it << 4));
+                TADD(0, TCLK() - tm0);
                 if (ok) tc_fence_after();
-                uint32_t started = 0;
+                const uint32_t d_tmem = tmem + set * SET_COLS + t * COUT;
+                bool started = false;
                 for (int g = 0; g < nstages && ok; ++g) {
                     const uint32_t bits = active_tiles<KG>(m, g);
-                    const int act = __popc(bits);   // active tiles of this stage group
-                    const bool mine = (bits & (parity ? 0xAAAAAAAAu : 0x55555555u)) != 0u;
-                    if (!act) continue;
+                    if (!bits) continue;
                     const uint32_t sb = my_b % B_STAGES;
-                    // Both issuers wait for the block, also one with nothing to do for this group: its
-                    // release below must count for this use of the slot, not for an earlier one.
-#ifdef SESSD_UMMA_TIMING
-                    const long long tb0 = clock64();
-#endif
-                    ok = mbar_wait(smem_u32(&ctl->b_full[sb]), (my_b / B_STAGES) & 1u, abort_flag, 5 | (int)(my_b << 4));
-#ifdef SESSD_UMMA_TIMING
-                    if (warp == 4 && blockIdx.x < 1) {
-                        tacc[11] += (unsigned long long)(clock64() - tb0);
-                    }
-#endif
+                    const long long tm1 = TCLK();
+                    ok = mbar_wait<false, true>(smem_u32(&ctl->b_full[sb]), (my_b / B_STAGES) & 1u, abort_flag,
+                                                5 | (int)(my_b << 4));
+                    TADD(1, TCLK() - tm1);
                     if (!ok) break;
-                    if (mine) {
-                        const uint32_t b_addr = smem_u32(sB + sb * B_BYTES);
-                        uint32_t pos = my_a;
-                        for (int t = 0; t < TILES && ok; ++t) {
-                            if (!((bits >> t) & 1u)) continue;
-                            if ((t & 1) != parity) {   // the other issuer's stage
-                                ++pos;
-                                continue;
-                            }
-                            const uint32_t sa = pos % A_STAGES;
-#ifdef SESSD_UMMA_TIMING
-                            const long long tm0 = clock64();
-#endif
-                            ok = mbar_wait(smem_u32(&ctl->a_full[parity][sa]), (full_phase >> sa) & 1u, abort_flag,
-                                           6 | (int)(pos << 4));
-                            full_phase ^= 1u << sa;   // this issuer's next use of the slot is the next phase
-                            if (!ok) break;
-#ifdef SESSD_UMMA_TIMING
-                            if (warp == 4 && blockIdx.x < 1) {   // cycles this issuer waited for gathered rows
-                                const long long tm1 = clock64();
-                                tacc[2] += (unsigned long long)(tm1 - tm0);
-                                tacc[19] += (unsigned long long)(tm1 - ctl->t_issue[sa]);   // gathers issued -> seen landed
-                                if (tm1 - tm0 < 100) tacc[20] += 1;                          // landed already when asked
-                            }
-#endif
-                            fence_proxy_async();   // the gathered rows were written through the generic proxy
-                            tc_fence_after();
-                            const uint32_t a_addr = smem_u32(sA + sa * A_BYTES);
+                    if ((bits >> t) & 1u) {
+                        const uint32_t pos = my_a + (uint32_t)__popc(bits & ((1u << t) - 1u));
+                        const uint32_t sa = pos % NSLOT;
+                        const long long tm2 = TCLK();
+                        ok = mbar_wait<false, true>(smem_u32(&ctl->a_full[t][sa]), (full_phase >> sa) & 1u, abort_flag,
+                                                    6 | (int)(pos << 4));
+                        full_phase ^= 1u << sa;   // this issuer's next use of the slot is the next phase
+                        if (!ok) break;
+                        const long long tm3 = TCLK();
+                        TADD(2, tm3 - tm2);
+                        fence_proxy_async();   // the gathered rows were written through the generic proxy
+                        tc_fence_after();
+                        const uint64_t adesc = umma_desc(smem_u32(sA + sa * A_BYTES));
+                        const uint64_t bdesc = umma_desc(smem_u32(sB + sb * B_BYTES));
 #pragma unroll
-                            for (int kk = 0; kk < 4; ++kk) {
-                                umma_f16(tmem + t * COUT, umma_desc(a_addr + kk * 32), umma_desc(b_addr + kk * 32), IDESC,
-                                         (((started >> t) & 1u) || kk > 0) ? 1u : 0u);
-                            }
-                            started |= 1u << t;
-                            umma_commit(smem_u32(&ctl->a_empty[sa]));   // frees the A stage once these MMAs have read it
-#ifdef SESSD_UMMA_TIMING
-                            if (blockIdx.x < 1) ctl->t_commit[sa] = clock64();
-                            if (warp == 4 && blockIdx.x < 1) {
-                                tacc[10] += (unsigned long long)(clock64() - tm0);   // wait + issue + commit of one stage
-                                tacc[12] += 1;
-                            }
-#endif
-                            ++pos;
-                        }
-                        if (ok) umma_commit(smem_u32(&ctl->b_empty[sb]));
+                        for (int kk = 0; kk < 4; ++kk)
+                            umma_f16(d_tmem, adesc + 2 * kk, bdesc + 2 * kk, IDESC, (started || kk > 0) ? 1u : 0u);
+                        started = true;
+                        umma_commit(smem_u32(&ctl->a_empty[sa]));   // frees the A slot once these MMAs have read it
+                        umma_commit(smem_u32(&ctl->b_empty[sb]));   // and this issuer's hold on the weight block
+                        TADD(3, TCLK() - tm3);
+                        TADD(4, 1);
                     } else {
                         mbar_arrive(smem_u32(&ctl->b_empty[sb]));   // nothing to read from this weight block
                     }
-                    my_a += act;
+                    my_a += (uint32_t)__popc(bits);
                     ++my_b;
                 }
                 if (ok) {
-                    if (started) umma_commit(smem_u32(&ctl->acc_full));
-                    else mbar_arrive(smem_u32(&ctl->acc_full));
+                    if (started) umma_commit(smem_u32(&ctl->acc_full[set]));
+                    else mbar_arrive(smem_u32(&ctl->acc_full[set]));
                 }
             }
             __syncwarp();
-        } else if (warp == 6) {
+        } else if (warp == INDEX_WARP) {
             // ---------------- neighbour-index loader ----------------
-            // Copies, for every (stage, tile) pair in consumption order, the KG x 128 neighbour indices
-            // into the index ring with 4-byte cp.async, several blocks ahead of the gather warps. Rows
-            // past max_voxels are zero-filled; the gather warps ignore rows past the frame's row count.
+            // Copies, for every item in consumption order, the KG x 128 neighbour indices into the next block of
+            // the index ring, two to three slot cycles ahead of the gather warp that will use them. A (tile,
+            // offset) row of the map is 512 contiguous bytes, so an item is KG bulk copies that report to the
+            // block's barrier by byte count; the lanes of the warp work on IDX_BATCH consecutive items at once
+            // (one dependent chain of wait, expect and copy per lane instead of one per item). Indices of rows
+            // past the frame's row count or of offsets past kvol are not loaded; the gather warps ignore them.
             const int32_t* nbr_b = nbr + (size_t)b * kvol * max_voxels;
-            uint32_t my_i = a_it;
-            bool ok = true;
-            int g = -1, t = 0;
-            uint32_t rem = 0;
-            while (ok && next_item<KG>(m, nstages, g, rem, t)) {
-                const uint32_t si = my_i % IDX_STAGES;
-                ok = mbar_wait<true>(smem_u32(&ctl->i_empty[si]), ((my_i / IDX_STAGES) & 1u) ^ 1u, abort_flag, 7 | (int)(my_i << 4));
-                if (!ok) break;
+            if (idx_bulk) {
+                uint8_t* list = ctl->idx_list;
+                {
+                    const uint32_t bits = lane < nstages ? active_tiles<KG>(m, lane) : 0u;
+                    const int cnt_l = __popc(bits);
+                    int incl = cnt_l;
 #pragma unroll
-                for (int j = 0; j < KG; ++j) {
-                    const int k = g * KG + j;
-#pragma unroll
-                    for (int q = 0; q < TILE_M / 32; ++q) {
-                        const int r = q * 32 + lane;
-                        const int row = row0 + t * TILE_M + r;
-                        const bool in_range = k < kvol && row < max_voxels;
-                        const int32_t* src = nbr_b + (in_range ? (size_t)k * max_voxels + row : 0);
-                        asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;" ::"r"(
-                                         smem_u32(&s_idx[si * IDX_WORDS + j * TILE_M + r])),
-                                     "l"(src), "r"(in_range ? 4u : 0u)
-                                     : "memory");
+                    for (int d = 1; d < 32; d <<= 1) {
+                        const int v = __shfl_up_sync(0xFFFFFFFFu, incl, d);
+                        if (lane >= d) incl += v;
                     }
+                    int at = incl - cnt_l;
+#pragma unroll
+                    for (int tt = 0; tt < TILES; ++tt)
+                        if ((bits >> tt) & 1u) list[at++] = (uint8_t)((lane << 2) | tt);
+                    __syncwarp();
                 }
-                cp_async_arrive_noinc(smem_u32(&ctl->i_full[si]));
-                ++my_i;
+                // The lanes step through the batches together: an item's wait tests the parity of the previous use
+                // of its block, which is only meaningful once the lane that handled that use (a lane of an earlier
+                // batch) has passed its own wait. A lane running batches ahead of the others would break that.
+                bool live = true;
+                for (int base = 0; base < n_a; base += IDX_BATCH) {
+                    const int e = base + lane;
+                    if (live && lane < IDX_BATCH && e < n_a) {
+                        const uint32_t q = a_it + (uint32_t)e;
+                        const uint32_t j = q % NIDX;
+                        const int code = list[e];
+                        const int g = code >> 2, t = code & 3;
+                        live = mbar_wait(smem_u32(&ctl->i_empty[j]), ((q / NIDX) & 1u) ^ 1u, abort_flag, 7 | (int)(q << 4));
+                        if (live) {
+                            const int row = row0 + t * TILE_M;
+                            int rows = max_voxels - row;
+                            rows = rows > TILE_M ? TILE_M : rows;
+                            int nk = kvol - g * KG;
+                            nk = nk > KG ? KG : nk;
+                            const uint32_t bar = smem_u32(&ctl->i_full[j]);
+                            ctl->idx_uses[j] = q / NIDX + 1u;
+                            mbar_arrive_expect_tx(bar, (uint32_t)(nk * rows * 4));
+                            for (int jj = 0; jj < nk; ++jj)
+                                bulk_load(smem_u32(&s_idx[j * IDX_WORDS + jj * TILE_M]),
+                                          nbr_b + (size_t)(g * KG + jj) * max_voxels + row, (uint32_t)(rows * 4), bar);
+                        }
+                    }
+                    live = __all_sync(0xFFFFFFFFu, live);   // also the batch boundary: no lane starts the next batch early
+                    if (!live) break;
+                }
+            } else {
+                // map rows that are not 16-byte aligned (max_voxels not a multiple of 4): 4-byte copies, item by item
+                uint32_t q = a_it;
+                int g = -1, t = 0;
+                uint32_t rem = 0;
+                while (next_item<KG>(m, nstages, g, rem, t)) {
+                    const uint32_t j = q % NIDX;
+                    if (!mbar_wait(smem_u32(&ctl->i_empty[j]), ((q / NIDX) & 1u) ^ 1u, abort_flag, 7 | (int)(q << 4))) break;
+#pragma unroll
+                    for (int jj = 0; jj < KG; ++jj) {
+                        const int k = g * KG + jj;
+#pragma unroll
+                        for (int w4 = 0; w4 < TILE_M / 32; ++w4) {
+                            const int r = w4 * 32 + lane;
+                            const int row = row0 + t * TILE_M + r;
+                            const bool in_range = k < kvol && row < max_voxels;
+                            const int32_t* src = nbr_b + (in_range ? (size_t)k * max_voxels + row : 0);
+                            asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;" ::"r"(
+                                             smem_u32(&s_idx[j * IDX_WORDS + jj * TILE_M + r])),
+                                         "l"(src), "r"(in_range ? 4u : 0u)
+                                         : "memory");
+                        }
+                    }
+                    cp_async_arrive_noinc(smem_u32(&ctl->i_full[j]));
+                    ++q;
+                }
             }
         } else {
             // ---------------- weight streamer ----------------
             if (lane == 0 && !withhold_weights) {
                 uint32_t my_b = b_it;
-                bool ok = true;
-                for (int g = 0; g < nstages && ok; ++g) {
-                    bool stage_any = false;
-#pragma unroll
-                    for (int t = 0; t < TILES; ++t) stage_any |= stage_active<KG>(m[t], g);
-                    if (!stage_any) continue;
+                for (int g = 0; g < nstages; ++g) {
+                    if (!active_tiles<KG>(m, g)) continue;
                     const uint32_t sb = my_b % B_STAGES;
-                    ok = mbar_wait<true>(smem_u32(&ctl->b_empty[sb]), ((my_b / B_STAGES) & 1u) ^ 1u, abort_flag, 8 | (int)(my_b << 4));
-                    if (!ok) break;
+                    if (!mbar_wait(smem_u32(&ctl->b_empty[sb]), ((my_b / B_STAGES) & 1u) ^ 1u, abort_flag,
+                                   8 | (int)(my_b << 4)))
+                        break;
                     const uint32_t bar = smem_u32(&ctl->b_full[sb]);
                     mbar_arrive_expect_tx(bar, B_BYTES);
                     bulk_load(smem_u32(sB + sb * B_BYTES), wtiles + (size_t)g * B_BYTES, B_BYTES, bar);
@@ -715,18 +797,24 @@ conv_umma_kernel(const __half* __restrict__ in, __half* __restrict__ out, const 
         }
         a_it += n_a;
         b_it += n_b;
-        if (any) ++st_it;
+        if (any) ++acc_it;
     }
 
     tc_fence_before();
     __syncthreads();
 #ifdef SESSD_UMMA_TIMING
-    if ((tid == 0 || tid == 128) && blockIdx.x < 1) {
+    if (tid == 0) {   // spread of the CTA lifetimes: max and sum over the grid
         unsigned long long* dbg = reinterpret_cast<unsigned long long*>(status) + 96;
-        tacc[tid == 0 ? 8 : 13] = (unsigned long long)(clock64() - t_cta0);
+        const unsigned long long life = (unsigned long long)(clock64() - t_cta0);
+        atomicMax(dbg + 30, life);
+        atomicAdd(dbg + 31, life);
+    }
+    if (blockIdx.x == 0 && lane == 0 && (warp == 0 || warp == EPI_WARPS || warp == FIRST_GATHER_WARP || warp == INDEX_WARP)) {
+        unsigned long long* dbg = reinterpret_cast<unsigned long long*>(status) + 96 +
+                                  (warp == 0 ? 0 : (warp == EPI_WARPS ? 8 : (warp == INDEX_WARP ? 24 : 16)));
+        tacc[7] = (unsigned long long)(clock64() - t_cta0);
 #pragma unroll
-        for (int i = 0; i < 32; ++i)
-            if (tacc[i]) dbg[i] = tacc[i];
+        for (int i = 0; i < (warp == INDEX_WARP ? 6 : 8); ++i) dbg[i] = tacc[i];
     }
 #endif
     if (*abort_flag) {
@@ -734,9 +822,17 @@ conv_umma_kernel(const __half* __restrict__ in, __half* __restrict__ out, const 
         // memory: the gather and index warps wait for their cp.async copies, the issuers commit to a barrier that
         // warp 4 waits on (bounded) before it frees the tensor memory, the weight streamer waits (bounded) for
         // its last bulk copies.
-        if (warp < GATHER_WARPS || warp == 6) asm volatile("cp.async.wait_all;" ::: "memory");   // rows and indices
-        if ((warp == 4 || warp == 7) && lane == 0) umma_commit(smem_u32(&ctl->mma_drain));
-        if (warp == 5 && lane == 0) {
+        if (warp >= FIRST_GATHER_WARP || warp == INDEX_WARP) asm volatile("cp.async.wait_all;" ::: "memory");
+        if (warp >= EPI_WARPS && warp < WEIGHT_WARP && lane == 0) umma_commit(smem_u32(&ctl->mma_drain));
+        if (warp == INDEX_WARP && idx_bulk) {
+            for (int j = lane; j < NIDX; j += 32) {
+                const uint32_t uses = ctl->idx_uses[j];
+                if (!uses) continue;
+                const long long t0 = clock64();
+                while (!mbar_try_wait(smem_u32(&ctl->i_full[j]), (uses - 1u) & 1u) && clock64() - t0 < WAIT_LIMIT_CYCLES) {}
+            }
+        }
+        if (warp == WEIGHT_WARP && lane == 0) {
             const uint32_t first = b_issued > (uint32_t)B_STAGES ? b_issued - B_STAGES : 0u;
             for (uint32_t j = first; j < b_issued; ++j) {
                 const uint32_t bar = smem_u32(&ctl->b_full[j % B_STAGES]);
@@ -750,7 +846,7 @@ conv_umma_kernel(const __half* __restrict__ in, __half* __restrict__ out, const 
         atomicOr(status, SESSD_STATUS_TIMEOUT);
         atomicCAS(status + 1, 0, ctl->abort_where);   // first report wins: which wait, at which ring position
     }
-    if (warp == 4) {
+    if (warp == EPI_WARPS) {
         if (*abort_flag && lane == 0) {
             // the tensor memory is given back only when no MMA of this CTA can still write to it
             const long long t0 = clock64();
@@ -765,8 +861,8 @@ conv_umma_kernel(const __half* __restrict__ in, __half* __restrict__ out, const 
 template <int CIN, int COUT>
 int launch_one(const ConvLaunch& c, cudaStream_t stream) {
     static const std::string name = "conv_umma<f16," + std::to_string(CIN) + "," + std::to_string(COUT) + ">";
-    constexpr int ctas_per_sm = 2;   // shared memory and registers are budgeted for two resident CTAs
     const int smem = umma_smem_bytes<CIN, COUT>();
+    static_assert(umma_smem_bytes<CIN, COUT>() <= 227 * 1024, "ring does not fit the shared memory of one SM");
     // the attribute belongs to the device's context: set it once per device (repeating it is harmless, so a
     // race between two host threads only costs a second call)
     static std::atomic<uint64_t> configured{0};
@@ -777,7 +873,7 @@ int launch_one(const ConvLaunch& c, cudaStream_t stream) {
         SESSD_CUDA(cudaFuncSetAttribute(conv_umma_kernel<CIN, COUT>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
         configured.fetch_or(bit, std::memory_order_release);
     }
-    SESSD_LAUNCH_NAMED(name.c_str(), (conv_umma_kernel<CIN, COUT>), persistent_grid(ctas_per_sm), UMMA_THREADS, smem, stream,
+    SESSD_LAUNCH_NAMED(name.c_str(), (conv_umma_kernel<CIN, COUT>), persistent_grid(1), Ring<CIN>::THREADS, smem, stream,
                        static_cast<const __half*>(c.in), static_cast<__half*>(c.out), c.nbr, c.tile_mask, c.out_num,
                        static_cast<const uint8_t*>(c.umma_weights), c.scale, c.shift, c.relu, c.batch, c.max_voxels,
                        c.kvol, static_cast<__half*>(c.dense), reinterpret_cast<const int4*>(c.out_coors), c.D, c.H, c.W,

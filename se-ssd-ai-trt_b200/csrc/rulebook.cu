@@ -2,11 +2,24 @@
 //
 // The reference builds, in every plugin call, a dense index grid (up to 369 MB, reset with
 // cudaMemset), a candidate list per voxel and an input-stationary pair list per kernel offset
-// (submConv3dlayer.cu:271-459, sparseConv3dlayer.cu:310-555). Here the active coordinates of a
-// frame live in an open-addressing table (a few hundred KB), and the rulebook is kept in
+// (submConv3dlayer.cu:271-459, sparseConv3dlayer.cu:310-555). Here the rulebook is kept in
 // output-stationary form: nbr[b][k][o] = input row that feeds output row o through kernel offset k,
 // or -1. Pair (k, i, o) of the reference exists exactly when nbr[b][k][o] == i, because
 // k = in - out*stride + pad per axis (submConv3dlayer.cu:328-329) and input rows are unique.
+//
+// Where the rows of a frame come from decides how a coordinate is turned back into its row:
+//   - the voxeliser's rows (full resolution, 92 M cells, 80 K of them active) sit in an x-grouped
+//     open-addressing table (32-byte buckets of four x-neighbours);
+//   - the rows a strided layer produces are numbered through an occupancy grid of the output level: one
+//     bit per cell, 64 x-neighbours per word, each word followed by the number of rows before it. Every
+//     candidate output of every input row sets its bit (sparseConv3dlayer.cu:310-386 with the truncating
+//     divisions kept); a count and a scan/emit pass then number the set bits in (z, y, x) order and write
+//     the output coordinates. A cell's row is prefix + popcount(bits below), one 16-byte read, and the
+//     three x-neighbours of a 3x3x3 kernel share that read. The grids are small (3 MB per frame at half
+//     resolution, 0.4 MB at quarter resolution) and stay in L2. The reference numbers outputs in the
+//     arrival order of an atomic over a dense scan (sparseConv3dlayer.cu:529-541); (z, y, x) order is
+//     deterministic and keeps the rows of a 128-row tile close together in space;
+//   - coordinates handed in by a caller (the stand-alone plugin entry points) go into a flat table.
 #include "numbering.cuh"
 
 namespace sessd {
@@ -93,104 +106,6 @@ __device__ __forceinline__ void split_small(int e, int m, int* q, int* r) {   //
         *r = e - *q * m;
     }
 }
-
-constexpr int kSlotBits = 24;                       // slot_of = kernel offset << 24 | table slot
-constexpr uint32_t kSlotMask = (1u << kSlotBits) - 1u;
-
-// Candidate outputs of every input row of a strided convolution. Entry t = i*ncand + e, where
-// e = (cz * span_max_y + cy) * span_max_x + cx walks the row's candidate box from its upper corner downward,
-// x fastest: the reference's enumeration order (sparseConv3dlayer.cu:351-383) with the slots of candidates
-// that do not exist for this row left empty, so entry order = the order a sequential pass meets them.
-// Each in-bounds candidate claims its cell in the output table, lowers the cell's rank to t, and records
-// table slot and kernel offset k = in - out*stride + pad per axis (:366) in slot_of.
-__global__ void __launch_bounds__(kThreads)
-spconv_candidates_kernel(const int4* __restrict__ in_coors, const int32_t* __restrict__ in_num, int batch,
-                         int max_voxels, ConvGeom g, Table out_table, int32_t* __restrict__ slot_of,
-                         int32_t* status) {
-    const int64_t per_frame = (int64_t)max_voxels * g.ncand;
-    const int chunks = (int)((per_frame + kThreads - 1) / kThreads);
-    const int items = batch * chunks;
-    for (int it = blockIdx.x; it < items; it += gridDim.x) {
-        const int b = it / chunks;
-        const int t = (it - b * chunks) * kThreads + threadIdx.x;
-        int n = in_num[b];
-        n = n > max_voxels ? max_voxels : n;
-        if (t >= n * g.ncand) continue;
-        const int i = g.cand_shift >= 0 ? (t >> g.cand_shift) : t / g.ncand;
-        const int e = t - i * g.ncand;
-        int cz, cy, cx, rest;
-        split_small(e, g.span_max[2], &rest, &cx);
-        split_small(rest, g.span_max[1], &cz, &cy);
-        const int4 c4 = __ldg(&in_coors[(size_t)b * max_voxels + i]);
-        const int c[3] = {c4.y, c4.z, c4.w};
-        const int cj[3] = {cz, cy, cx};
-        int o[3];
-        bool ok = true;
-        int k = 0;
-#pragma unroll
-        for (int j = 0; j < 3; ++j) {
-            // C integer division, as in the reference (sparseConv3dlayer.cu:339-348); dilation is 1
-            const int lo = div_trunc(c[j] - (g.K[j] - 1) - 1 + g.S[j] + g.P[j], g.S[j]);
-            const int hi = div_trunc(c[j] + g.P[j], g.S[j]);
-            o[j] = hi - cj[j];
-            ok = ok && cj[j] <= hi - lo && o[j] >= 0 && o[j] < g.out_shape[j];
-            k = k * g.K[j] + (c[j] - o[j] * g.S[j] + g.P[j]);
-        }
-        int value = -1;
-        if (ok) {
-            const uint32_t key = ((uint32_t)o[0] * g.out_shape[1] + o[1]) * g.out_shape[2] + o[2];
-            // One 64-bit slot per cell: key in the high word, smallest entry index (rank) in the low word.
-            // A free slot is all ones, so both claiming a cell and lowering its rank are one atomic.
-            unsigned long long* slots =
-                reinterpret_cast<unsigned long long*>(out_table.rank) + (size_t)b * out_table.cap;
-            const unsigned long long mine = ((unsigned long long)key << 32) | (uint32_t)t;
-            uint32_t h = hash_slot(key, out_table.shift);
-            int slot = -1;
-            for (uint32_t probe = 0; probe < out_table.cap; ++probe) {
-                unsigned long long cur = slots[h];
-                if (cur == ~0ull) cur = atomicCAS(&slots[h], ~0ull, mine);
-                if (cur == ~0ull) {
-                    slot = (int)h;   // claimed with our rank
-                    break;
-                }
-                if ((uint32_t)(cur >> 32) == key) {
-                    if ((uint32_t)cur > (uint32_t)t) atomicMin(&slots[h], mine);
-                    slot = (int)h;
-                    break;
-                }
-                h = (h + 1) & (out_table.cap - 1);
-            }
-            if (slot < 0) atomicOr(status, SESSD_STATUS_HASH_FULL);
-            else value = (k << kSlotBits) | slot;
-        }
-        slot_of[(size_t)b * per_frame + t] = value;
-    }
-}
-
-struct OutputEmit {
-    Table t;
-    int Yo, Xo, max_voxels;
-    int32_t* out_coors;
-    int32_t* out_num;
-    int32_t* status;
-    __device__ void frame_total(int b, int total) const {
-        out_num[b] = total > max_voxels ? max_voxels : total;
-        if (total > max_voxels) atomicOr(status, SESSD_STATUS_VOXEL_OVERFLOW);
-    }
-    __device__ void operator()(int b, int /*e*/, int slot, int id) const {
-        const size_t gslot = (size_t)b * t.cap + (uint32_t)slot;
-        if (id >= max_voxels) {
-            t.vals[gslot] = -1;
-            return;
-        }
-        t.vals[gslot] = id;
-        const uint32_t key = t.keys[gslot * t.key_stride];
-        const int plane = Yo * Xo;
-        const int z = key / plane, rem = key - z * plane;
-        const int y = rem / Xo, x = rem - y * Xo;
-        reinterpret_cast<int4*>(out_coors)[(size_t)b * max_voxels + id] = make_int4(b, z, y, x);
-    }
-};
 
 // One block per kernel offset: compacts nbr[frame][k][*] into the reference's pair columns.
 __global__ void __launch_bounds__(kThreads)
@@ -387,13 +302,19 @@ nbr_build_subm_kernel(const int4* __restrict__ coors, const int32_t* __restrict_
     }
 }
 
-// Strided layers: the neighbour map falls out of the candidate entries. Entry t = (input row i, candidate e)
-// carries its table slot and kernel offset k; with output row id = vals[slot] it contributes
-// nbr[b][k][id] = i. The map must have been filled with -1 for rows < out_num beforehand.
+// ---- occupancy grids -----------------------------------------------------------------------------
+
+__device__ __forceinline__ unsigned long long rec_bits(const uint4& r) {
+    return (unsigned long long)r.x | ((unsigned long long)r.y << 32);
+}
+
+// Marks the candidate outputs of every input row. Thread = (input row i, candidate e), where
+// e = (cz * span_max_y + cy) * span_max_x + cx walks the row's candidate box from its upper corner downward:
+// the reference's enumeration (sparseConv3dlayer.cu:339-383). A bit that is already set is not set again,
+// so most threads finish with one L2 read.
 __global__ void __launch_bounds__(kThreads)
-nbr_scatter_strided_kernel(const int32_t* __restrict__ in_num, int batch, int max_voxels, ConvGeom g, Table out_table,
-                           const int32_t* __restrict__ slot_of, int32_t* __restrict__ nbr,
-                           uint32_t* __restrict__ tile_mask, int tiles_per_frame) {
+mark_outputs_kernel(const int4* __restrict__ in_coors, const int32_t* __restrict__ in_num, int batch, int max_voxels,
+                    ConvGeom g, BitGrid out) {
     const int64_t per_frame = (int64_t)max_voxels * g.ncand;
     const int chunks = (int)((per_frame + kThreads - 1) / kThreads);
     const int items = batch * chunks;
@@ -402,37 +323,242 @@ nbr_scatter_strided_kernel(const int32_t* __restrict__ in_num, int batch, int ma
         const int t = (it - b * chunks) * kThreads + threadIdx.x;
         int n = in_num[b];
         n = n > max_voxels ? max_voxels : n;
+        if ((it - b * chunks) * kThreads >= n * g.ncand) continue;   // uniform over the block
         if (t >= n * g.ncand) continue;
-        const int v = slot_of[(size_t)b * per_frame + t];
-        if (v < 0) continue;
-        const int id = out_table.vals[(size_t)b * out_table.cap + ((uint32_t)v & kSlotMask)];
-        if (id < 0) continue;  // output dropped by the max_voxels cap
-        const int k = v >> kSlotBits;
         const int i = g.cand_shift >= 0 ? (t >> g.cand_shift) : t / g.ncand;
-        nbr[((size_t)b * g.kvol + k) * max_voxels + id] = i;
-        uint32_t* m = &tile_mask[(size_t)b * tiles_per_frame + (id >> 7)];
-        if (!((*reinterpret_cast<volatile uint32_t*>(m) >> k) & 1u)) atomicOr(m, 1u << k);
+        const int e = t - i * g.ncand;
+        int cz, cy, cx, rest;
+        split_small(e, g.span_max[2], &rest, &cx);
+        split_small(rest, g.span_max[1], &cz, &cy);
+        const int4 c4 = __ldg(&in_coors[(size_t)b * max_voxels + i]);
+        const int c[3] = {c4.y, c4.z, c4.w};
+        const int cj[3] = {cz, cy, cx};
+        int o[3];
+        bool ok = true;
+#pragma unroll
+        for (int j = 0; j < 3; ++j) {
+            // C integer division, as in the reference (sparseConv3dlayer.cu:339-348); dilation is 1
+            const int lo = div_trunc(c[j] - (g.K[j] - 1) - 1 + g.S[j] + g.P[j], g.S[j]);
+            const int hi = div_trunc(c[j] + g.P[j], g.S[j]);
+            o[j] = hi - cj[j];
+            const int k = c[j] - o[j] * g.S[j] + g.P[j];   // the offset this pair would get (:366)
+            ok = ok && cj[j] <= hi - lo && o[j] >= 0 && o[j] < g.out_shape[j] && k >= 0 && k < g.K[j] &&
+                 c[j] >= 0 && c[j] < g.in_shape[j];
+        }
+        if (!ok) continue;
+        unsigned long long* word = reinterpret_cast<unsigned long long*>(
+            out.rec + (size_t)b * out.words + ((size_t)o[0] * out.Y + o[1]) * out.xw + (o[2] >> 6));
+        const unsigned long long bit = 1ull << (o[2] & 63);
+        if (!(*reinterpret_cast<volatile unsigned long long*>(word) & bit)) atomicOr(word, bit);
     }
 }
 
-// Fills nbr[b][k][0 .. out_num[b]) with -1 (one int4 per thread where aligned).
+// Set bits of every 1024-word chunk of every frame.
 __global__ void __launch_bounds__(kThreads)
-nbr_clear_kernel(int32_t* __restrict__ nbr, const int32_t* __restrict__ out_num, int batch, int max_voxels, int kvol) {
-    const int chunks = (max_voxels + kThreads * 4 - 1) / (kThreads * 4);
-    const int items = batch * kvol * chunks;
+count_bits_kernel(BitGrid g, int batch, int32_t* __restrict__ chunk_counts) {
+    const int items = batch * g.chunks;
     for (int it = blockIdx.x; it < items; it += gridDim.x) {
-        const int bk = it / chunks;
-        const int b = bk / kvol;
-        const int o = ((it - bk * chunks) * kThreads + threadIdx.x) * 4;
+        const int b = it / g.chunks, c = it - b * g.chunks;
+        const uint4* rec = g.rec + (size_t)b * g.words;
+        int cnt = 0;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int w = c * kChunk + threadIdx.x * 4 + j;
+            if (w < g.words) cnt += __popcll(rec_bits(rec[w]));
+        }
+        const int total = block_sum(cnt);
+        if (threadIdx.x == 0) chunk_counts[(size_t)b * g.chunks + c] = total;
+    }
+}
+
+// Numbers the set bits of a frame in word order (= (z, y, x) order): writes every word's prefix, the output
+// coordinates (sparseConv3dlayer.cu:436-441 writes them per pair) and the frame's row count. Rows past
+// max_voxels are dropped (their bits stay set; look-ups reject ids >= max_voxels) and reported.
+__global__ void __launch_bounds__(kThreads)
+number_outputs_kernel(BitGrid g, int batch, int max_voxels, const int32_t* __restrict__ chunk_counts,
+                      int4* __restrict__ out_coors, int32_t* __restrict__ out_num, int32_t* status) {
+    const int items = batch * g.chunks;
+    for (int it = blockIdx.x; it < items; it += gridDim.x) {
+        const int b = it / g.chunks, c = it - b * g.chunks;
+        const int32_t* counts = chunk_counts + (size_t)b * g.chunks;
+        if (c == 0) {
+            int partial = 0;
+            for (int j = threadIdx.x; j < g.chunks; j += kThreads) partial += counts[j];
+            const int total = block_sum(partial);
+            if (threadIdx.x == 0) {
+                out_num[b] = total > max_voxels ? max_voxels : total;
+                if (total > max_voxels) atomicOr(status, SESSD_STATUS_VOXEL_OVERFLOW);
+            }
+        }
+        int partial = 0;
+        for (int j = threadIdx.x; j < c; j += kThreads) partial += counts[j];
+        const int base = block_sum(partial);
+        uint4* rec = g.rec + (size_t)b * g.words;
+        unsigned long long bits[4];
+        int cnt = 0;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int w = c * kChunk + threadIdx.x * 4 + j;
+            bits[j] = w < g.words ? rec_bits(rec[w]) : 0ull;
+            cnt += __popcll(bits[j]);
+        }
+        int unused;
+        int id = base + block_exclusive_scan(cnt, &unused);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int w = c * kChunk + threadIdx.x * 4 + j;
+            if (w >= g.words) continue;
+            rec[w].z = (uint32_t)id;
+            unsigned long long rem = bits[j];
+            if (!rem) continue;
+            const int row = w / g.xw;                 // z * Y + y
+            const int x0 = (w - row * g.xw) << 6;
+            const int z = row / g.Y, y = row - z * g.Y;
+            while (rem) {
+                const int bit = __ffsll((long long)rem) - 1;
+                rem &= rem - 1ull;
+                if (id < max_voxels) out_coors[(size_t)b * max_voxels + id] = make_int4(b, z, y, x0 + bit);
+                ++id;
+            }
+        }
+    }
+}
+
+// Rows of up to three x-neighbours (x0, x0+1, x0+2; `count` of them) of one (z, y) line of the input level.
+struct BitsIndex {
+    BitGrid g;
+    int max_rows;
+    struct Probe { uint4 a, b; int w; bool two; };
+    __device__ __forceinline__ void probe(int b, int z, int y, int x0, int count, bool on, Probe* p) const {
+        p->a = p->b = make_uint4(0u, 0u, 0u, 0u);
+        p->two = false;
+        p->w = 0;
+        if (!on) return;
+        const int lo = x0 < 0 ? 0 : x0, hi = x0 + count - 1 >= g.X ? g.X - 1 : x0 + count - 1;
+        if (lo > hi) return;
+        const uint4* rec = g.rec + (size_t)b * g.words + ((size_t)z * g.Y + y) * g.xw;
+        p->w = lo >> 6;
+        p->a = __ldg(rec + p->w);
+        p->two = (hi >> 6) != p->w;
+        if (p->two) p->b = __ldg(rec + p->w + 1);
+    }
+    __device__ __forceinline__ int finish(const Probe& p, int x) const {
+        if (x < 0 || x >= g.X) return -1;
+        const uint4& r = (x >> 6) == p.w ? p.a : p.b;
+        if ((x >> 6) != p.w && !p.two) return -1;
+        const unsigned long long bits = rec_bits(r);
+        const int bit = x & 63;
+        if (!((bits >> bit) & 1ull)) return -1;
+        const int id = (int)r.z + __popcll(bits & ((1ull << bit) - 1ull));
+        return id < max_rows ? id : -1;
+    }
+};
+
+struct BucketIndex {
+    Buckets t;
+    int Y, X;
+    struct Probe { BucketProbe a, b; uint32_t ga, gb; uint32_t center; bool on; };
+    __device__ __forceinline__ void probe(int b, int z, int y, int x0, int count, bool on, Probe* p) const {
+        const uint32_t* base = t.data + (size_t)b * t.cap * 8;
+        const int lo = x0 < 0 ? 0 : x0, hi = x0 + count - 1 >= X ? X - 1 : x0 + count - 1;
+        p->on = on && lo <= hi;
+        p->center = p->on ? ((uint32_t)z * Y + y) * X : 0u;   // key of x = 0 on this line
+        p->ga = (p->center + (uint32_t)(p->on ? lo : 0)) >> 2;
+        p->gb = (p->center + (uint32_t)(p->on ? hi : 0)) >> 2;
+        bucket_probe(base, t.shift, p->ga, p->on, &p->a);
+        bucket_probe(base, t.shift, p->gb, p->on && p->gb != p->ga, &p->b);
+    }
+    __device__ __forceinline__ int finish(int b, const Probe& p, int x, int4* va, int4* vb, bool* done) const {
+        if (!p.on || x < 0 || x >= X) return -1;
+        const uint32_t* base = t.data + (size_t)b * t.cap * 8;
+        if (!*done) {
+            *va = bucket_finish(base, t.cap, p.ga, p.a);
+            *vb = p.gb != p.ga ? bucket_finish(base, t.cap, p.gb, p.b) : *va;
+            *done = true;
+        }
+        const uint32_t key = p.center + (uint32_t)x;
+        return pick4((key >> 2) == p.ga ? *va : *vb, key & 3u);
+    }
+};
+
+// kind: 0 = occupancy grid of the input level, 1 = x-grouped table, 2 = flat table.
+struct InputIndexDev {
+    int kind;
+    BitsIndex bits;
+    BucketIndex buckets;
+    Table table;
+};
+
+// Neighbour map of any layer whose output rows and input index exist: one thread per output row walks the
+// K0 x K1 lines of its receptive field, has the index reads of a kz plane in flight together, and writes
+// nbr[b][k][o] (coalesced over o) plus the per-128-row-tile offset mask (one ballot per offset, one atomic
+// per warp). in = out*stride - pad + k, the inverse of the offset formula at submConv3dlayer.cu:328.
+template <int KIND>
+__global__ void __launch_bounds__(kThreads, 4)
+map_rows_kernel(const int4* __restrict__ out_coors, const int32_t* __restrict__ out_num, int batch, int max_voxels,
+                ConvGeom g, InputIndexDev in, int32_t* __restrict__ nbr, uint32_t* __restrict__ tile_mask,
+                int tiles_per_frame) {
+    const int chunks = (max_voxels + kThreads - 1) / kThreads;
+    const int items = batch * chunks;
+    const int K0 = g.K[0], K1 = g.K[1], K2 = g.K[2];
+    for (int it = blockIdx.x; it < items; it += gridDim.x) {
+        const int b = it / chunks;
+        const int o0 = (it - b * chunks) * kThreads;
         int n = out_num[b];
         n = n > max_voxels ? max_voxels : n;
-        if (o >= n) continue;
-        int32_t* p = nbr + (size_t)bk * max_voxels + o;
-        if ((max_voxels & 3) == 0) {
-            *reinterpret_cast<int4*>(p) = make_int4(-1, -1, -1, -1);   // may run up to 3 rows past n: inside the row block
-        } else {
-            for (int q = 0; q < 4 && o + q < max_voxels; ++q) p[q] = -1;
+        if (o0 >= n) continue;
+        const int o = o0 + threadIdx.x;
+        const bool live = o < n;
+        int4 c = make_int4(0, 0, 0, 0);
+        if (live) c = __ldg(&out_coors[(size_t)b * max_voxels + o]);
+        const int bz = c.y * g.S[0] - g.P[0], by = c.z * g.S[1] - g.P[1], bx = c.w * g.S[2] - g.P[2];
+        int32_t* out = nbr + (size_t)b * g.kvol * max_voxels + o;
+        uint32_t bits = 0;
+#pragma unroll
+        for (int kz = 0; kz < 3; ++kz) {
+            if (kz >= K0) break;
+            const int z = bz + kz;
+            const bool z_ok = live && z >= 0 && z < g.in_shape[0];
+            BitsIndex::Probe pb[3];
+            BucketIndex::Probe pk[3];
+#pragma unroll
+            for (int ky = 0; ky < 3; ++ky) {
+                if (ky >= K1) break;
+                const int y = by + ky;
+                const bool on = z_ok && y >= 0 && y < g.in_shape[1];
+                if (KIND == 0) in.bits.probe(b, z, y, bx, K2, on, &pb[ky]);
+                if (KIND == 1) in.buckets.probe(b, z, y, bx, K2, on, &pk[ky]);
+            }
+#pragma unroll
+            for (int ky = 0; ky < 3; ++ky) {
+                if (ky >= K1) break;
+                const int y = by + ky;
+                const bool on = z_ok && y >= 0 && y < g.in_shape[1];
+                int4 va, vb;
+                bool done = false;
+#pragma unroll
+                for (int kx = 0; kx < 3; ++kx) {
+                    if (kx >= K2) break;
+                    const int x = bx + kx;
+                    int row = -1;
+                    if (on) {
+                        if (KIND == 0) row = in.bits.finish(pb[ky], x);
+                        if (KIND == 1) row = in.buckets.finish(b, pk[ky], x, &va, &vb, &done);
+                        if (KIND == 2 && x >= 0 && x < g.in_shape[2]) {
+                            const uint32_t key = ((uint32_t)z * g.in_shape[1] + y) * g.in_shape[2] + x;
+                            const int slot = table_find(in.table.keys + (size_t)b * in.table.cap, in.table.cap,
+                                                        in.table.shift, key);
+                            if (slot >= 0) row = in.table.vals[(size_t)b * in.table.cap + slot];
+                        }
+                    }
+                    const int k = (kz * K1 + ky) * K2 + kx;
+                    if (live) out[(size_t)k * max_voxels] = row;
+                    if (__ballot_sync(0xFFFFFFFFu, row >= 0)) bits |= 1u << k;
+                }
+            }
         }
+        if ((threadIdx.x & 31) == 0 && bits && live)
+            atomicOr(&tile_mask[(size_t)b * tiles_per_frame + (o >> 7)], bits);
     }
 }
 
@@ -472,16 +598,6 @@ int launch_nbr_build_subm(const int32_t* coors, const int32_t* voxel_num, int ba
     SESSD_LAUNCH(nbr_build_subm_kernel, persistent_grid(8), kThreads, 0, stream, reinterpret_cast<const int4*>(coors),
                  voxel_num, batch, max_voxels, shape[0], shape[1], shape[2], t, nbr, tile_mask,
                  (max_voxels + 127) / 128);
-    return SESSD_OK;
-}
-
-int launch_nbr_scatter_strided(const int32_t* in_coors, const int32_t* in_num, const int32_t* out_num, int batch,
-                               int max_voxels, const ConvGeom& g, const Table& out_table, const int32_t* slot_of,
-                               int32_t* nbr, uint32_t* tile_mask, cudaStream_t stream) {
-    SESSD_LAUNCH(nbr_clear_kernel, persistent_grid(8), kThreads, 0, stream, nbr, out_num, batch, max_voxels, g.kvol);
-    (void)in_coors;   // the entries carry their kernel offset; coordinates are not needed again
-    SESSD_LAUNCH(nbr_scatter_strided_kernel, persistent_grid(8), kThreads, 0, stream, in_num, batch, max_voxels, g, out_table, slot_of, nbr,
-                 tile_mask, (max_voxels + 127) / 128);
     return SESSD_OK;
 }
 
@@ -545,25 +661,39 @@ int launch_nbr_build(const int32_t* out_coors, const int32_t* out_num, int batch
     return SESSD_OK;
 }
 
-int launch_spconv_outputs(const int32_t* in_coors, const int32_t* in_num, int batch, int max_voxels, const ConvGeom& g,
-                          const Table& out_table, int32_t* slot_of, int32_t* chunk_counts, int chunks_per_frame,
-                          int32_t* out_coors, int32_t* out_num, int32_t* status, cudaStream_t stream) {
-    SESSD_LAUNCH(spconv_candidates_kernel, persistent_grid(8), kThreads, 0, stream,
-                 reinterpret_cast<const int4*>(in_coors), in_num, batch, max_voxels, g, out_table, slot_of, status);
-    NumberingArgs a{};
-    a.slot_of = slot_of;
-    a.entry_stride = (int64_t)max_voxels * g.ncand;
-    a.entry_count = in_num;
-    a.entry_mul = g.ncand;
-    a.slot_mask = kSlotMask;
-    a.entry_limit = max_voxels;
-    a.chunk_counts = chunk_counts;
-    a.chunks_per_frame = chunks_per_frame;
-    a.batch = batch;
-    int rc = launch_count_owners(a, out_table, stream);
-    if (rc) return rc;
-    OutputEmit e{out_table, g.out_shape[1], g.out_shape[2], max_voxels, out_coors, out_num, status};
-    SESSD_LAUNCH(emit_owners_kernel<OutputEmit>, persistent_grid(8), kThreads, 0, stream, a, out_table, e);
+int launch_mark_outputs(const int32_t* in_coors, const int32_t* in_num, int batch, int max_voxels, const ConvGeom& g,
+                        const BitGrid& out, cudaStream_t stream) {
+    SESSD_LAUNCH(mark_outputs_kernel, persistent_grid(8), kThreads, 0, stream, reinterpret_cast<const int4*>(in_coors),
+                 in_num, batch, max_voxels, g, out);
+    return SESSD_OK;
+}
+
+int launch_number_outputs(const BitGrid& out, int batch, int max_voxels, int32_t* chunk_counts, int32_t* out_coors,
+                          int32_t* out_num, int32_t* status, cudaStream_t stream) {
+    SESSD_LAUNCH(count_bits_kernel, persistent_grid(8), kThreads, 0, stream, out, batch, chunk_counts);
+    SESSD_LAUNCH(number_outputs_kernel, persistent_grid(8), kThreads, 0, stream, out, batch, max_voxels, chunk_counts,
+                 reinterpret_cast<int4*>(out_coors), out_num, status);
+    return SESSD_OK;
+}
+
+int launch_map_rows(const int32_t* out_coors, const int32_t* out_num, int batch, int max_voxels, const ConvGeom& g,
+                    const InputIndex& in, int32_t* nbr, uint32_t* tile_mask, cudaStream_t stream) {
+    InputIndexDev d{};
+    d.kind = in.kind;
+    d.bits = BitsIndex{in.bits, max_voxels};
+    d.buckets = BucketIndex{in.buckets, g.in_shape[1], g.in_shape[2]};
+    d.table = in.table;
+    const int tiles = (max_voxels + 127) / 128;
+    const int4* oc = reinterpret_cast<const int4*>(out_coors);
+    if (in.kind == 0)
+        SESSD_LAUNCH_NAMED("map_rows_kernel<grid>", map_rows_kernel<0>, persistent_grid(8), kThreads, 0, stream, oc, out_num,
+                           batch, max_voxels, g, d, nbr, tile_mask, tiles);
+    else if (in.kind == 1)
+        SESSD_LAUNCH_NAMED("map_rows_kernel<buckets>", map_rows_kernel<1>, persistent_grid(8), kThreads, 0, stream, oc,
+                           out_num, batch, max_voxels, g, d, nbr, tile_mask, tiles);
+    else
+        SESSD_LAUNCH_NAMED("map_rows_kernel<table>", map_rows_kernel<2>, persistent_grid(8), kThreads, 0, stream, oc,
+                           out_num, batch, max_voxels, g, d, nbr, tile_mask, tiles);
     return SESSD_OK;
 }
 

@@ -61,6 +61,24 @@ def canonical_voxels(coors, n, grid_zyx):
     return order, key[order]
 
 
+def match_rows(got_coors, want_coors):
+    """Index array `perm` with got_coors[perm] == want_coors, row for row: the library numbers the outputs of a
+    strided layer in (z, y, x) order, the oracle in first-seen order (the reference: arrival order of an atomic),
+    and the contract is equality after canonical sorting. Fails when the two coordinate sets differ."""
+    def keys(c):
+        c = np.asarray(c).astype(np.int64)
+        return ((c[:, 0] * 4096 + c[:, 1]) * 4096 + c[:, 2]) * 4096 + c[:, 3]
+
+    kg, kw = keys(got_coors), keys(want_coors)
+    assert len(kg) == len(kw)
+    og, ow = np.argsort(kg, kind="stable"), np.argsort(kw, kind="stable")
+    np.testing.assert_array_equal(kg[og], kw[ow])
+    assert len(np.unique(kw)) == len(kw)
+    perm = np.empty(len(kw), np.int64)
+    perm[ow] = og
+    return perm
+
+
 def canonical_rulebook(pairs, pair_num, in_coors, out_coors, in_shape, out_shape):
     """Rulebook as a sorted array of (k, in_key, out_key) triples: independent of row numbering."""
     def keys(c, shape):

@@ -6,7 +6,7 @@ repeats the oracle's summation order, so they are in fact identical); fp16 withi
 import numpy as np
 import pytest
 
-from conftest import canonical_rulebook, rel_err
+from conftest import canonical_rulebook, match_rows, rel_err
 
 pytestmark = pytest.mark.gpu
 
@@ -79,8 +79,15 @@ def _check_layer(gpu, oracle, layer, frames, W, scale=None, shift=None, relu=Fal
             oc, on, pairs, pnum, st = oracle.spconv_rulebook(c, n, layer.ksize, layer.stride, layer.padding,
                                                              layer.out_shape, maxV)
         assert st == 0 and g["num"] == on
-        # row numbering is reproduced exactly (first-seen order) ...
-        np.testing.assert_array_equal(g["coors"][:on], oc[:on])
+        # the same set of output coordinates (a submanifold layer keeps the caller's rows; a strided layer numbers
+        # its outputs in (z, y, x) order, the oracle in first-seen order) ...
+        perm = match_rows(g["coors"][:on], oc[:on])
+        if layer.subm:
+            np.testing.assert_array_equal(perm, np.arange(on))
+        else:
+            gk = g["coors"][:on].astype(np.int64)
+            lin = (gk[:, 1] * layer.out_shape[1] + gk[:, 2]) * layer.out_shape[2] + gk[:, 3]
+            assert (np.diff(lin) > 0).all()
         assert not g["coors"][on:].any()
         # ... and the rulebook is identical after canonical sorting, with identical per-offset counts
         np.testing.assert_array_equal(g["pair_num"], pnum)
@@ -93,7 +100,7 @@ def _check_layer(gpu, oracle, layer, frames, W, scale=None, shift=None, relu=Fal
             want = oracle.scale_shift_relu(want, scale, shift, relu, half_out=half)
         elif half:
             want = want.astype(np.float16).astype(np.float32)
-        got = g["features"][:on]
+        got = g["features"][:on][perm]
         assert rel_err(got, want) <= tol, rel_err(got, want)
         if not half:
             np.testing.assert_array_equal(got, want)   # same summation order as the oracle
@@ -187,6 +194,9 @@ def test_every_cell_active_tiny_grid(gpu, oracle):
 
 
 def test_output_overflow_sets_status_and_truncates(gpu, oracle):
+    """More active outputs than max_voxels: the status bit is set, exactly max_voxels rows come back, they are the
+    first max_voxels of the full output set in (z, y, x) order, and their features are those of the untruncated
+    layer (the reference writes past its buffers in this situation)."""
     rs = np.random.RandomState(9)
     shape = (9, 22, 26)
     c = _random_coords(rs, 600, shape)
@@ -198,8 +208,14 @@ def test_output_overflow_sets_status_and_truncates(gpu, oracle):
                                                      layer.out_shape, 640)
     assert st & oracle.VOXEL_OVERFLOW and res[0]["status"] & gpu.STATUS_VOXEL_OVERFLOW
     assert res[0]["num"] == on == 640
-    np.testing.assert_array_equal(res[0]["coors"][:on], oc[:on])
-    np.testing.assert_array_equal(res[0]["features"][:on], oracle.conv_apply(f, pairs, pnum, W, on))
+    fc, fn, fpairs, fpnum, fst = oracle.spconv_rulebook(c, len(c), layer.ksize, layer.stride, layer.padding,
+                                                        layer.out_shape, 8192)
+    assert fst == 0 and fn > 640
+    full = oracle.conv_apply(f, fpairs, fpnum, W, fn)
+    lin = (fc[:fn, 1].astype(np.int64) * layer.out_shape[1] + fc[:fn, 2]) * layer.out_shape[2] + fc[:fn, 3]
+    first = np.argsort(lin)[:640]
+    np.testing.assert_array_equal(res[0]["coors"][:640], fc[first])
+    np.testing.assert_array_equal(res[0]["features"][:640], full[first])
 
 
 def test_bad_coordinate_is_reported_not_dereferenced(gpu):
