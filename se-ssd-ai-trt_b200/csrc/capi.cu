@@ -80,7 +80,7 @@ struct ConvWorkspace {
     void* ones_base;      // tables: every word 0xFFFFFFFF before use
     size_t ones_bytes;
     Buckets buckets;      // submanifold 3x3x3: x-grouped table of the input coordinates
-    Table in_table;       // every other layer: flat table of the input coordinates
+    Table in_table;       // other submanifold geometries: flat table of the input coordinates
     BitGrid out_bits;     // strided: occupancy grid of the output level
     void* zero_base;      // occupancy grid + tile masks: zero before use
     size_t zero_bytes;
@@ -106,10 +106,6 @@ void conv_workspace_layout(Bump& bump, const sessd_conv_params* p, const ConvGeo
         w->ones_base = block;
         w->ones_bytes = per * 2 * sizeof(uint32_t);
     } else {
-        uint32_t* block = bump.take<uint32_t>(per * 2);
-        w->in_table = Table{block, nullptr, reinterpret_cast<int32_t*>(block ? block + per : nullptr), cap, shift, 1, 1};
-        w->ones_base = block;
-        w->ones_bytes = per * 2 * sizeof(uint32_t);
         w->out_bits = bitgrid_shape(g.out_shape);
         w->chunk_counts = bump.take<int32_t>((size_t)batch * w->out_bits.chunks);
     }
@@ -453,8 +449,10 @@ static int conv_enqueue_common(const sessd_conv_params* p, const sessd_conv_weig
     const int32_t* in_coors = static_cast<const int32_t*>(inputs[1]);
     const int32_t* in_num = static_cast<const int32_t*>(inputs[2]);
     SESSD_CUDA(cudaMemsetAsync(ws.status, 0, kStatusInts * sizeof(int32_t), stream));
-    rc = launch_fill_ones(ws.ones_base, ws.ones_bytes, stream);
-    if (rc) return rc;
+    if (ws.ones_bytes) {
+        rc = launch_fill_ones(ws.ones_base, ws.ones_bytes, stream);
+        if (rc) return rc;
+    }
     rc = launch_fill_zero(ws.zero_base, ws.zero_bytes, stream);
     if (rc) return rc;
     const int32_t* out_num = in_num;
@@ -471,20 +469,14 @@ static int conv_enqueue_common(const sessd_conv_params* p, const sessd_conv_weig
         rc = launch_tile_mask(ws.nbr, in_num, batch, maxV, g.kvol, ws.tile_mask, stream);
         if (rc) return rc;
     } else {
-        // the caller's input rows come in any order: a flat table turns coordinates back into rows
-        rc = launch_table_build(in_coors, in_num, batch, maxV, g.in_shape, ws.in_table, ws.status, stream);
-        if (rc) return rc;
         rc = launch_mark_outputs(in_coors, in_num, batch, maxV, g, ws.out_bits, stream);
         if (rc) return rc;
         rc = launch_number_outputs(ws.out_bits, batch, maxV, ws.chunk_counts, static_cast<int32_t*>(outputs[1]),
                                    static_cast<int32_t*>(outputs[2]), ws.status, stream);
         if (rc) return rc;
         out_num = static_cast<const int32_t*>(outputs[2]);
-        InputIndex idx{};
-        idx.kind = 2;
-        idx.table = ws.in_table;
-        rc = launch_map_rows(static_cast<const int32_t*>(outputs[1]), out_num, batch, maxV, g, idx, ws.nbr, ws.tile_mask,
-                             stream);
+        // the caller's input rows come in any order and have no grid of their own: input-stationary map
+        rc = launch_scatter_rows(in_coors, in_num, out_num, batch, maxV, g, ws.out_bits, ws.nbr, ws.tile_mask, stream);
         if (rc) return rc;
     }
     ConvLaunch c{};
@@ -707,38 +699,24 @@ static int backbone_enqueue_impl(const sessd_backbone* bb, int batch, int max_po
                       /*zero_tail=*/false, stream);
     if (rc) return rc;
     std::vector<char> nbr_ready(bb->nlevels, 0);
-    bool buckets0_ready = false;
-    // how the rows of a level are found from coordinates: level 0 through the x-grouped table of the
-    // voxeliser's rows, every derived level through the occupancy grid that numbered it
-    auto input_index = [&](int level, InputIndex* idx) -> int {
-        *idx = InputIndex{};
-        if (level > 0) {
-            idx->kind = 0;
-            idx->bits = w.bits[level];
-            return SESSD_OK;
-        }
-        idx->kind = 1;
-        idx->buckets = w.buckets0;
-        if (buckets0_ready) return SESSD_OK;
-        buckets0_ready = true;
-        return launch_bucket_build(w.coors[0], w.num[0], batch, maxV, &bb->level_shape[0], w.buckets0, w.status, stream);
-    };
     const void* cur = w.voxel_feat;
     for (size_t i = 0; i < bb->layers.size(); ++i) {
         const sessd_backbone::Layer& L = bb->layers[i];
         const int32_t* nbr;
         const uint32_t* tile_mask;
-        InputIndex idx;
         if (L.p.subm) {
             if (!nbr_ready[L.level_in]) {
-                rc = input_index(L.level_in, &idx);
-                if (rc) return rc;
-                if (L.level_in == 0)
+                if (L.level_in == 0) {
+                    // the voxeliser's rows: x-grouped table, then one thread per row looks its 27 neighbours up
+                    rc = launch_bucket_build(w.coors[0], w.num[0], batch, maxV, &bb->level_shape[0], w.buckets0, w.status,
+                                             stream);
+                    if (rc) return rc;
                     rc = launch_nbr_build_subm(w.coors[0], w.num[0], batch, maxV, L.g.in_shape, w.buckets0, w.nbr_subm[0],
                                                w.mask_subm[0], stream);
-                else
-                    rc = launch_map_rows(w.coors[L.level_in], w.num[L.level_in], batch, maxV, L.g, idx,
+                } else {
+                    rc = launch_map_rows(w.coors[L.level_in], w.num[L.level_in], batch, maxV, L.g, w.bits[L.level_in],
                                          w.nbr_subm[L.level_in], w.mask_subm[L.level_in], stream);
+                }
                 if (rc) return rc;
                 nbr_ready[L.level_in] = 1;
             }
@@ -750,10 +728,12 @@ static int backbone_enqueue_impl(const sessd_backbone* bb, int batch, int max_po
             rc = launch_number_outputs(w.bits[L.level_out], batch, maxV, w.chunk_counts, w.coors[L.level_out],
                                        w.num[L.level_out], w.status, stream);
             if (rc) return rc;
-            rc = input_index(L.level_in, &idx);
-            if (rc) return rc;
-            rc = launch_map_rows(w.coors[L.level_out], w.num[L.level_out], batch, maxV, L.g, idx, w.nbr_strided,
-                                 w.mask_layer[i], stream);
+            if (L.level_in == 0)   // no grid for the voxeliser's rows: every candidate finds its output row instead
+                rc = launch_scatter_rows(w.coors[0], w.num[0], w.num[L.level_out], batch, maxV, L.g, w.bits[L.level_out],
+                                         w.nbr_strided, w.mask_layer[i], stream);
+            else
+                rc = launch_map_rows(w.coors[L.level_out], w.num[L.level_out], batch, maxV, L.g, w.bits[L.level_in],
+                                     w.nbr_strided, w.mask_layer[i], stream);
             if (rc) return rc;
             nbr = w.nbr_strided;
             tile_mask = w.mask_layer[i];

@@ -247,17 +247,15 @@ int launch_mark_outputs(const int32_t* in_coors, const int32_t* in_num, int batc
                         const BitGrid& out, cudaStream_t stream);
 int launch_number_outputs(const BitGrid& out, int batch, int max_voxels, int32_t* chunk_counts, int32_t* out_coors,
                           int32_t* out_num, int32_t* status, cudaStream_t stream);
-// How the rows of a layer's input level are found from coordinates: 0 = occupancy grid, 1 = x-grouped table,
-// 2 = flat table.
-struct InputIndex {
-    int kind;
-    BitGrid bits;
-    Buckets buckets;
-    Table table;
-};
-// Neighbour map + tile masks of a layer (any kernel up to 3x3x3, any stride) from its output rows.
+// Neighbour map + tile masks of a layer (any kernel up to 3x3x3, any stride) whose input level has an occupancy
+// grid: output-stationary, one thread per output row.
 int launch_map_rows(const int32_t* out_coors, const int32_t* out_num, int batch, int max_voxels, const ConvGeom& g,
-                    const InputIndex& in, int32_t* nbr, uint32_t* tile_mask, cudaStream_t stream);
+                    const BitGrid& in, int32_t* nbr, uint32_t* tile_mask, cudaStream_t stream);
+// The same for a strided layer whose input rows have no grid (voxeliser rows, caller's rows): input-stationary,
+// every candidate of every input row finds its output row in the numbered output grid. Clears the map first.
+int launch_scatter_rows(const int32_t* in_coors, const int32_t* in_num, const int32_t* out_num, int batch,
+                        int max_voxels, const ConvGeom& g, const BitGrid& out, int32_t* nbr, uint32_t* tile_mask,
+                        cudaStream_t stream);
 int launch_bucket_build(const int32_t* coors, const int32_t* voxel_num, int batch, int max_voxels, const int shape[3],
                         const Buckets& t, int32_t* status, cudaStream_t stream);
 // 3x3x3 / stride 1 / pad 1 neighbour map from a bucket table, plus the per-128-row-tile offset masks.

@@ -454,49 +454,13 @@ struct BitsIndex {
     }
 };
 
-struct BucketIndex {
-    Buckets t;
-    int Y, X;
-    struct Probe { BucketProbe a, b; uint32_t ga, gb; uint32_t center; bool on; };
-    __device__ __forceinline__ void probe(int b, int z, int y, int x0, int count, bool on, Probe* p) const {
-        const uint32_t* base = t.data + (size_t)b * t.cap * 8;
-        const int lo = x0 < 0 ? 0 : x0, hi = x0 + count - 1 >= X ? X - 1 : x0 + count - 1;
-        p->on = on && lo <= hi;
-        p->center = p->on ? ((uint32_t)z * Y + y) * X : 0u;   // key of x = 0 on this line
-        p->ga = (p->center + (uint32_t)(p->on ? lo : 0)) >> 2;
-        p->gb = (p->center + (uint32_t)(p->on ? hi : 0)) >> 2;
-        bucket_probe(base, t.shift, p->ga, p->on, &p->a);
-        bucket_probe(base, t.shift, p->gb, p->on && p->gb != p->ga, &p->b);
-    }
-    __device__ __forceinline__ int finish(int b, const Probe& p, int x, int4* va, int4* vb, bool* done) const {
-        if (!p.on || x < 0 || x >= X) return -1;
-        const uint32_t* base = t.data + (size_t)b * t.cap * 8;
-        if (!*done) {
-            *va = bucket_finish(base, t.cap, p.ga, p.a);
-            *vb = p.gb != p.ga ? bucket_finish(base, t.cap, p.gb, p.b) : *va;
-            *done = true;
-        }
-        const uint32_t key = p.center + (uint32_t)x;
-        return pick4((key >> 2) == p.ga ? *va : *vb, key & 3u);
-    }
-};
-
-// kind: 0 = occupancy grid of the input level, 1 = x-grouped table, 2 = flat table.
-struct InputIndexDev {
-    int kind;
-    BitsIndex bits;
-    BucketIndex buckets;
-    Table table;
-};
-
-// Neighbour map of any layer whose output rows and input index exist: one thread per output row walks the
-// K0 x K1 lines of its receptive field, has the index reads of a kz plane in flight together, and writes
+// Neighbour map of a layer whose input level has an occupancy grid: one thread per output row walks the
+// K0 x K1 lines of its receptive field, has the grid reads of a kz plane in flight together, and writes
 // nbr[b][k][o] (coalesced over o) plus the per-128-row-tile offset mask (one ballot per offset, one atomic
 // per warp). in = out*stride - pad + k, the inverse of the offset formula at submConv3dlayer.cu:328.
-template <int KIND>
 __global__ void __launch_bounds__(kThreads, 4)
 map_rows_kernel(const int4* __restrict__ out_coors, const int32_t* __restrict__ out_num, int batch, int max_voxels,
-                ConvGeom g, InputIndexDev in, int32_t* __restrict__ nbr, uint32_t* __restrict__ tile_mask,
+                ConvGeom g, BitsIndex in, int32_t* __restrict__ nbr, uint32_t* __restrict__ tile_mask,
                 int tiles_per_frame) {
     const int chunks = (max_voxels + kThreads - 1) / kThreads;
     const int items = batch * chunks;
@@ -520,37 +484,22 @@ map_rows_kernel(const int4* __restrict__ out_coors, const int32_t* __restrict__ 
             const int z = bz + kz;
             const bool z_ok = live && z >= 0 && z < g.in_shape[0];
             BitsIndex::Probe pb[3];
-            BucketIndex::Probe pk[3];
 #pragma unroll
             for (int ky = 0; ky < 3; ++ky) {
                 if (ky >= K1) break;
                 const int y = by + ky;
-                const bool on = z_ok && y >= 0 && y < g.in_shape[1];
-                if (KIND == 0) in.bits.probe(b, z, y, bx, K2, on, &pb[ky]);
-                if (KIND == 1) in.buckets.probe(b, z, y, bx, K2, on, &pk[ky]);
+                in.probe(b, z, y, bx, K2, z_ok && y >= 0 && y < g.in_shape[1], &pb[ky]);
             }
 #pragma unroll
             for (int ky = 0; ky < 3; ++ky) {
                 if (ky >= K1) break;
                 const int y = by + ky;
                 const bool on = z_ok && y >= 0 && y < g.in_shape[1];
-                int4 va, vb;
-                bool done = false;
 #pragma unroll
                 for (int kx = 0; kx < 3; ++kx) {
                     if (kx >= K2) break;
                     const int x = bx + kx;
-                    int row = -1;
-                    if (on) {
-                        if (KIND == 0) row = in.bits.finish(pb[ky], x);
-                        if (KIND == 1) row = in.buckets.finish(b, pk[ky], x, &va, &vb, &done);
-                        if (KIND == 2 && x >= 0 && x < g.in_shape[2]) {
-                            const uint32_t key = ((uint32_t)z * g.in_shape[1] + y) * g.in_shape[2] + x;
-                            const int slot = table_find(in.table.keys + (size_t)b * in.table.cap, in.table.cap,
-                                                        in.table.shift, key);
-                            if (slot >= 0) row = in.table.vals[(size_t)b * in.table.cap + slot];
-                        }
-                    }
+                    const int row = on ? in.finish(pb[ky], x) : -1;
                     const int k = (kz * K1 + ky) * K2 + kx;
                     if (live) out[(size_t)k * max_voxels] = row;
                     if (__ballot_sync(0xFFFFFFFFu, row >= 0)) bits |= 1u << k;
@@ -559,6 +508,78 @@ map_rows_kernel(const int4* __restrict__ out_coors, const int32_t* __restrict__ 
         }
         if ((threadIdx.x & 31) == 0 && bits && live)
             atomicOr(&tile_mask[(size_t)b * tiles_per_frame + (o >> 7)], bits);
+    }
+}
+
+// Fills nbr[b][k][0 .. out_num[b]) with -1 (one int4 per thread where aligned).
+__global__ void __launch_bounds__(kThreads)
+nbr_clear_kernel(int32_t* __restrict__ nbr, const int32_t* __restrict__ out_num, int batch, int max_voxels, int kvol) {
+    const int chunks = (max_voxels + kThreads * 4 - 1) / (kThreads * 4);
+    const int items = batch * kvol * chunks;
+    for (int it = blockIdx.x; it < items; it += gridDim.x) {
+        const int bk = it / chunks;
+        const int b = bk / kvol;
+        const int o = ((it - bk * chunks) * kThreads + threadIdx.x) * 4;
+        int n = out_num[b];
+        n = n > max_voxels ? max_voxels : n;
+        if (o >= n) continue;
+        int32_t* p = nbr + (size_t)bk * max_voxels + o;
+        if ((max_voxels & 3) == 0) {
+            *reinterpret_cast<int4*>(p) = make_int4(-1, -1, -1, -1);   // may run up to 3 rows past n: inside the row block
+        } else {
+            for (int q = 0; q < 4 && o + q < max_voxels; ++q) p[q] = -1;
+        }
+    }
+}
+
+// Neighbour map of a strided layer whose input rows have no occupancy grid (the voxeliser's rows, or rows handed
+// in by a caller): input-stationary. Thread = (input row i, candidate e) as in mark_outputs_kernel; the candidate's
+// row in the numbered output grid is one read, and the pair lands as nbr[b][k][out] = i with
+// k = in - out*stride + pad per axis (sparseConv3dlayer.cu:366). Each (k, out) has at most one input, so the
+// writes never collide. The map must hold -1 for rows < out_num beforehand.
+__global__ void __launch_bounds__(kThreads)
+scatter_rows_kernel(const int4* __restrict__ in_coors, const int32_t* __restrict__ in_num, int batch, int max_voxels,
+                    ConvGeom g, BitsIndex out, int32_t* __restrict__ nbr, uint32_t* __restrict__ tile_mask,
+                    int tiles_per_frame) {
+    const int64_t per_frame = (int64_t)max_voxels * g.ncand;
+    const int chunks = (int)((per_frame + kThreads - 1) / kThreads);
+    const int items = batch * chunks;
+    for (int it = blockIdx.x; it < items; it += gridDim.x) {
+        const int b = it / chunks;
+        const int t = (it - b * chunks) * kThreads + threadIdx.x;
+        int n = in_num[b];
+        n = n > max_voxels ? max_voxels : n;
+        if ((it - b * chunks) * kThreads >= n * g.ncand) continue;   // uniform over the block
+        if (t >= n * g.ncand) continue;
+        const int i = g.cand_shift >= 0 ? (t >> g.cand_shift) : t / g.ncand;
+        const int e = t - i * g.ncand;
+        int cz, cy, cx, rest;
+        split_small(e, g.span_max[2], &rest, &cx);
+        split_small(rest, g.span_max[1], &cz, &cy);
+        const int4 c4 = __ldg(&in_coors[(size_t)b * max_voxels + i]);
+        const int c[3] = {c4.y, c4.z, c4.w};
+        const int cj[3] = {cz, cy, cx};
+        int o[3];
+        bool ok = true;
+        int k = 0;
+#pragma unroll
+        for (int j = 0; j < 3; ++j) {
+            const int lo = div_trunc(c[j] - (g.K[j] - 1) - 1 + g.S[j] + g.P[j], g.S[j]);
+            const int hi = div_trunc(c[j] + g.P[j], g.S[j]);
+            o[j] = hi - cj[j];
+            const int kj = c[j] - o[j] * g.S[j] + g.P[j];
+            ok = ok && cj[j] <= hi - lo && o[j] >= 0 && o[j] < g.out_shape[j] && kj >= 0 && kj < g.K[j] &&
+                 c[j] >= 0 && c[j] < g.in_shape[j];
+            k = k * g.K[j] + kj;
+        }
+        if (!ok) continue;
+        BitsIndex::Probe p;
+        out.probe(b, o[0], o[1], o[2], 1, true, &p);
+        const int id = out.finish(p, o[2]);
+        if (id < 0) continue;   // output dropped by the max_voxels cap
+        nbr[((size_t)b * g.kvol + k) * max_voxels + id] = i;
+        uint32_t* m = &tile_mask[(size_t)b * tiles_per_frame + (id >> 7)];
+        if (!((*reinterpret_cast<volatile uint32_t*>(m) >> k) & 1u)) atomicOr(m, 1u << k);
     }
 }
 
@@ -677,23 +698,18 @@ int launch_number_outputs(const BitGrid& out, int batch, int max_voxels, int32_t
 }
 
 int launch_map_rows(const int32_t* out_coors, const int32_t* out_num, int batch, int max_voxels, const ConvGeom& g,
-                    const InputIndex& in, int32_t* nbr, uint32_t* tile_mask, cudaStream_t stream) {
-    InputIndexDev d{};
-    d.kind = in.kind;
-    d.bits = BitsIndex{in.bits, max_voxels};
-    d.buckets = BucketIndex{in.buckets, g.in_shape[1], g.in_shape[2]};
-    d.table = in.table;
-    const int tiles = (max_voxels + 127) / 128;
-    const int4* oc = reinterpret_cast<const int4*>(out_coors);
-    if (in.kind == 0)
-        SESSD_LAUNCH_NAMED("map_rows_kernel<grid>", map_rows_kernel<0>, persistent_grid(8), kThreads, 0, stream, oc, out_num,
-                           batch, max_voxels, g, d, nbr, tile_mask, tiles);
-    else if (in.kind == 1)
-        SESSD_LAUNCH_NAMED("map_rows_kernel<buckets>", map_rows_kernel<1>, persistent_grid(8), kThreads, 0, stream, oc,
-                           out_num, batch, max_voxels, g, d, nbr, tile_mask, tiles);
-    else
-        SESSD_LAUNCH_NAMED("map_rows_kernel<table>", map_rows_kernel<2>, persistent_grid(8), kThreads, 0, stream, oc,
-                           out_num, batch, max_voxels, g, d, nbr, tile_mask, tiles);
+                    const BitGrid& in, int32_t* nbr, uint32_t* tile_mask, cudaStream_t stream) {
+    SESSD_LAUNCH(map_rows_kernel, persistent_grid(8), kThreads, 0, stream, reinterpret_cast<const int4*>(out_coors),
+                 out_num, batch, max_voxels, g, BitsIndex{in, max_voxels}, nbr, tile_mask, (max_voxels + 127) / 128);
+    return SESSD_OK;
+}
+
+int launch_scatter_rows(const int32_t* in_coors, const int32_t* in_num, const int32_t* out_num, int batch,
+                        int max_voxels, const ConvGeom& g, const BitGrid& out, int32_t* nbr, uint32_t* tile_mask,
+                        cudaStream_t stream) {
+    SESSD_LAUNCH(nbr_clear_kernel, persistent_grid(8), kThreads, 0, stream, nbr, out_num, batch, max_voxels, g.kvol);
+    SESSD_LAUNCH(scatter_rows_kernel, persistent_grid(8), kThreads, 0, stream, reinterpret_cast<const int4*>(in_coors),
+                 in_num, batch, max_voxels, g, BitsIndex{out, max_voxels}, nbr, tile_mask, (max_voxels + 127) / 128);
     return SESSD_OK;
 }
 
