@@ -240,6 +240,16 @@ __device__ __forceinline__ bool stage_active(uint32_t kmask, int g) {
     return ((kmask >> (g * KG)) & ((1u << KG) - 1u)) != 0u;
 }
 
+// One bit per stage (at bit position g * KG) that is set when the tile has a neighbour under any offset of the stage.
+template <int KG>
+__device__ __forceinline__ uint32_t stage_bits(uint32_t kmask) {
+    if (KG == 1) return kmask;
+    if (KG == 2) return (kmask | (kmask >> 1)) & 0x55555555u;
+    uint32_t v = kmask | (kmask >> 1);
+    v |= v >> 2;
+    return v & 0x11111111u;
+}
+
 // Bit t set when row tile t has a neighbour under the offsets of stage g. The masks are only ever indexed
 // with compile-time constants, so they stay in registers.
 template <int KG>
@@ -345,6 +355,7 @@ conv_umma_kernel(const __half* __restrict__ in, __half* __restrict__ out, const 
     tc_fence_after();
     const uint32_t tmem = ctl->tmem_base;
     volatile int* abort_flag = &ctl->abort_flag;
+    const bool leader = elect_one();   // one lane per warp, the same one for the whole kernel
 #ifdef SESSD_UMMA_TIMING
     const long long t_cta0 = clock64();
     unsigned long long tacc[8] = {};
@@ -371,11 +382,7 @@ conv_umma_kernel(const __half* __restrict__ in, __half* __restrict__ out, const 
     {
         const int per = (total_tiles + THREADS - 1) / THREADS;
         const int first = tid * per, last = first + per < total_tiles ? first + per : total_tiles;
-        auto tile_weight = [&](uint32_t mask) {
-            int items = 0;
-            for (int g = 0; g < nstages; ++g) items += stage_active<KG>(mask, g) ? 1 : 0;
-            return (uint32_t)(items + 2);
-        };
+        auto tile_weight = [&](uint32_t mask) { return (uint32_t)(__popc(stage_bits<KG>(mask)) + 2); };
         int f = 0, f_first = 0, f_tiles = batch > 0 ? (frame_rows(0) + TILE_M - 1) / TILE_M : 0;
         auto seek = [&](int tile) {   // frame of a tile of the sequence (tiles are visited in ascending order)
             while (f < batch && tile >= f_first + f_tiles) {
@@ -454,12 +461,11 @@ conv_umma_kernel(const __half* __restrict__ in, __half* __restrict__ out, const 
             m[t] = t < cnt ? __ldg(tile_mask + (size_t)b * tiles_per_frame + tile0 + t) : 0u;
             any |= m[t];
         }
-        int n_a = 0, n_b = 0;   // items and weight blocks this group consumes
-        for (int g = 0; g < nstages; ++g) {
-            const int act = __popc(active_tiles<KG>(m, g));
-            n_a += act;
-            n_b += act ? 1 : 0;
-        }
+        // items and weight blocks this group consumes
+        const uint32_t sb0 = stage_bits<KG>(m[0]), sb1 = stage_bits<KG>(m[1]), sb2 = stage_bits<KG>(m[2]),
+                       sb3 = stage_bits<KG>(m[3]);
+        const int n_a = __popc(sb0) + __popc(sb1) + __popc(sb2) + __popc(sb3);
+        const int n_b = __popc(sb0 | sb1 | sb2 | sb3);
         const uint32_t set = acc_it & 1u;           // accumulator set of this group (groups without work use none)
         const uint32_t set_phase = (acc_it >> 1) & 1u;
 
@@ -640,9 +646,28 @@ conv_umma_kernel(const __half* __restrict__ in, __half* __restrict__ out, const 
             // weight block and release it, also one with nothing to do for the stage: each of its waits and
             // arrivals must count for this use of the weight slot, not for an earlier one (a slot refilled while
             // an issuer has not yet tested its previous use would leave that issuer waiting on the wrong phase).
-            if (lane == 0 && any) {
+            // The whole warp walks the stages together: the schedule of the group is worked out once, lane g for
+            // stage g (which weight slot and phase, whether tile t takes part, which A slot its item sits in), and
+            // handed round with a shuffle, so that the serial part is only waits, the tensor-core instructions of
+            // one elected lane (always the same one: commits count the instructions of their own thread) and
+            // arrivals.
+            if (any) {
                 const int t = warp - EPI_WARPS;
-                uint32_t my_a = a_it, my_b = b_it;
+                uint32_t info = 0;
+                {
+                    const uint32_t bits = lane < nstages ? active_tiles<KG>(m, lane) : 0u;
+                    const int act = __popc(bits), blk = bits ? 1 : 0;
+                    int acts = act, blks = blk;   // inclusive scans over the stages
+#pragma unroll
+                    for (int d = 1; d < 32; d <<= 1) {
+                        const int va = __shfl_up_sync(0xFFFFFFFFu, acts, d), vb = __shfl_up_sync(0xFFFFFFFFu, blks, d);
+                        if (lane >= d) acts += va, blks += vb;
+                    }
+                    const uint32_t pos = a_it + (uint32_t)(acts - act) + (uint32_t)__popc(bits & ((1u << t) - 1u));
+                    const uint32_t my_b = b_it + (uint32_t)(blks - blk);
+                    info = (bits ? 1u : 0u) | (((bits >> t) & 1u) << 1) | ((my_b % B_STAGES) << 2) |
+                           (((my_b / B_STAGES) & 1u) << 3) | ((pos % NSLOT) << 4) | (pos << 8);
+                }
                 // the epilogue must have read this set's previous contents (two groups back)
                 const long long tm0 = TCLK();
                 bool ok = mbar_wait<false, true>(smem_u32(&ctl->acc_empty[set]), set_phase ^ 1u, abort_flag,
@@ -652,43 +677,42 @@ conv_umma_kernel(const __half* __restrict__ in, __half* __restrict__ out, const 
                 const uint32_t d_tmem = tmem + set * SET_COLS + t * COUT;
                 bool started = false;
                 for (int g = 0; g < nstages && ok; ++g) {
-                    const uint32_t bits = active_tiles<KG>(m, g);
-                    if (!bits) continue;
-                    const uint32_t sb = my_b % B_STAGES;
+                    const uint32_t inf = __shfl_sync(0xFFFFFFFFu, info, g);
+                    if (!(inf & 1u)) continue;
+                    const uint32_t sb = (inf >> 2) & 1u;
                     const long long tm1 = TCLK();
-                    ok = mbar_wait<false, true>(smem_u32(&ctl->b_full[sb]), (my_b / B_STAGES) & 1u, abort_flag,
-                                                5 | (int)(my_b << 4));
+                    ok = mbar_wait<false, true>(smem_u32(&ctl->b_full[sb]), (inf >> 3) & 1u, abort_flag,
+                                                5 | (int)((b_it + g) << 4));
                     TADD(1, TCLK() - tm1);
                     if (!ok) break;
-                    if ((bits >> t) & 1u) {
-                        const uint32_t pos = my_a + (uint32_t)__popc(bits & ((1u << t) - 1u));
-                        const uint32_t sa = pos % NSLOT;
+                    if (inf & 2u) {
+                        const uint32_t sa = (inf >> 4) & 15u;
                         const long long tm2 = TCLK();
                         ok = mbar_wait<false, true>(smem_u32(&ctl->a_full[t][sa]), (full_phase >> sa) & 1u, abort_flag,
-                                                    6 | (int)(pos << 4));
+                                                    6 | (int)((inf >> 8) << 4));
                         full_phase ^= 1u << sa;   // this issuer's next use of the slot is the next phase
                         if (!ok) break;
                         const long long tm3 = TCLK();
                         TADD(2, tm3 - tm2);
-                        fence_proxy_async();   // the gathered rows were written through the generic proxy
-                        tc_fence_after();
-                        const uint64_t adesc = umma_desc(smem_u32(sA + sa * A_BYTES));
-                        const uint64_t bdesc = umma_desc(smem_u32(sB + sb * B_BYTES));
+                        if (leader) {
+                            fence_proxy_async();   // the gathered rows were written through the generic proxy
+                            tc_fence_after();
+                            const uint64_t adesc = umma_desc(smem_u32(sA + sa * A_BYTES));
+                            const uint64_t bdesc = umma_desc(smem_u32(sB + sb * B_BYTES));
 #pragma unroll
-                        for (int kk = 0; kk < 4; ++kk)
-                            umma_f16(d_tmem, adesc + 2 * kk, bdesc + 2 * kk, IDESC, (started || kk > 0) ? 1u : 0u);
+                            for (int kk = 0; kk < 4; ++kk)
+                                umma_f16(d_tmem, adesc + 2 * kk, bdesc + 2 * kk, IDESC, (started || kk > 0) ? 1u : 0u);
+                            umma_commit(smem_u32(&ctl->a_empty[sa]));   // frees the A slot once these MMAs have read it
+                            umma_commit(smem_u32(&ctl->b_empty[sb]));   // and this issuer's hold on the weight block
+                        }
                         started = true;
-                        umma_commit(smem_u32(&ctl->a_empty[sa]));   // frees the A slot once these MMAs have read it
-                        umma_commit(smem_u32(&ctl->b_empty[sb]));   // and this issuer's hold on the weight block
                         TADD(3, TCLK() - tm3);
                         TADD(4, 1);
-                    } else {
+                    } else if (leader) {
                         mbar_arrive(smem_u32(&ctl->b_empty[sb]));   // nothing to read from this weight block
                     }
-                    my_a += (uint32_t)__popc(bits);
-                    ++my_b;
                 }
-                if (ok) {
+                if (ok && leader) {
                     if (started) umma_commit(smem_u32(&ctl->acc_full[set]));
                     else mbar_arrive(smem_u32(&ctl->acc_full[set]));
                 }
@@ -823,7 +847,7 @@ conv_umma_kernel(const __half* __restrict__ in, __half* __restrict__ out, const 
         // warp 4 waits on (bounded) before it frees the tensor memory, the weight streamer waits (bounded) for
         // its last bulk copies.
         if (warp >= FIRST_GATHER_WARP || warp == INDEX_WARP) asm volatile("cp.async.wait_all;" ::: "memory");
-        if (warp >= EPI_WARPS && warp < WEIGHT_WARP && lane == 0) umma_commit(smem_u32(&ctl->mma_drain));
+        if (warp >= EPI_WARPS && warp < WEIGHT_WARP && leader) umma_commit(smem_u32(&ctl->mma_drain));
         if (warp == INDEX_WARP && idx_bulk) {
             for (int j = lane; j < NIDX; j += 32) {
                 const uint32_t uses = ctl->idx_uses[j];
