@@ -16,20 +16,23 @@
 //   warps 0-3    epilogue (warp w reads tensor-memory lanes 32w .. 32w+31). The accumulators are double
 //                buffered (2 sets x 4 tiles x Cout columns), so the epilogue of one group runs while the
 //                other roles are already working on the next group.
-//   warps 4-7    MMA issuers, one thread each; issuer t owns tile t of every group. Issuing costs the
-//                thread on the order of a hundred cycles per tcgen05.mma / commit, so four threads share it.
+//   warps 4-7    MMA issuers; issuer t owns tile t of every group. The warp works out the group's schedule
+//                once (lane g for stage g) and walks it together; one elected lane issues the tcgen05.mma and
+//                commit instructions (each costs its thread on the order of a hundred cycles, so four share).
 //   warp  8      streams the weight blocks (cp.async.bulk) into a two-slot ring.
-//   warp  9      prefetches the neighbour indices of upcoming (tile, stage) items into shared memory.
+//   warp  9      prefetches the neighbour indices of upcoming (tile, stage) items into a ring of index blocks
+//                with bulk copies, sixteen items side by side (one lane each), two to three slot cycles ahead.
 //   warps 10..   gather. The A ring has one 16 KB slot per gather warp: item q (the q-th (tile, stage) pair
 //                of the CTA's life) lives in slot q % NSLOT and is filled by warp q % NSLOT alone with
 //                sixteen-byte cp.async copies that publish the slot themselves (mbarrier arrival of the
-//                copies). With 11-12 slots in flight the latency chain of one slot (issue, landing, MMA,
+//                copies). With 10-11 slots in flight the latency chain of one slot (issue, landing, MMA,
 //                commit) is covered and no barrier is shared between gather warps.
 // Every barrier has one waiting role that sees each of its phases in order (a parity wait is only safe
-// then): a_full exists per (issuer, slot), index blocks are tied to the A slot of the same gather warp.
-// A CTA walks an equal share of all occupied row tiles (row counts are read on the device). Every wait is
-// bounded by a clock limit, after which the CTA raises SESSD_STATUS_TIMEOUT (and reports which wait in the
-// status block), stops issuing work, waits for its own copies and MMAs, frees its tensor memory and returns.
+// then): a_full exists per (issuer, slot); index block j is always read by gather warp j % NSLOT.
+// A CTA walks a contiguous range of the occupied row tiles, cut so that every CTA gets the same number of
+// (tile, stage) items (row counts and masks are read on the device). Every wait is bounded by a clock limit,
+// after which the CTA raises SESSD_STATUS_TIMEOUT (and reports which wait in the status block), stops issuing
+// work, waits for its own copies and MMAs, frees its tensor memory and returns.
 #include <atomic>
 #include <cstdlib>
 #include <string>
@@ -273,13 +276,6 @@ __device__ __forceinline__ bool next_item(const uint32_t (&m)[TILES], int nstage
     return true;
 }
 
-#ifdef SESSD_UMMA_TIMING
-#define TCLK() clock64()
-#define TADD(i, v) do { if (blockIdx.x == 0) tacc[i] += (unsigned long long)(v); } while (0)
-#else
-#define TCLK() 0LL
-#define TADD(i, v) do { } while (0)
-#endif
 
 template <int CIN, int COUT>
 __global__ void __launch_bounds__(Ring<CIN>::THREADS, 1)
@@ -356,10 +352,6 @@ conv_umma_kernel(const __half* __restrict__ in, __half* __restrict__ out, const 
     const uint32_t tmem = ctl->tmem_base;
     volatile int* abort_flag = &ctl->abort_flag;
     const bool leader = elect_one();   // one lane per warp, the same one for the whole kernel
-#ifdef SESSD_UMMA_TIMING
-    const long long t_cta0 = clock64();
-    unsigned long long tacc[8] = {};
-#endif
 
     uint32_t a_it = 0, b_it = 0, acc_it = 0;  // items, weight blocks and accumulator sets used so far; every role advances them identically
     uint32_t full_phase = 0;                  // MMA issuers: bit s = parity of the next phase of their a_full[t][s]
@@ -446,7 +438,6 @@ conv_umma_kernel(const __half* __restrict__ in, __half* __restrict__ out, const 
             n = frame_rows(b);
             frame_tiles = (n + TILE_M - 1) / TILE_M;
         }
-        const long long tg0 = TCLK();
         const int tile0 = cur - frame_first;
         int cnt = range_hi - cur;
         cnt = cnt > TILES ? TILES : cnt;
@@ -469,7 +460,6 @@ conv_umma_kernel(const __half* __restrict__ in, __half* __restrict__ out, const 
         const uint32_t set = acc_it & 1u;           // accumulator set of this group (groups without work use none)
         const uint32_t set_phase = (acc_it >> 1) & 1u;
 
-        TADD(6, TCLK() - tg0);
         if (warp >= FIRST_GATHER_WARP) {
             // ---------------- gather producers ----------------
             // Gather warp s fills slot s with every NSLOT-th item and issues all of its copies: while one warp
@@ -511,9 +501,7 @@ conv_umma_kernel(const __half* __restrict__ in, __half* __restrict__ out, const 
                 const int code = list[e];
                 const int g = code >> 2, t = code & 3;
                 // row indices of this item, fetched ahead of time by the index warp
-                const long long tq0 = TCLK();
                 if (!mbar_wait(smem_u32(&ctl->i_full[ji]), iuse, abort_flag, 1 | (int)(q << 4))) break;
-                const long long tq1 = TCLK();
 
                 // all 32 indices first (the copies below are compiler barriers, a load could not move above them)
                 int vv[32];
@@ -525,9 +513,7 @@ conv_umma_kernel(const __half* __restrict__ in, __half* __restrict__ out, const 
                                  : "r"(idx_base + 16 * w4));
                     vv[4 * w4] = v.x, vv[4 * w4 + 1] = v.y, vv[4 * w4 + 2] = v.z, vv[4 * w4 + 3] = v.w;
                 }
-                const long long tq2 = TCLK();
                 if (!mbar_wait(smem_u32(&ctl->a_empty[s]), use ^ 1u, abort_flag, 2 | (int)(q << 4))) break;
-                const long long tq3 = TCLK();
                 const bool k_ok = g * KG + koff < kvol;
                 const int rows_left = n - (row0 + t * TILE_M + jrow);   // rows of this lane group inside the frame
                 // Every instruction of this loop is on the critical path of the item, so the common case - all
@@ -556,22 +542,15 @@ conv_umma_kernel(const __half* __restrict__ in, __half* __restrict__ out, const 
                 mbar_arrive(smem_u32(&ctl->i_empty[ji]));
                 // publishes the slot, when the copies land, to the issuer that owns row tile t
                 cp_async_arrive_noinc(smem_u32(&ctl->a_full[t][s]));
-                TADD(0, tq1 - tq0);
-                TADD(1, tq3 - tq2);
-                TADD(2, TCLK() - tq3);
-                TADD(3, 1);
-                TADD(4, tq2 - tq1);
             }
         } else if (warp < EPI_WARPS) {
             // ---------------- epilogue ----------------
             bool got = true;
-            const long long te0 = TCLK();
             if (any) {
                 got = mbar_wait<true>(smem_u32(&ctl->acc_full[set]), set_phase, abort_flag, 3 | (int)(acc_it << 4));
                 got = __all_sync(0xFFFFFFFFu, got);
                 if (got) tc_fence_after();
             }
-            const long long te1 = TCLK();
             // Column blocks of CB channels keep the register footprint small.
             constexpr int CB = COUT < 32 ? COUT : 32;
 #pragma unroll 1
@@ -637,9 +616,6 @@ conv_umma_kernel(const __half* __restrict__ in, __half* __restrict__ out, const 
                 tc_fence_before();
                 mbar_arrive(smem_u32(&ctl->acc_empty[set]));   // the set may be overwritten
             }
-            TADD(0, te1 - te0);
-            TADD(1, TCLK() - te1);
-            TADD(2, 1);
         } else if (warp < WEIGHT_WARP) {
             // ---------------- MMA issuers ----------------
             // Issuer t owns tile t: its accumulator, the items (t, g) and their slots. All four wait for every
@@ -669,10 +645,8 @@ conv_umma_kernel(const __half* __restrict__ in, __half* __restrict__ out, const 
                            (((my_b / B_STAGES) & 1u) << 3) | ((pos % NSLOT) << 4) | (pos << 8);
                 }
                 // the epilogue must have read this set's previous contents (two groups back)
-                const long long tm0 = TCLK();
                 bool ok = mbar_wait<false, true>(smem_u32(&ctl->acc_empty[set]), set_phase ^ 1u, abort_flag,
                                                  4 | (int)(acc_it << 4));
-                TADD(0, TCLK() - tm0);
                 if (ok) tc_fence_after();
                 const uint32_t d_tmem = tmem + set * SET_COLS + t * COUT;
                 bool started = false;
@@ -680,20 +654,15 @@ conv_umma_kernel(const __half* __restrict__ in, __half* __restrict__ out, const 
                     const uint32_t inf = __shfl_sync(0xFFFFFFFFu, info, g);
                     if (!(inf & 1u)) continue;
                     const uint32_t sb = (inf >> 2) & 1u;
-                    const long long tm1 = TCLK();
                     ok = mbar_wait<false, true>(smem_u32(&ctl->b_full[sb]), (inf >> 3) & 1u, abort_flag,
                                                 5 | (int)((b_it + g) << 4));
-                    TADD(1, TCLK() - tm1);
                     if (!ok) break;
                     if (inf & 2u) {
                         const uint32_t sa = (inf >> 4) & 15u;
-                        const long long tm2 = TCLK();
                         ok = mbar_wait<false, true>(smem_u32(&ctl->a_full[t][sa]), (full_phase >> sa) & 1u, abort_flag,
                                                     6 | (int)((inf >> 8) << 4));
                         full_phase ^= 1u << sa;   // this issuer's next use of the slot is the next phase
                         if (!ok) break;
-                        const long long tm3 = TCLK();
-                        TADD(2, tm3 - tm2);
                         if (leader) {
                             fence_proxy_async();   // the gathered rows were written through the generic proxy
                             tc_fence_after();
@@ -706,8 +675,6 @@ conv_umma_kernel(const __half* __restrict__ in, __half* __restrict__ out, const 
                             umma_commit(smem_u32(&ctl->b_empty[sb]));   // and this issuer's hold on the weight block
                         }
                         started = true;
-                        TADD(3, TCLK() - tm3);
-                        TADD(4, 1);
                     } else if (leader) {
                         mbar_arrive(smem_u32(&ctl->b_empty[sb]));   // nothing to read from this weight block
                     }
@@ -826,21 +793,6 @@ conv_umma_kernel(const __half* __restrict__ in, __half* __restrict__ out, const 
 
     tc_fence_before();
     __syncthreads();
-#ifdef SESSD_UMMA_TIMING
-    if (tid == 0) {   // spread of the CTA lifetimes: max and sum over the grid
-        unsigned long long* dbg = reinterpret_cast<unsigned long long*>(status) + 96;
-        const unsigned long long life = (unsigned long long)(clock64() - t_cta0);
-        atomicMax(dbg + 30, life);
-        atomicAdd(dbg + 31, life);
-    }
-    if (blockIdx.x == 0 && lane == 0 && (warp == 0 || warp == EPI_WARPS || warp == FIRST_GATHER_WARP || warp == INDEX_WARP)) {
-        unsigned long long* dbg = reinterpret_cast<unsigned long long*>(status) + 96 +
-                                  (warp == 0 ? 0 : (warp == EPI_WARPS ? 8 : (warp == INDEX_WARP ? 24 : 16)));
-        tacc[7] = (unsigned long long)(clock64() - t_cta0);
-#pragma unroll
-        for (int i = 0; i < (warp == INDEX_WARP ? 6 : 8); ++i) dbg[i] = tacc[i];
-    }
-#endif
     if (*abort_flag) {
         // An aborting CTA must not return while its own copies are still writing shared memory or its MMAs tensor
         // memory: the gather and index warps wait for their cp.async copies, the issuers commit to a barrier that
