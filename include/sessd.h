@@ -108,10 +108,17 @@ void* sessd_voxelize_num_points(const sessd_voxel_params* p, int batch, int max_
  *     that first call outside any stream capture;
  *   - all calls on one device share the array: it keeps the previous call's contents (each call resets
  *     what it needs), and two calls that overlap on the GPU (different streams) race. Serialise them;
- *   - the device status word lives inside the array and is not exposed: detect overflow by
- *     voxel_num[b] == p->max_voxels. */
+ *   - the device status word lives inside the array; sessd_voxelize_static_status() reads it (a full frame and a
+ *     frame that lost voxels both end with voxel_num[b] == p->max_voxels, only the status bit tells them apart);
+ *   - the looked-up address is kept per device ordinal for the life of the process: after cudaDeviceReset (or
+ *     any other destruction of the device's primary context) the library must not be used again without being
+ *     reloaded. */
 int sessd_voxelize_enqueue_static(const sessd_voxel_params* p, int batch, int max_points, int out_dtype,
                                   const void* const* inputs, void* const* outputs, void* stream);
+/* Status word left by the last sessd_voxelize_enqueue_static call on the current device: synchronises `stream`
+ * and returns the word (>= 0, SESSD_STATUS_* bits) or a negative sessd_error (SESSD_ERR_PARAM before the first
+ * call on this device). Allocates nothing. Like the entry point it serves, it has no counterpart in the reference. */
+int sessd_voxelize_static_status(void* stream);
 
 /* ------------------------------------------------------------------------------------------
  * Sparse convolutions.  Replace SubmConv3dLayerPlugin (submConv3dlayer.h:19-121) and
@@ -252,7 +259,10 @@ typedef struct sessd_pipeline sessd_pipeline;
 int sessd_pipeline_create(const sessd_backbone* bb, int batch, int max_points, int nstreams, sessd_pipeline** out);
 void sessd_pipeline_destroy(sessd_pipeline* pl);
 /* host_points f32 [nframes][max_points][4], host_sizes i32 [nframes];
- * host_voxel_num i32 [nframes], host_status i32 [nframes] (status of the group the frame ran in). */
+ * host_voxel_num i32 [nframes], host_status i32 [nframes]: the status word of the stream slot the frame's group ran
+ * on, as it stood after that group. Within one run a slot's word is not cleared between groups, so it also holds
+ * the conditions of the slot's earlier groups, and the words of the last group of every slot together cover the
+ * whole run (a run clears them when it starts). */
 int sessd_pipeline_run_host(sessd_pipeline* pl, const float* host_points, const int32_t* host_sizes, int nframes,
                             int32_t* host_voxel_num, int32_t* host_status, float* elapsed_ms);
 /* Same work with the points already on the device: points f32 [nframes][max_points][4], sizes i32 [nframes].
@@ -355,11 +365,12 @@ int sessd_read_status(const void* workspace, void* stream);
 const char* sessd_last_cuda_error(void);
 /* Library version string. */
 const char* sessd_version(void);
-/* Test hook for the time-out path, process-wide, off by default: while on, the tensor-core convolution kernel's
- * weight streamer stays silent, so the kernel's bounded waits run out (about 0.1 s), every block leaves through
- * its abort path, the call returns SESSD_OK and the status word carries SESSD_STATUS_TIMEOUT with the code of
- * the wait in the second status word. Nothing faults or hangs; the next call with the hook off is normal. */
-int sessd_debug_withhold_weights(int on);
+/* Test hook for the time-out path, per weight object, off by default: while on, the tensor-core convolution
+ * kernel launched with these weights keeps its weight streamer silent, so the kernel's bounded waits run out (about
+ * 0.1 s), every block leaves through its abort path, the call returns SESSD_OK and the status word carries
+ * SESSD_STATUS_TIMEOUT with the code of the wait in the second status word. Nothing faults or hangs; other weight
+ * objects and the next call with the hook off are not affected. */
+int sessd_conv_weights_debug_withhold(sessd_conv_weights* w, int on);
 
 /* ------------------------------------------------------------------------------------------
  * On-disk formats either side of the path (host code, no GPU needed).

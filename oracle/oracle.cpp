@@ -608,13 +608,18 @@ float bev_iou(const float* a9, const BevBox& a, const float* b9, const BevBox& b
 }  // namespace
 
 // boxes: [n][9]. Boxes are taken in descending score (column 8); the reference's std::sort leaves the order
-// of equal scores open, here the lower input row goes first. A box is kept unless an earlier kept box
+// of equal scores open, here the lower input row goes first. A NaN score (undefined behaviour for the reference's
+// comparator) ranks as minus infinity. A box is kept unless an earlier kept box
 // overlaps it with IoU >= thresh. kept [n][9] receives the kept boxes in that order (rows after the count
 // are zero); returns the count. order (optional, [n]) receives the input row of every kept box.
 int oracle_rotated_nms(const float* boxes, int n, float thresh, float* kept, int32_t* order) {
     std::vector<int> idx(n);
     for (int i = 0; i < n; ++i) idx[i] = i;
-    std::stable_sort(idx.begin(), idx.end(), [&](int a, int b) { return boxes[a * 9 + 8] > boxes[b * 9 + 8]; });
+    auto rank_score = [&](int i) {
+        const float s = boxes[i * 9 + 8];
+        return s != s ? -INFINITY : s;
+    };
+    std::stable_sort(idx.begin(), idx.end(), [&](int a, int b) { return rank_score(a) > rank_score(b); });
     std::vector<BevBox> bev(n);
     for (int i = 0; i < n; ++i) bev[i] = bev_box(boxes + (size_t)idx[i] * 9);
     std::vector<char> dead(n, 0);

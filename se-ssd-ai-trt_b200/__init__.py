@@ -21,7 +21,7 @@ STATUS_BOX_OVERFLOW = 32
 
 EXPORTS = (
     "sessd_voxel_configure", "sessd_voxelize_workspace_bytes", "sessd_voxelize_enqueue", "sessd_voxelize_num_points",
-    "sessd_voxelize_enqueue_static",
+    "sessd_voxelize_enqueue_static", "sessd_voxelize_static_status",
     "sessd_conv_weights_create", "sessd_conv_weights_destroy", "sessd_conv_workspace_bytes",
     "sessd_subm_conv_enqueue", "sessd_sparse_conv_enqueue", "sessd_conv_rulebook_export",
     "sessd_sparse2dense_enqueue", "sessd_sparse2dense_padded_enqueue", "sessd_zero_pad2d_enqueue",
@@ -35,7 +35,7 @@ EXPORTS = (
     "sessd_anchor_decode_enqueue", "sessd_filter_boxes_workspace_bytes", "sessd_filter_boxes_enqueue",
     "sessd_decode_filter_enqueue", "sessd_rotated_nms_workspace_bytes", "sessd_rotated_nms_enqueue",
     "sessd_wts_load", "sessd_wts_destroy", "sessd_wts_count", "sessd_wts_entry", "sessd_wts_find", "sessd_wts_save",
-    "sessd_fold_batchnorm", "sessd_backbone_create_from_wts", "sessd_points_load", "sessd_debug_withhold_weights",
+    "sessd_fold_batchnorm", "sessd_backbone_create_from_wts", "sessd_points_load", "sessd_conv_weights_debug_withhold",
 )
 
 

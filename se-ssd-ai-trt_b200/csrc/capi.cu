@@ -122,8 +122,7 @@ void conv_workspace_layout(Bump& bump, const sessd_conv_params* p, const ConvGeo
 }
 
 bool conv_params_ok(const sessd_conv_params* p, int batch) {
-    // table slots travel in 24 bits beside the kernel offset (strided rulebook entries)
-    if (p->in_channel < 1 || p->out_channel < 1 || p->max_voxels < 1 || p->max_voxels > (1 << 22)) return false;
+    if (p->in_channel < 1 || p->out_channel < 1 || p->max_voxels < 1) return false;
     if (batch < 1 || batch > kMaxBatch) return false;
     if ((uint64_t)batch * p->max_voxels * 27ull > 0x7FFFFFFFull) return false;
     return true;
@@ -131,11 +130,8 @@ bool conv_params_ok(const sessd_conv_params* p, int batch) {
 
 size_t esize(int dtype) { return dtype == SESSD_F32 ? 4 : 2; }
 
-std::atomic<int> g_withhold_weights{0};   // sessd_debug_withhold_weights
-
 int choose_conv(const ConvLaunch& c_in, cudaStream_t stream) {
-    ConvLaunch c = c_in;
-    c.debug_withhold_weights = g_withhold_weights.load(std::memory_order_relaxed);
+    const ConvLaunch& c = c_in;
     if (c.dtype == SESSD_F16 && conv_umma_supported(c.cin, c.cout) && c.umma_weights) return launch_conv_umma(c, stream);
     return launch_conv_simt(c, stream);
 }
@@ -255,8 +251,9 @@ extern "C" {
 
 const char* sessd_version(void) { return "sessd-b200 0.1 (sm_100a)"; }
 
-int sessd_debug_withhold_weights(int on) {
-    g_withhold_weights.store(on ? 1 : 0, std::memory_order_relaxed);
+int sessd_conv_weights_debug_withhold(sessd_conv_weights* w, int on) {
+    if (!w) return SESSD_ERR_NULL;
+    w->impl.debug_withhold = on ? 1 : 0;
     return SESSD_OK;
 }
 const char* sessd_last_cuda_error(void) { return t_last_error.c_str(); }
@@ -497,6 +494,7 @@ static int conv_enqueue_common(const sessd_conv_params* p, const sessd_conv_weig
     c.cout = p->out_channel;
     c.dtype = w->impl.dtype;
     c.status = ws.status;
+    c.debug_withhold_weights = w->impl.debug_withhold;
     rc = choose_conv(c, stream);
     if (rc) return rc;
     // Rows past the active count are zero in the reference (outputs are memset, submConv3dlayer.cu:594).
@@ -667,7 +665,7 @@ size_t sessd_backbone_workspace_bytes(const sessd_backbone* bb, int batch, int m
 
 static int backbone_enqueue_impl(const sessd_backbone* bb, int batch, int max_points, const void* points,
                                 const void* points_size, void* dense, void* workspace, size_t workspace_bytes,
-                                void* stream_, bool count_pairs) {
+                                void* stream_, bool count_pairs, bool keep_status = false) {
     if (!bb || !points || !points_size || !workspace) return SESSD_ERR_NULL;
     if (bb->has_s2d && !dense) return SESSD_ERR_NULL;
     if (!voxel_params_ok(&bb->vp, batch, max_points)) return SESSD_ERR_PARAM;
@@ -679,7 +677,9 @@ static int backbone_enqueue_impl(const sessd_backbone* bb, int batch, int max_po
     if (bump.total() > workspace_bytes) return SESSD_ERR_WORKSPACE;
     if (!workspace_aligned(workspace)) return SESSD_ERR_PARAM;
     const int maxV = bb->max_voxels;
-    SESSD_CUDA(cudaMemsetAsync(w.status, 0, kStatusInts * sizeof(int32_t), stream));
+    // keep_status (pipelines): word 0 is left alone, so that it collects the conditions of every group of a run
+    SESSD_CUDA(cudaMemsetAsync(w.status + (keep_status ? 1 : 0), 0, (kStatusInts - (keep_status ? 1 : 0)) * sizeof(int32_t),
+                               stream));
     int rc = launch_fill_ones(w.ones_base, w.ones_bytes, stream);
     if (rc) return rc;
     rc = launch_fill_zero(w.zero_base, w.zero_bytes, stream);
@@ -761,6 +761,7 @@ static int backbone_enqueue_impl(const sessd_backbone* bb, int batch, int max_po
         c.cout = L.p.out_channel;
         c.dtype = bb->dtype;
         c.status = w.status;
+        c.debug_withhold_weights = L.w->impl.debug_withhold;
         if (bb->has_s2d && i + 1 == bb->layers.size()) {
             // The padded plane is (top + H + bottom) x (left + W + right); starting the scatter (top, left)
             // into it folds the reference's ZeroPad2dPlugin (zeroPad2d.cu:192-198) into this epilogue.
@@ -926,6 +927,8 @@ static int pipeline_run(sessd_pipeline* pl, const void* points, const int32_t* s
     const int last_layer = (int)bb->layers.size() - 1;
     SESSD_CUDA(cudaEventRecord(pl->start, pl->streams[0]));
     for (int s = 1; s < pl->nstreams; ++s) SESSD_CUDA(cudaStreamWaitEvent(pl->streams[s], pl->start, 0));
+    // a slot's status word collects the conditions of all its groups of this run
+    for (int s = 0; s < pl->nstreams; ++s) SESSD_CUDA(cudaMemsetAsync(pl->ws[s], 0, 4, pl->streams[s]));
     int group = 0;
     for (int f0 = 0; f0 < nframes; f0 += pl->batch, ++group) {
         const int s = group % pl->nstreams;
@@ -956,8 +959,8 @@ static int pipeline_run(sessd_pipeline* pl, const void* points, const int32_t* s
                 cudaGraph_t graph = nullptr;
                 const uint64_t launches_before = g_launches.load(std::memory_order_relaxed);
                 SESSD_CUDA(cudaStreamBeginCapture(st, cudaStreamCaptureModeThreadLocal));
-                rc = sessd_backbone_enqueue(bb, nb, pl->max_points, pl->pts[s], pl->sizes[s], pl->dense[s], pl->ws[s],
-                                            pl->ws_bytes, st);
+                rc = backbone_enqueue_impl(bb, nb, pl->max_points, pl->pts[s], pl->sizes[s], pl->dense[s], pl->ws[s],
+                                           pl->ws_bytes, st, false, true);
                 const cudaError_t e_end = cudaStreamEndCapture(st, &graph);
                 // the captured launches were recorded, not run: they count when the graph is launched
                 pl->graph_kernels[s] = g_launches.load(std::memory_order_relaxed) - launches_before;
@@ -980,7 +983,8 @@ static int pipeline_run(sessd_pipeline* pl, const void* points, const int32_t* s
             SESSD_CUDA(cudaGraphLaunch(pl->graphs[s], st));
             g_launches.fetch_add(pl->graph_kernels[s], std::memory_order_relaxed);
         } else {
-            rc = sessd_backbone_enqueue(bb, nb, pl->max_points, dpts, dsizes, pl->dense[s], pl->ws[s], pl->ws_bytes, st);
+            rc = backbone_enqueue_impl(bb, nb, pl->max_points, dpts, dsizes, pl->dense[s], pl->ws[s], pl->ws_bytes, st, false,
+                                       true);
             if (rc) return rc;
             if (nb == pl->batch) pl->warmed[s] = 1;
         }

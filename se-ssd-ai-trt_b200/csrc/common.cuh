@@ -322,6 +322,7 @@ struct sessd_conv_weights_impl {
     float* scale;   // device or null
     float* shift;   // device or null
     int relu, dtype, kvol, cin, cout;
+    int debug_withhold;   // tests of the time-out path: the tensor-core kernel's weight streamer stays silent
 };
 
 }  // namespace sessd

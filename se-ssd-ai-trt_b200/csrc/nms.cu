@@ -140,6 +140,10 @@ __device__ __forceinline__ int frame_count(const NmsArgs& a, int b) {
     return v > (uint32_t)a.max_box ? a.max_box : (int)v;
 }
 
+// Scores are ranked as a total order: a NaN score (a non-finite head output can produce one) counts as minus
+// infinity, so that every box gets a rank of its own and every rank is written.
+__device__ __forceinline__ float rank_score(float s) { return s != s ? -INFINITY : s; }
+
 // Kernel 1: rank by (score descending, row ascending) by counting, then the geometry of every ranked box.
 __global__ void __launch_bounds__(kThreads)
 nms_rank_kernel(NmsArgs a) {
@@ -147,10 +151,10 @@ nms_rank_kernel(NmsArgs a) {
         const int n = frame_count(a, b);
         const float* bx = a.boxes + (size_t)b * a.max_box * 9;
         for (int i = threadIdx.x; i < n; i += kThreads) {
-            const float si = bx[i * 9 + 8];
+            const float si = rank_score(bx[i * 9 + 8]);
             int rank = 0;
             for (int j = 0; j < n; ++j) {
-                const float sj = bx[j * 9 + 8];
+                const float sj = rank_score(bx[j * 9 + 8]);
                 rank += (sj > si || (sj == si && j < i)) ? 1 : 0;
             }
             a.order[(size_t)b * a.max_box + rank] = i;
@@ -305,6 +309,7 @@ nms_reduce_kernel(NmsArgs a, int smem_words) {
             if ((kw >> r) & 1ull) {
                 const int pos = s_base[c] + __popcll(kw & ((1ull << r) - 1ull));
                 const int src = a.order[(size_t)b * a.max_box + i];
+                if ((unsigned)src >= (unsigned)n) continue;   // cannot happen with a total order; never read out of bounds
 #pragma unroll
                 for (int e = 0; e < 9; ++e) out[(size_t)pos * 9 + e] = bx[(size_t)src * 9 + e];
             }

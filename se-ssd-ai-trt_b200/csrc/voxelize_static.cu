@@ -55,3 +55,19 @@ extern "C" int sessd_voxelize_enqueue_static(const sessd_voxel_params* p, int ba
     return sessd_voxelize_enqueue(p, batch, max_points, out_dtype, inputs, outputs, scratch, kStaticScratchBytes,
                                   stream);
 }
+
+// Status word of the last sessd_voxelize_enqueue_static call on the current device (the word sits at the start of
+// the built-in array): synchronises `stream`, copies the word to the host and returns it (>= 0), or a negative
+// sessd_error (SESSD_ERR_PARAM when no call has been made on this device yet). Allocates nothing.
+extern "C" int sessd_voxelize_static_status(void* stream) {
+    int dev = 0;
+    SESSD_CUDA(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64) return SESSD_ERR_PARAM;
+    void* scratch = nullptr;
+    {
+        std::lock_guard<std::mutex> lock(g_setup_mutex);
+        scratch = g_scratch_addr[dev];
+    }
+    if (!scratch) return SESSD_ERR_PARAM;
+    return sessd_read_status(scratch, stream);
+}

@@ -11,8 +11,9 @@ pytestmark = pytest.mark.gpu
 GOLDEN = os.path.join(os.path.dirname(__file__), "golden")
 
 
-def _oracle_layer(oracle, case, l, W, sc, sh, c, n, f, fp16):
-    """One conv layer + folded BatchNorm + ReLU on the oracle: (coors, n, features) -> the same for the output."""
+def _oracle_layer(oracle, case, l, W, sc, sh, c, n, f, fp16, pair_log=None):
+    """One conv layer + folded BatchNorm + ReLU on the oracle: (coors, n, features) -> the same for the output.
+    pair_log (a list) receives the layer's number of rulebook pairs."""
     maxV = case["max_voxels"]
     if l.subm:
         pairs, pnum, st = oracle.subm_rulebook(c, n, l.out_shape, maxV)
@@ -21,11 +22,13 @@ def _oracle_layer(oracle, case, l, W, sc, sh, c, n, f, fp16):
         oc, on, pairs, pnum, st = oracle.spconv_rulebook(c, n, l.ksize, l.stride, l.padding, l.out_shape, maxV)
         oc = oc[:on].copy()
     assert st == 0
+    if pair_log is not None:
+        pair_log.append(int(pnum.astype(np.int64).sum()))
     y = oracle.conv_apply(f, pairs, pnum, W, on, half_inputs=fp16)
     return oc, on, oracle.scale_shift_relu(y, sc, sh, True, half_out=fp16)
 
 
-def _oracle_layers(oracle, case, fp16):
+def _oracle_layers(oracle, case, fp16, pair_log=None):
     """Runs the oracle layer by layer, returning (coors, n, features) after every layer."""
     vox, coors, npv, n, st = oracle.voxelize(case["points"], case["range"], case["voxel"], case["max_voxels"])
     feat = vox[:n]
@@ -34,7 +37,7 @@ def _oracle_layers(oracle, case, fp16):
     outs = [(coors[:n].copy(), n, feat)]
     for l, W, sc, sh in zip(case["layers"], case["weights"], case["scale"], case["shift"]):
         c, n, f = outs[-1]
-        outs.append(_oracle_layer(oracle, case, l, W, sc, sh, c, n, f, fp16))
+        outs.append(_oracle_layer(oracle, case, l, W, sc, sh, c, n, f, fp16, pair_log))
     return outs
 
 
@@ -161,6 +164,36 @@ def test_full_size_backbone_fp16_20k_points(gpu, oracle):
     c, n, f = want[-1]
     gf, gc, gn = views[-1]
     np.testing.assert_array_equal(dense, oracle.sparse2dense(gf[0, :n], gc[0, :n], n, 64, 2, 200, 176))
+
+
+def test_sweep_frame_every_layer_against_the_oracle(gpu, oracle):
+    """The configuration the throughput figure is quoted on: one 120,000-point sweep frame, max_voxels 200,000,
+    fp16, through sessd_backbone_enqueue. Row counts, coordinate sets and per-layer rulebook pair counts are exact;
+    every layer's features are within 1e-2 (relative) of the oracle applied to the same input; the BEV map is the
+    scatter of the last layer."""
+    import torch
+
+    S = gpu.synth
+    w, sc, sh = gpu.random_weights()
+    case = dict(points=S.sweep_frame(0), range=S.POINT_RANGE, voxel=S.VOXEL_SIZE, max_voxels=200000,
+                layers=gpu.schedule.LAYERS, weights=w, scale=sc, shift=sh, bev=(64, 2, 200, 176))
+    want_pairs = []
+    want = _oracle_layers(oracle, case, fp16=True, pair_log=want_pairs)
+    dense, views = _gpu_run(gpu, case, 1)
+    _check_fp16_layers(oracle, case, want, views)
+    c, n, f = want[-1]
+    gf, gc, gn = views[-1]
+    np.testing.assert_array_equal(dense, oracle.sparse2dense(gf[0, :n], gc[0, :n], n, 64, 2, 200, 176))
+    want_dense = oracle.sparse2dense(f, c, n, 64, 2, 200, 176)
+    assert _max_norm_err(dense, want_dense) <= 2e-2
+    # the P of the flop count 2 * P * Cin * Cout, layer by layer (indice_num of the reference, submConv3dlayer.cu:413)
+    bb = gpu.Backbone(200000, w, sc, sh, dtype=1)
+    pts = torch.from_numpy(case["points"][None]).cuda()
+    sizes = torch.tensor([len(case["points"])], dtype=torch.int32, device="cuda")
+    d, ws = bb.run(pts, sizes)
+    got_pairs = gpu.pair_counts(bb, pts, sizes, ws, d)
+    bb.close()
+    assert got_pairs == want_pairs
 
 
 def test_round_trip_dense_to_sparse_at_sweep_size(gpu):

@@ -268,11 +268,11 @@ def test_bounded_waits_run_out_report_and_leave_the_context_usable(gpu):
     good = gpu.subm_conv(tf, tc, tn, p, w)
     assert good["status"] == 0
     want = good["features"].clone()
-    gpu.lib().sessd_debug_withhold_weights(1)
+    assert gpu.lib().sessd_conv_weights_debug_withhold(w.handle, 1) == 0
     try:
         r = gpu.subm_conv(tf, tc, tn, p, w, keep_workspace=True)
     finally:
-        gpu.lib().sessd_debug_withhold_weights(0)
+        gpu.lib().sessd_conv_weights_debug_withhold(w.handle, 0)
     assert r["status"] & gpu.STATUS_TIMEOUT
     where = int(r["workspace"][4:8].view(torch.int32)[0])
     assert where & 15 == 5                    # an MMA issuer waiting for a weight block

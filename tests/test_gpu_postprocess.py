@@ -161,6 +161,33 @@ def test_rotated_nms_matches_oracle(gpu, oracle, thresh):
             assert 0 < len(want) < n                                    # the case does suppress something
 
 
+def test_rotated_nms_with_non_finite_scores(gpu, oracle):
+    """A NaN or infinite score (a non-finite fp16 head output makes one) must not break the ranking: NaN ranks as
+    minus infinity, +inf first, every box still gets a rank of its own and the kept list equals the oracle's."""
+    import torch
+
+    rs = np.random.RandomState(77)
+    n, M = 200, 256
+    for attempt in range(20):
+        cand = _random_boxes(rs, n, 60.0)
+        if _clear_of_threshold(oracle, cand, 0.1):
+            break
+    else:
+        pytest.fail("could not draw boxes clear of the threshold")
+    cand[[3, 50, 51, 120], 8] = np.nan
+    cand[[7, 90], 8] = np.inf
+    cand[[11, 140], 8] = -np.inf
+    boxes = np.zeros((1, M, 9), np.float32)
+    boxes[0, :n] = cand
+    kept, kept_num = gpu.rotated_nms(torch.from_numpy(boxes).cuda(), torch.tensor([n], dtype=torch.int32, device="cuda"), 0.1)
+    kept, kept_num = kept.cpu().numpy(), kept_num.cpu().numpy()
+    want, order = oracle.rotated_nms(cand, 0.1)
+    assert int(kept_num[0]) == len(want)
+    np.testing.assert_array_equal(kept[0, :len(want)].view(np.uint32), want.view(np.uint32))   # bit patterns: NaN == NaN
+    assert not kept[0, len(want):].any()
+    assert order[0] == 7 and order[1] == 90    # +inf first, lower row first among equals
+
+
 def test_rotated_nms_table_larger_than_the_staged_copy(gpu, oracle):
     """A 1,200-row box table: its suppression mask (1,200 x 19 words) does not fit the block's staging buffer,
     so the greedy pass reads the mask in place; same answer as the oracle."""

@@ -67,3 +67,20 @@ def test_static_scratch_rejects_requests_beyond_its_size(gpu):
     rc, *_ = _call_static(gpu, big, pts, sizes)
     assert rc == -3
     assert b"built-in scratch" in gpu.lib().sessd_last_cuda_error()
+
+
+def test_static_scratch_reports_lost_voxels_through_its_status_reader(gpu):
+    """A frame with more voxels than max_voxels ends with voxel_num == max_voxels, exactly like a frame that fits
+    exactly; the status word inside the built-in array tells the two apart."""
+    import torch
+
+    f = gpu.synth.single_frame()
+    pts = torch.from_numpy(f[None]).cuda()
+    sizes = torch.tensor([len(f)], dtype=torch.int32, device="cuda")
+    small = gpu.voxel_params(4000)
+    rc, voxels, coors, num = _call_static(gpu, small, pts, sizes)
+    assert rc == 0 and int(num[0]) == 4000
+    st = gpu.lib().sessd_voxelize_static_status(None)
+    assert st >= 0 and st & gpu.STATUS_VOXEL_OVERFLOW
+    rc, voxels, coors, num = _call_static(gpu, gpu.voxel_params(20000), pts, sizes)
+    assert rc == 0 and gpu.lib().sessd_voxelize_static_status(None) == 0
