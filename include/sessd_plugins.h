@@ -70,6 +70,11 @@ int sessd_plugin_enqueue(sessd_plugin* p, const sessd_tensor_desc* input_desc, c
 size_t sessd_plugin_serialization_size(const sessd_plugin* p);
 void sessd_plugin_serialize(const sessd_plugin* p, void* buffer);
 
+/* 1 when the library was built with TensorRT's headers present, i.e. when it also holds the seven
+ * nvinfer1::IPluginV2DynamicExt classes over the plugins above and registers their creators with
+ * REGISTER_TENSORRT_PLUGIN as the reference does (voxelGenerator.h:111 and the sibling headers); 0 otherwise. */
+int sessd_tensorrt_shim_present(void);
+
 #ifdef __cplusplus
 }
 #endif

@@ -11,7 +11,7 @@ _CSRC = os.path.join(_HERE, "csrc")
 LIB_PATH = os.path.join(_HERE, "libsessd.so")
 
 SOURCES = ["capi.cu", "voxelize.cu", "rulebook.cu", "conv_simt.cu", "conv_umma.cu", "sparse2dense.cu", "voxelize_static.cu",
-           "postprocess.cu", "nms.cu", "plugins.cu", "formats.cu"]
+           "postprocess.cu", "nms.cu", "plugins.cu", "formats.cu", "trt_shim.cpp"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "-Xcompiler", "-fPIC", "-shared",
@@ -23,6 +23,19 @@ def _nvcc() -> str:
     if not os.path.exists(nvcc):
         raise RuntimeError("nvcc not found: the CUDA library cannot be built")
     return nvcc
+
+
+def tensorrt_include_dir():
+    """Directory that holds TensorRT's NvInferPlugin.h, or None. csrc/trt_shim.cpp (the IPluginV2DynamicExt classes
+    over the plugin mirrors) compiles to an empty object without it; with it the library also links nvinfer."""
+    roots = [os.environ.get("TENSORRT_ROOT", ""), "/usr", "/usr/local", "/usr/local/cuda", "/usr/local/tensorrt",
+             "/opt/tensorrt"]
+    dirs = [os.path.join(r, sub) for r in roots if r for sub in ("include", "include/x86_64-linux-gnu", "targets/x86_64-linux/include")]
+    dirs += [d for d in os.environ.get("CPATH", "").split(":") if d]
+    for d in dirs:
+        if os.path.exists(os.path.join(d, "NvInferPlugin.h")):
+            return d
+    return None
 
 
 def _stale() -> bool:
@@ -39,6 +52,9 @@ def build(force: bool = False, verbose: bool = False) -> str:
         return LIB_PATH
     srcs = [os.path.join(_CSRC, s) for s in SOURCES if os.path.exists(os.path.join(_CSRC, s))]
     cmd = [_nvcc(), *NVCC_FLAGS, "-I", os.path.join(_ROOT, "include"), "-I", _CSRC, "-o", LIB_PATH, *srcs]
+    trt = tensorrt_include_dir()
+    if trt:
+        cmd += ["-I", trt, "-lnvinfer"]
     if verbose:
         cmd += ["-Xptxas", "-v"]
         print(" ".join(cmd))
