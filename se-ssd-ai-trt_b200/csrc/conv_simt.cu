@@ -186,6 +186,66 @@ conv_simt_kernel(const T* __restrict__ in, T* __restrict__ out, const int32_t* _
     }
 }
 
+__device__ __forceinline__ float to_float(float v) { return v; }
+__device__ __forceinline__ float to_float(__half v) { return __half2float(v); }
+
+// Any channel counts (the reference's kernel takes in_channel and out_channel as run-time values,
+// submConv3dlayer.cu:479-518): one warp per output row, lane = output channel (in rounds of 32), the same order of
+// additions as above - per neighbour a fused chain over ci, neighbours added in ascending k. The pairs of the
+// network's schedule never come here; this keeps the plugin entry points usable for other layer shapes.
+template <typename T>
+__global__ void __launch_bounds__(kThreads)
+conv_generic_kernel(const T* __restrict__ in, T* __restrict__ out, const int32_t* __restrict__ nbr,
+                    const int32_t* __restrict__ out_num, const T* __restrict__ weights, const float* __restrict__ scale,
+                    const float* __restrict__ shift, int relu, int batch, int max_voxels, int kvol, int cin, int cout,
+                    T* __restrict__ dense, const int4* __restrict__ out_coors, int D, int H, int W) {
+    constexpr int ROWS = kThreads / 32;
+    const int lane = threadIdx.x & 31, wrow = threadIdx.x >> 5;
+    const int chunks = (max_voxels + ROWS - 1) / ROWS;
+    const int items = batch * chunks;
+    for (int it = blockIdx.x; it < items; it += gridDim.x) {
+        const int b = it / chunks;
+        const int o = (it - b * chunks) * ROWS + wrow;
+        int n = out_num[b];
+        n = n > max_voxels ? max_voxels : n;
+        if (o >= n) continue;
+        const int32_t* nb = nbr + (size_t)b * kvol * max_voxels + o;
+        const T* in_b = in + (size_t)b * max_voxels * cin;
+        T* d = nullptr;
+        if (dense) {
+            const int4 c4 = __ldg(&out_coors[(size_t)b * max_voxels + o]);
+            d = dense + (size_t)b * cout * D * H * W + ((size_t)c4.y * H + c4.z) * W + c4.w;
+        }
+        for (int co = lane; co < cout; co += 32) {
+            float acc = 0.f;
+            for (int k = 0; k < kvol; ++k) {
+                const int idx = __ldg(nb + (size_t)k * max_voxels);
+                if (idx < 0) continue;
+                const T* x = in_b + (size_t)idx * cin;
+                const T* wk = weights + (size_t)k * cin * cout + co;
+                float sum = 0.f;
+                for (int ci = 0; ci < cin; ++ci) sum = fmaf(to_float(x[ci]), to_float(wk[(size_t)ci * cout]), sum);
+                acc = __fadd_rn(acc, sum);
+            }
+            if (scale) acc = fmaf(acc, __ldg(scale + co), shift ? __ldg(shift + co) : 0.f);
+            if (relu) acc = acc > 0.f ? acc : 0.f;
+            const T v = from_float<T>(acc);
+            out[((size_t)b * max_voxels + o) * cout + co] = v;
+            if (d) d[(size_t)co * D * H * W] = v;
+        }
+    }
+}
+
+template <typename T>
+int launch_generic(const ConvLaunch& c, cudaStream_t stream) {
+    SESSD_LAUNCH_NAMED(sizeof(T) == 4 ? "conv_generic<f32>" : "conv_generic<f16>", conv_generic_kernel<T>,
+                       persistent_grid(8), kThreads, 0, stream, static_cast<const T*>(c.in), static_cast<T*>(c.out), c.nbr,
+                       c.out_num, static_cast<const T*>(c.weights), c.scale, c.shift, c.relu, c.batch, c.max_voxels,
+                       c.kvol, c.cin, c.cout, static_cast<T*>(c.dense), reinterpret_cast<const int4*>(c.out_coors), c.D,
+                       c.H, c.W);
+    return SESSD_OK;
+}
+
 template <typename T, int CIN, int COUT>
 int launch_one(const ConvLaunch& c, cudaStream_t stream) {
     static const std::string name = std::string("conv_simt<") + (sizeof(T) == 4 ? "f32," : "f16,") +
@@ -208,15 +268,12 @@ int dispatch(const ConvLaunch& c, cudaStream_t stream) {
     SESSD_CASE(32, 64)
     SESSD_CASE(64, 64)
 #undef SESSD_CASE
-    return SESSD_ERR_UNSUPPORTED;
+    return launch_generic<T>(c, stream);   // any other pair of channel counts
 }
 
 }  // namespace
 
-bool conv_simt_supported(int cin, int cout) {
-    return (cin == 4 && cout == 16) || (cin == 16 && (cout == 16 || cout == 32)) || (cin == 32 && (cout == 32 || cout == 64)) ||
-           (cin == 64 && cout == 64);
-}
+bool conv_simt_supported(int cin, int cout) { return cin >= 1 && cout >= 1 && cin <= 4096 && cout <= 4096; }
 
 int launch_conv_simt(const ConvLaunch& c, cudaStream_t stream) {
     return c.dtype == SESSD_F32 ? dispatch<float>(c, stream) : dispatch<__half>(c, stream);

@@ -147,6 +147,25 @@ def test_subm_other_kernel_sizes_take_the_generic_map_path(gpu, oracle, ksize, p
     _check_layer(gpu, oracle, layer, frames, W, dtype=dtype)
 
 
+@pytest.mark.parametrize("cin,cout,dtype", [(3, 5, 0), (8, 24, 0), (24, 8, 1), (5, 40, 1), (128, 16, 0)])
+def test_channel_counts_outside_the_schedule(gpu, oracle, cin, cout, dtype):
+    """The reference's plugins take any in_channel / out_channel (submConv3dlayer.cu:479-518 loops over run-time
+    counts); pairs that have no specialised kernel run on the run-time-shaped CUDA-core kernel, with the same
+    parity bar: rulebook exact, fp32 bit-equal to the oracle's order of additions, fp16 within 1e-2."""
+    rs = np.random.RandomState(cin * 131 + cout)
+    shape = (6, 20, 24)
+    frames = [(_random_coords(rs, n, shape), None) for n in (500, 90)]
+    frames = [(c, rs.randn(len(c), cin).astype(np.float32)) for c, _ in frames]
+    W = (rs.randn(27, cin, cout) / np.sqrt(9 * cin)).astype(np.float32)
+    sc = (1 + 0.1 * rs.randn(cout)).astype(np.float32)
+    sh = (0.1 * rs.randn(cout)).astype(np.float32)
+    _check_layer(gpu, oracle, _layer(gpu, True, cin, cout, (3, 3, 3), (1, 1, 1), (1, 1, 1), shape), frames, W, sc, sh,
+                 True, dtype=dtype)
+    Ws = (rs.randn(27, cin, cout) / np.sqrt(4 * cin)).astype(np.float32)
+    _check_layer(gpu, oracle, _layer(gpu, False, cin, cout, (3, 3, 3), (2, 2, 2), (1, 1, 1), shape), frames, Ws,
+                 dtype=dtype, maxV=2048)
+
+
 STRIDED = [
     ((3, 3, 3), (2, 2, 2), (1, 1, 1), (9, 22, 26), 16, 32),
     ((3, 3, 3), (2, 2, 2), (1, 1, 1), (7, 20, 24), 32, 64),
