@@ -265,6 +265,13 @@ void sessd_pipeline_destroy(sessd_pipeline* pl);
  * whole run (a run clears them when it starts). */
 int sessd_pipeline_run_host(sessd_pipeline* pl, const float* host_points, const int32_t* host_sizes, int nframes,
                             int32_t* host_voxel_num, int32_t* host_status, float* elapsed_ms);
+/* The same, and every group's dense BEV maps are also copied to the host: host_dense (ideally pinned) holds
+ * nstreams regions of batch maps each, [nstreams][batch][C*D][H][W] in the backbone's data type; the maps of a group
+ * land in the region of the stream slot it ran on (group g uses slot g % nstreams) and are overwritten by that slot's
+ * next group. The reference itself copies only the filtered boxes back (se-ssd-ai-trt.cpp:1876-1879); this variant
+ * measures what it costs a host-side consumer of the map. */
+int sessd_pipeline_run_host_bev(sessd_pipeline* pl, const float* host_points, const int32_t* host_sizes, int nframes,
+                                int32_t* host_voxel_num, int32_t* host_status, void* host_dense, float* elapsed_ms);
 /* Same work with the points already on the device: points f32 [nframes][max_points][4], sizes i32 [nframes].
  * Kernels are enqueued on the pipeline's streams; elapsed device time between the first and the last
  * stream event is returned in *elapsed_ms when it is non-null. */

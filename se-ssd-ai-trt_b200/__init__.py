@@ -29,7 +29,7 @@ EXPORTS = (
     "sessd_backbone_workspace_bytes", "sessd_backbone_enqueue", "sessd_backbone_pair_counts",
     "sessd_backbone_layer_view",
     "sessd_backbone_final_level", "sessd_pipeline_create", "sessd_pipeline_destroy", "sessd_pipeline_run_host",
-    "sessd_pipeline_run_device", "sessd_pipeline_dense", "sessd_pipeline_workspace", "sessd_pipeline_use_graphs",
+    "sessd_pipeline_run_device", "sessd_pipeline_run_host_bev", "sessd_pipeline_dense", "sessd_pipeline_workspace", "sessd_pipeline_use_graphs",
     "sessd_launch_count",
     "sessd_profile_begin", "sessd_profile_end", "sessd_read_status", "sessd_last_cuda_error", "sessd_version",
     "sessd_anchor_decode_enqueue", "sessd_filter_boxes_workspace_bytes", "sessd_filter_boxes_enqueue",
@@ -188,6 +188,14 @@ def voxelize(points, points_size, params: VoxelParams, out_dtype=F32):
     return dict(voxels=voxels, coors=coors, voxel_num=num, num_points=npv, status=status)
 
 
+def voxelize_into(points, points_size, params: VoxelParams, voxels, coors, voxel_num, workspace, out_dtype=F32):
+    """sessd_voxelize_enqueue into caller-owned outputs and workspace (nothing is allocated, nothing is read back)."""
+    B, P = points.shape[0], points.shape[1]
+    _check(lib().sessd_voxelize_enqueue(C.byref(params), B, P, out_dtype, _vp(points, points_size),
+                                        _vp(voxels, coors, voxel_num), C.c_void_p(workspace.data_ptr()),
+                                        C.c_size_t(workspace.numel()), _stream()), "sessd_voxelize_enqueue")
+
+
 class ConvWeights:
     """Device weights of one sparse conv layer (+ optional folded scale/shift/ReLU epilogue)."""
 
@@ -243,6 +251,13 @@ def subm_conv(feat, coors, voxel_num, params: ConvParams, weights: ConvWeights, 
     if keep_workspace:
         r["workspace"] = ws
     return r
+
+
+def subm_conv_into(feat, coors, voxel_num, params: ConvParams, weights: ConvWeights, out, workspace):
+    """sessd_subm_conv_enqueue into a caller-owned output and workspace (nothing is allocated or read back)."""
+    _check(lib().sessd_subm_conv_enqueue(C.byref(params), weights.handle, feat.shape[0], _vp(feat, coors, voxel_num),
+                                         _vp(out), C.c_void_p(workspace.data_ptr()), C.c_size_t(workspace.numel()),
+                                         _stream()), "sessd_subm_conv_enqueue")
 
 
 def sparse_conv(feat, coors, voxel_num, params: ConvParams, weights: ConvWeights, keep_workspace=False):
@@ -511,6 +526,16 @@ class Pipeline:
         _check(lib().sessd_pipeline_run_host(self.handle, C.c_void_p(points.data_ptr()), C.c_void_p(sizes.data_ptr()),
                                              points.shape[0], C.c_void_p(voxel_num.data_ptr()),
                                              C.c_void_p(status.data_ptr()), C.byref(ms)), "sessd_pipeline_run_host")
+        return float(ms.value)
+
+    def run_host_bev(self, points, sizes, voxel_num, status, host_dense) -> float:
+        """run_host, and every group's BEV maps are copied into host_dense, pinned [nstreams, batch, C*D, H, W]
+        (the region of the stream slot the group ran on)."""
+        ms = C.c_float(0)
+        _check(lib().sessd_pipeline_run_host_bev(self.handle, C.c_void_p(points.data_ptr()), C.c_void_p(sizes.data_ptr()),
+                                                 points.shape[0], C.c_void_p(voxel_num.data_ptr()),
+                                                 C.c_void_p(status.data_ptr()), C.c_void_p(host_dense.data_ptr()),
+                                                 C.byref(ms)), "sessd_pipeline_run_host_bev")
         return float(ms.value)
 
     def dense(self, s):

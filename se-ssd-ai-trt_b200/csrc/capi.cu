@@ -919,7 +919,7 @@ void* sessd_pipeline_workspace(sessd_pipeline* pl, int s) {
 }
 
 static int pipeline_run(sessd_pipeline* pl, const void* points, const int32_t* sizes, int nframes, bool host,
-                        int32_t* host_voxel_num, int32_t* host_status, float* elapsed_ms) {
+                        int32_t* host_voxel_num, int32_t* host_status, float* elapsed_ms, void* host_dense = nullptr) {
     if (!pl || !points || !sizes) return SESSD_ERR_NULL;
     if (nframes < 1) return SESSD_ERR_PARAM;
     const sessd_backbone* bb = pl->bb;
@@ -997,6 +997,13 @@ static int pipeline_run(sessd_pipeline* pl, const void* points, const int32_t* s
             if (host_status)
                 SESSD_CUDA(cudaMemcpyAsync(host_status + f0, pl->ws[s], 4, cudaMemcpyDeviceToHost, st));
         }
+        if (host && host_dense && pl->dense_bytes) {
+            // the group's BEV maps go to the host region of its stream slot (a consumer takes them from there
+            // before the slot's next group lands)
+            const size_t per_frame = pl->dense_bytes / pl->batch;
+            SESSD_CUDA(cudaMemcpyAsync(static_cast<char*>(host_dense) + (size_t)s * pl->dense_bytes, pl->dense[s],
+                                       (size_t)nb * per_frame, cudaMemcpyDeviceToHost, st));
+        }
     }
     float worst = 0.f;
     for (int s = 0; s < pl->nstreams; ++s) SESSD_CUDA(cudaEventRecord(pl->done[s], pl->streams[s]));
@@ -1018,6 +1025,12 @@ static int pipeline_run(sessd_pipeline* pl, const void* points, const int32_t* s
 int sessd_pipeline_run_host(sessd_pipeline* pl, const float* host_points, const int32_t* host_sizes, int nframes,
                             int32_t* host_voxel_num, int32_t* host_status, float* elapsed_ms) {
     return pipeline_run(pl, host_points, host_sizes, nframes, true, host_voxel_num, host_status, elapsed_ms);
+}
+
+int sessd_pipeline_run_host_bev(sessd_pipeline* pl, const float* host_points, const int32_t* host_sizes, int nframes,
+                                int32_t* host_voxel_num, int32_t* host_status, void* host_dense, float* elapsed_ms) {
+    if (!host_dense) return SESSD_ERR_NULL;
+    return pipeline_run(pl, host_points, host_sizes, nframes, true, host_voxel_num, host_status, elapsed_ms, host_dense);
 }
 
 int sessd_pipeline_run_device(sessd_pipeline* pl, const void* points, const void* sizes, int nframes,

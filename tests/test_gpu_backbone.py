@@ -385,6 +385,12 @@ def test_pipeline_groups_equal_direct_backbone_runs(gpu, graphs):
             assert torch.equal(pipe.dense(0)[0], want_dense[4]) and torch.equal(pipe.dense(0)[1], want_dense[5])
             assert torch.equal(pipe.dense(1)[0], want_dense[6])
     assert len(set(launches)) == 1 and launches[0] > 0      # replayed kernels are counted like launched ones
+    # the variant that also brings the BEV maps to the host: one region per stream slot, holding its last group
+    host_dense = torch.zeros((2, B) + tuple(want_dense[0].shape), dtype=torch.float16).pin_memory()
+    pipe.run_host_bev(host_pts, host_sizes, vnum, status, host_dense)
+    assert vnum.tolist() == want_num and status.tolist() == [0] * F
+    assert torch.equal(host_dense[0, 0], want_dense[4].cpu()) and torch.equal(host_dense[0, 1], want_dense[5].cpu())
+    assert torch.equal(host_dense[1, 0], want_dense[6].cpu())
     pipe.close()
     bb.close()
 
