@@ -19,7 +19,7 @@
 //   warps 4-7    MMA issuers; issuer t owns tile t of every group. The warp works out the group's schedule
 //                once (lane g for stage g) and walks it together; one elected lane issues the tcgen05.mma and
 //                commit instructions (each costs its thread on the order of a hundred cycles, so four share).
-//   warp  8      streams the weight blocks (cp.async.bulk) into a two-slot ring.
+//   warp  8      streams the weight blocks (cp.async.bulk) into a three-slot ring.
 //   warp  9      prefetches the neighbour indices of upcoming (tile, stage) items into a ring of index blocks
 //                with bulk copies, sixteen items side by side (one lane each), two to three slot cycles ahead.
 //   warps 10..   gather. The A ring has one 16 KB slot per gather warp: item q (the q-th (tile, stage) pair
@@ -53,7 +53,7 @@ constexpr int INDEX_WARP = WEIGHT_WARP + 1;
 constexpr int FIRST_GATHER_WARP = INDEX_WARP + 1;
 constexpr int NSLOT_MAX = 12;
 constexpr int NIDX_MAX = 36;
-constexpr int B_STAGES = 2;
+constexpr int B_STAGES = 3;                  // weight ring: a group needs up to 27 blocks, each an L2 round trip away
 constexpr int ROW_BYTES = 128;               // 64 halves per A/B row
 constexpr int A_BYTES = TILE_M * ROW_BYTES;  // 16 KB
 constexpr int KVOL_MAX = 27;
@@ -374,7 +374,9 @@ conv_umma_kernel(const __half* __restrict__ in, __half* __restrict__ out, const 
     {
         const int per = (total_tiles + THREADS - 1) / THREADS;
         const int first = tid * per, last = first + per < total_tiles ? first + per : total_tiles;
-        auto tile_weight = [&](uint32_t mask) { return (uint32_t)(__popc(stage_bits<KG>(mask)) + 2); };
+        // a tile costs its items plus its share of the group hand-over and of the epilogue, about eight items' worth
+        // (fitted to the CTA lifetimes of 1/4-resolution launches)
+        auto tile_weight = [&](uint32_t mask) { return (uint32_t)(__popc(stage_bits<KG>(mask)) + 8); };
         int f = 0, f_first = 0, f_tiles = batch > 0 ? (frame_rows(0) + TILE_M - 1) / TILE_M : 0;
         auto seek = [&](int tile) {   // frame of a tile of the sequence (tiles are visited in ascending order)
             while (f < batch && tile >= f_first + f_tiles) {
@@ -427,31 +429,50 @@ conv_umma_kernel(const __half* __restrict__ in, __half* __restrict__ out, const 
     }
     __syncthreads();
     const int range_lo = ctl->range_lo, range_hi = ctl->range_hi;
-    int b = 0, frame_first = 0;                 // frame of the cursor and the global index of its first tile
-    int n = batch > 0 ? frame_rows(0) : 0;
-    int frame_tiles = (n + TILE_M - 1) / TILE_M;
-
-    for (int cur = range_lo; cur < range_hi;) {
-        while (cur >= frame_first + frame_tiles) {
-            frame_first += frame_tiles;
-            ++b;
-            n = frame_rows(b);
-            frame_tiles = (n + TILE_M - 1) / TILE_M;
+    // The walk is one group ahead of the work: the masks of the next group are requested when the current group
+    // starts, so that no role sits in the latency of those reads at a group boundary (every role of the CTA would
+    // stall there at about the same time and drain the pipeline).
+    int c_b = 0, c_first = 0;                   // cursor: frame and the global index of its first tile
+    int c_n = batch > 0 ? frame_rows(0) : 0;
+    int c_tiles = (c_n + TILE_M - 1) / TILE_M;
+    int c_cur = range_lo;
+    int nx_b = 0, nx_n = 0, nx_tile0 = 0, nx_cnt = 0;   // the next group
+    uint32_t nx_m[TILES] = {0u, 0u, 0u, 0u};
+    auto fetch_next = [&]() {
+        nx_cnt = 0;
+        if (c_cur >= range_hi) return;
+        while (c_cur >= c_first + c_tiles) {
+            c_first += c_tiles;
+            ++c_b;
+            c_n = frame_rows(c_b);
+            c_tiles = (c_n + TILE_M - 1) / TILE_M;
         }
-        const int tile0 = cur - frame_first;
-        int cnt = range_hi - cur;
+        nx_b = c_b;
+        nx_n = c_n;
+        nx_tile0 = c_cur - c_first;
+        int cnt = range_hi - c_cur;
         cnt = cnt > TILES ? TILES : cnt;
-        cnt = cnt > frame_tiles - tile0 ? frame_tiles - tile0 : cnt;
-        cur += cnt;
+        cnt = cnt > c_tiles - nx_tile0 ? c_tiles - nx_tile0 : cnt;
+        nx_cnt = cnt;
+        c_cur += cnt;
+#pragma unroll
+        for (int t = 0; t < TILES; ++t)
+            nx_m[t] = t < cnt ? __ldg(tile_mask + (size_t)nx_b * tiles_per_frame + nx_tile0 + t) : 0u;
+    };
+    fetch_next();
+
+    while (nx_cnt > 0) {
+        const int b = nx_b, n = nx_n, tile0 = nx_tile0, cnt = nx_cnt;
         const int row0 = tile0 * TILE_M;
-        if (*abort_flag) break;
         uint32_t m[TILES];
         uint32_t any = 0;
 #pragma unroll
         for (int t = 0; t < TILES; ++t) {
-            m[t] = t < cnt ? __ldg(tile_mask + (size_t)b * tiles_per_frame + tile0 + t) : 0u;
+            m[t] = nx_m[t];
             any |= m[t];
         }
+        fetch_next();   // reads issued now, used at the top of the next iteration
+        if (*abort_flag) break;
         // items and weight blocks this group consumes
         const uint32_t sb0 = stage_bits<KG>(m[0]), sb1 = stage_bits<KG>(m[1]), sb2 = stage_bits<KG>(m[2]),
                        sb3 = stage_bits<KG>(m[3]);
@@ -642,7 +663,7 @@ conv_umma_kernel(const __half* __restrict__ in, __half* __restrict__ out, const 
                     const uint32_t pos = a_it + (uint32_t)(acts - act) + (uint32_t)__popc(bits & ((1u << t) - 1u));
                     const uint32_t my_b = b_it + (uint32_t)(blks - blk);
                     info = (bits ? 1u : 0u) | (((bits >> t) & 1u) << 1) | ((my_b % B_STAGES) << 2) |
-                           (((my_b / B_STAGES) & 1u) << 3) | ((pos % NSLOT) << 4) | (pos << 8);
+                           (((my_b / B_STAGES) & 1u) << 4) | ((pos % NSLOT) << 5) | (pos << 9);
                 }
                 // the epilogue must have read this set's previous contents (two groups back)
                 bool ok = mbar_wait<false, true>(smem_u32(&ctl->acc_empty[set]), set_phase ^ 1u, abort_flag,
@@ -653,14 +674,14 @@ conv_umma_kernel(const __half* __restrict__ in, __half* __restrict__ out, const 
                 for (int g = 0; g < nstages && ok; ++g) {
                     const uint32_t inf = __shfl_sync(0xFFFFFFFFu, info, g);
                     if (!(inf & 1u)) continue;
-                    const uint32_t sb = (inf >> 2) & 1u;
-                    ok = mbar_wait<false, true>(smem_u32(&ctl->b_full[sb]), (inf >> 3) & 1u, abort_flag,
+                    const uint32_t sb = (inf >> 2) & 3u;
+                    ok = mbar_wait<false, true>(smem_u32(&ctl->b_full[sb]), (inf >> 4) & 1u, abort_flag,
                                                 5 | (int)((b_it + g) << 4));
                     if (!ok) break;
                     if (inf & 2u) {
-                        const uint32_t sa = (inf >> 4) & 15u;
+                        const uint32_t sa = (inf >> 5) & 15u;
                         ok = mbar_wait<false, true>(smem_u32(&ctl->a_full[t][sa]), (full_phase >> sa) & 1u, abort_flag,
-                                                    6 | (int)((inf >> 8) << 4));
+                                                    6 | (int)((inf >> 9) << 4));
                         full_phase ^= 1u << sa;   // this issuer's next use of the slot is the next phase
                         if (!ok) break;
                         if (leader) {
