@@ -61,7 +61,7 @@ def measured_traffic(workload, kernel):
 
 WORKLOADS = {
     # name: (points per frame, object clusters, frames per GPU per step, max_voxels, frames per launch group)
-    "sweep": dict(points=120000, boxes=40, frames=512, max_voxels=200000, batch=8,
+    "sweep": dict(points=120000, boxes=40, frames=512, max_voxels=200000, batch=16, streams=3,
                   desc="throughput sweep: 512 frames x 120,000 points per GPU"),
     "single": dict(points=20000, boxes=15, frames=2048, max_voxels=60000, batch=32,
                    desc="20,000-point frames (single-frame backbone case), 2048 per GPU"),
@@ -438,7 +438,7 @@ def main():
     ap.add_argument("--workload", default="sweep", choices=sorted(WORKLOADS))
     ap.add_argument("--frames", type=int, default=0, help="frames per GPU per step (default: the workload's)")
     ap.add_argument("--batch", type=int, default=0, help="frames per launch group")
-    ap.add_argument("--streams", type=int, default=4, help="launch groups in flight per GPU")
+    ap.add_argument("--streams", type=int, default=0, help="launch groups in flight per GPU (default: the workload's, else 4)")
     ap.add_argument("--graphs", action="store_true", help="replay each launch group from a CUDA graph")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--detect", action="store_true", help="(kept for compatibility: the 1-GPU line always carries `detect`)")
@@ -461,6 +461,8 @@ def main():
         wl["frames"] = args.frames
     if args.batch:
         wl["batch"] = args.batch
+    if not args.streams:
+        args.streams = wl.get("streams", 4)
 
     if args.impl == "reference":
         run_reference(args, pkg, wl, rank, world)

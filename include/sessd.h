@@ -254,7 +254,10 @@ int sessd_backbone_layer_view(const sessd_backbone* bb, int batch, int max_point
  * final voxel count and status word back to the host. Replaces the per-frame body of the reference's
  * inference loop (se-ssd-ai-trt.cpp:1858-1894: H2D copy, enqueueV2, D2H copy, stream sync). The dense
  * BEV map of the last group stays on the device (the reference also keeps it there for its 2D head).
- * A pipeline owns its device buffers and streams; create/destroy allocate and free them. */
+ * A pipeline owns its device buffers and streams; create/destroy allocate and free them. Host-buffer runs
+ * (without graph replay) copy a slot's next group in on a stream of their own while its current group
+ * computes, and the BEV maps of sessd_pipeline_run_host_bev out on another: the first such run allocates a
+ * second set of input (and BEV) buffers per slot for this. */
 typedef struct sessd_pipeline sessd_pipeline;
 int sessd_pipeline_create(const sessd_backbone* bb, int batch, int max_points, int nstreams, sessd_pipeline** out);
 void sessd_pipeline_destroy(sessd_pipeline* pl);
@@ -282,7 +285,8 @@ int sessd_pipeline_run_device(sessd_pipeline* pl, const void* points, const void
  * Device-resident inputs are then copied into the slot's staging buffers first. Off by default. No counterpart
  * in the reference, which launches every kernel of every frame from the host. */
 int sessd_pipeline_use_graphs(sessd_pipeline* pl, int enable);
-/* Dense BEV buffer / workspace of stream `s` (device pointers; dense is [batch][C*D][H][W]). */
+/* Dense BEV buffer / workspace of stream `s` (device pointers; dense is [batch][C*D][H][W]): the buffer the slot's
+ * latest group wrote (a slot alternates between two during sessd_pipeline_run_host_bev). */
 void* sessd_pipeline_dense(sessd_pipeline* pl, int s);
 void* sessd_pipeline_workspace(sessd_pipeline* pl, int s);
 /* Index of the last coordinate level of a backbone (number of strided layers). */

@@ -834,6 +834,16 @@ struct sessd_pipeline {
     std::vector<int32_t*> sizes;
     std::vector<cudaEvent_t> done;
     cudaEvent_t start;
+    // Host-buffer runs: the points of a slot's next group are copied in (stream h2d) while its current group
+    // computes, and a group's BEV maps are copied out (stream d2h) while the slot's next group computes. Each
+    // slot therefore has two input and two BEV buffers, used alternately ([2 * s + half]; half 0 are the
+    // buffers above, which every other kind of run uses alone).
+    cudaStream_t h2d, d2h;
+    cudaEvent_t bev_all;                                   // the output stream has copied the run's last BEV maps
+    std::vector<void*> pts_alt, dense_alt;
+    std::vector<int32_t*> sizes_alt;
+    std::vector<cudaEvent_t> in_ready, in_free, bev_out;   // [2 * s + half]
+    std::vector<int> last_half;                            // BEV buffer half of the slot's latest group
     // optional: the launch sequence of one full group, captured once per stream slot and replayed
     bool use_graphs;
     std::vector<cudaGraphExec_t> graphs;
@@ -850,6 +860,17 @@ void sessd_pipeline_destroy(sessd_pipeline* pl) {
     for (auto p : pl->dense) if (p) cudaFree(p);
     for (auto p : pl->pts) if (p) cudaFree(p);
     for (auto p : pl->sizes) if (p) cudaFree(p);
+    if (pl->h2d) cudaStreamSynchronize(pl->h2d);
+    if (pl->d2h) cudaStreamSynchronize(pl->d2h);
+    for (auto p : pl->pts_alt) if (p) cudaFree(p);
+    for (auto p : pl->dense_alt) if (p) cudaFree(p);
+    for (auto p : pl->sizes_alt) if (p) cudaFree(p);
+    for (auto e : pl->in_ready) if (e) cudaEventDestroy(e);
+    for (auto e : pl->in_free) if (e) cudaEventDestroy(e);
+    for (auto e : pl->bev_out) if (e) cudaEventDestroy(e);
+    if (pl->bev_all) cudaEventDestroy(pl->bev_all);
+    if (pl->h2d) cudaStreamDestroy(pl->h2d);
+    if (pl->d2h) cudaStreamDestroy(pl->d2h);
     for (auto g : pl->graphs) if (g) cudaGraphExecDestroy(g);
     for (auto e : pl->done) if (e) cudaEventDestroy(e);
     if (pl->start) cudaEventDestroy(pl->start);
@@ -884,7 +905,24 @@ int sessd_pipeline_create(const sessd_backbone* bb, int batch, int max_points, i
     pl->graphs.assign(nstreams, nullptr);
     pl->warmed.assign(nstreams, 0);
     pl->graph_kernels.assign(nstreams, 0);
+    pl->h2d = pl->d2h = nullptr;
+    pl->bev_all = nullptr;
+    pl->pts_alt.assign(nstreams, nullptr);
+    pl->dense_alt.assign(nstreams, nullptr);
+    pl->sizes_alt.assign(nstreams, nullptr);
+    pl->in_ready.assign(2 * nstreams, nullptr);
+    pl->in_free.assign(2 * nstreams, nullptr);
+    pl->bev_out.assign(2 * nstreams, nullptr);
+    pl->last_half.assign(nstreams, 0);
     cudaError_t e = cudaEventCreate(&pl->start);
+    if (e == cudaSuccess) e = cudaStreamCreateWithFlags(&pl->h2d, cudaStreamNonBlocking);
+    if (e == cudaSuccess) e = cudaStreamCreateWithFlags(&pl->d2h, cudaStreamNonBlocking);
+    if (e == cudaSuccess) e = cudaEventCreateWithFlags(&pl->bev_all, cudaEventDisableTiming);
+    for (int i = 0; i < 2 * nstreams && e == cudaSuccess; ++i) {
+        e = cudaEventCreateWithFlags(&pl->in_ready[i], cudaEventDisableTiming);
+        if (e == cudaSuccess) e = cudaEventCreateWithFlags(&pl->in_free[i], cudaEventDisableTiming);
+        if (e == cudaSuccess) e = cudaEventCreateWithFlags(&pl->bev_out[i], cudaEventDisableTiming);
+    }
     for (int s = 0; s < nstreams && e == cudaSuccess; ++s) {
         e = cudaStreamCreateWithFlags(&pl->streams[s], cudaStreamNonBlocking);
         if (e == cudaSuccess) e = cudaMalloc(&pl->ws[s], ws_bytes);
@@ -910,7 +948,7 @@ int sessd_pipeline_use_graphs(sessd_pipeline* pl, int enable) {
 
 void* sessd_pipeline_dense(sessd_pipeline* pl, int s) {
     if (!pl || s < 0 || s >= pl->nstreams) return nullptr;
-    return pl->dense[s];
+    return pl->last_half[s] ? pl->dense_alt[s] : pl->dense[s];
 }
 
 void* sessd_pipeline_workspace(sessd_pipeline* pl, int s) {
@@ -925,8 +963,21 @@ static int pipeline_run(sessd_pipeline* pl, const void* points, const int32_t* s
     const sessd_backbone* bb = pl->bb;
     const size_t frame_bytes = (size_t)pl->max_points * 16;
     const int last_layer = (int)bb->layers.size() - 1;
+    // Host-buffer runs without graph replay overlap the copies with the compute (see sessd_pipeline); the second
+    // set of buffers is allocated on the first such run.
+    const bool overlap = host && !pl->use_graphs;
+    if (overlap) {
+        for (int s = 0; s < pl->nstreams; ++s) {
+            if (!pl->pts_alt[s]) SESSD_CUDA(cudaMalloc(&pl->pts_alt[s], (size_t)pl->batch * pl->max_points * 16));
+            if (!pl->sizes_alt[s])
+                SESSD_CUDA(cudaMalloc(reinterpret_cast<void**>(&pl->sizes_alt[s]), (size_t)pl->batch * 4));
+            if (host_dense && pl->dense_bytes && !pl->dense_alt[s])
+                SESSD_CUDA(cudaMalloc(&pl->dense_alt[s], pl->dense_bytes));
+        }
+    }
     SESSD_CUDA(cudaEventRecord(pl->start, pl->streams[0]));
     for (int s = 1; s < pl->nstreams; ++s) SESSD_CUDA(cudaStreamWaitEvent(pl->streams[s], pl->start, 0));
+    if (overlap) SESSD_CUDA(cudaStreamWaitEvent(pl->h2d, pl->start, 0));
     // a slot's status word collects the conditions of all its groups of this run
     for (int s = 0; s < pl->nstreams; ++s) SESSD_CUDA(cudaMemsetAsync(pl->ws[s], 0, 4, pl->streams[s]));
     int group = 0;
@@ -936,7 +987,27 @@ static int pipeline_run(sessd_pipeline* pl, const void* points, const int32_t* s
         cudaStream_t st = pl->streams[s];
         const void* dpts;
         const int32_t* dsizes;
-        if (host) {
+        const int half = overlap ? (group / pl->nstreams) & 1 : 0;
+        const int slot2 = 2 * s + half;
+        void* dense_s = pl->dense[s];
+        if (overlap) {
+            // copy in on the input stream once the group that used this half before (two slot turns back) has run
+            void* in_pts = half ? pl->pts_alt[s] : pl->pts[s];
+            int32_t* in_sizes = half ? pl->sizes_alt[s] : pl->sizes[s];
+            SESSD_CUDA(cudaStreamWaitEvent(pl->h2d, pl->in_free[slot2], 0));
+            SESSD_CUDA(cudaMemcpyAsync(in_pts, static_cast<const char*>(points) + (size_t)f0 * frame_bytes,
+                                       (size_t)nb * frame_bytes, cudaMemcpyHostToDevice, pl->h2d));
+            SESSD_CUDA(cudaMemcpyAsync(in_sizes, sizes + f0, (size_t)nb * 4, cudaMemcpyHostToDevice, pl->h2d));
+            SESSD_CUDA(cudaEventRecord(pl->in_ready[slot2], pl->h2d));
+            SESSD_CUDA(cudaStreamWaitEvent(st, pl->in_ready[slot2], 0));
+            dpts = in_pts;
+            dsizes = in_sizes;
+            if (host_dense && pl->dense_bytes) {
+                // the BEV buffer of this half must have been copied out (its previous group's copy)
+                if (half) dense_s = pl->dense_alt[s];
+                SESSD_CUDA(cudaStreamWaitEvent(st, pl->bev_out[slot2], 0));
+            }
+        } else if (host) {
             SESSD_CUDA(cudaMemcpyAsync(pl->pts[s], static_cast<const char*>(points) + (size_t)f0 * frame_bytes,
                                        (size_t)nb * frame_bytes, cudaMemcpyHostToDevice, st));
             SESSD_CUDA(cudaMemcpyAsync(pl->sizes[s], sizes + f0, (size_t)nb * 4, cudaMemcpyHostToDevice, st));
@@ -983,11 +1054,13 @@ static int pipeline_run(sessd_pipeline* pl, const void* points, const int32_t* s
             SESSD_CUDA(cudaGraphLaunch(pl->graphs[s], st));
             g_launches.fetch_add(pl->graph_kernels[s], std::memory_order_relaxed);
         } else {
-            rc = backbone_enqueue_impl(bb, nb, pl->max_points, dpts, dsizes, pl->dense[s], pl->ws[s], pl->ws_bytes, st, false,
+            rc = backbone_enqueue_impl(bb, nb, pl->max_points, dpts, dsizes, dense_s, pl->ws[s], pl->ws_bytes, st, false,
                                        true);
             if (rc) return rc;
             if (nb == pl->batch) pl->warmed[s] = 1;
         }
+        pl->last_half[s] = dense_s == pl->dense[s] ? 0 : 1;
+        if (overlap) SESSD_CUDA(cudaEventRecord(pl->in_free[slot2], st));
         if (host && (host_voxel_num || host_status)) {
             void *feat, *coors, *num;
             rc = sessd_backbone_layer_view(bb, nb, pl->max_points, pl->ws[s], last_layer, &feat, &coors, &num);
@@ -1001,9 +1074,23 @@ static int pipeline_run(sessd_pipeline* pl, const void* points, const int32_t* s
             // the group's BEV maps go to the host region of its stream slot (a consumer takes them from there
             // before the slot's next group lands)
             const size_t per_frame = pl->dense_bytes / pl->batch;
-            SESSD_CUDA(cudaMemcpyAsync(static_cast<char*>(host_dense) + (size_t)s * pl->dense_bytes, pl->dense[s],
-                                       (size_t)nb * per_frame, cudaMemcpyDeviceToHost, st));
+            if (overlap) {
+                // on the output stream, behind the group; the slot's stream goes on with its next group
+                SESSD_CUDA(cudaEventRecord(pl->done[s], st));
+                SESSD_CUDA(cudaStreamWaitEvent(pl->d2h, pl->done[s], 0));
+                SESSD_CUDA(cudaMemcpyAsync(static_cast<char*>(host_dense) + (size_t)s * pl->dense_bytes, dense_s,
+                                           (size_t)nb * per_frame, cudaMemcpyDeviceToHost, pl->d2h));
+                SESSD_CUDA(cudaEventRecord(pl->bev_out[slot2], pl->d2h));
+            } else {
+                SESSD_CUDA(cudaMemcpyAsync(static_cast<char*>(host_dense) + (size_t)s * pl->dense_bytes, dense_s,
+                                           (size_t)nb * per_frame, cudaMemcpyDeviceToHost, st));
+            }
         }
+    }
+    if (overlap && host_dense && pl->dense_bytes) {
+        // the run ends when the last BEV copies have landed: every slot's stream waits for the output stream
+        SESSD_CUDA(cudaEventRecord(pl->bev_all, pl->d2h));
+        for (int s = 0; s < pl->nstreams; ++s) SESSD_CUDA(cudaStreamWaitEvent(pl->streams[s], pl->bev_all, 0));
     }
     float worst = 0.f;
     for (int s = 0; s < pl->nstreams; ++s) SESSD_CUDA(cudaEventRecord(pl->done[s], pl->streams[s]));

@@ -395,6 +395,54 @@ def test_pipeline_groups_equal_direct_backbone_runs(gpu, graphs):
     bb.close()
 
 
+def test_pipeline_host_runs_reuse_both_input_and_bev_buffers(gpu):
+    """Eleven frames in groups of two on two stream slots: every slot takes three groups, so that the copy-in
+    of a group waits for the group that used the same input buffer two turns earlier and the BEV buffer of a
+    group waits for the copy-out of its previous contents. Two runs in a row (the second starts with the
+    events the first one left); voxel counts of every frame and the BEV maps of the last group of each slot
+    must equal direct backbone runs."""
+    import torch
+
+    case = mk.small_case(gpu)
+    bb = gpu.Backbone(case["max_voxels"], case["weights"], case["scale"], case["shift"], dtype=1,
+                      layers=case["layers"], point_range=case["range"], voxel_size=case["voxel"])
+    P, F, B = len(case["points"]), 11, 2
+    rng = np.random.default_rng(11)
+    host_pts = torch.zeros((F, P, 4), dtype=torch.float32).pin_memory()
+    host_sizes = torch.zeros((F,), dtype=torch.int32).pin_memory()
+    vnum = torch.zeros((F,), dtype=torch.int32).pin_memory()
+    status = torch.zeros((F,), dtype=torch.int32).pin_memory()
+    pipe = gpu.Pipeline(bb, B, P, nstreams=2)
+    last = len(bb.layers) - 1
+    for rep in range(2):
+        for f in range(F):
+            n = int(rng.integers(P // 3, P + 1))
+            host_pts[f].zero_()
+            host_pts[f, :n] = torch.from_numpy(case["points"][rng.permutation(P)[:n]])
+            host_sizes[f] = n
+        want_dense, want_num = [], []
+        for f in range(F):
+            d, ws = bb.run(host_pts[f:f + 1].cuda(), host_sizes[f:f + 1].cuda())
+            torch.cuda.synchronize()
+            want_dense.append(d[0].clone())
+            want_num.append(int(bb.layer_view(ws, 1, P, last)[2][0]))
+        host_dense = torch.zeros((2, B) + tuple(want_dense[0].shape), dtype=torch.float16).pin_memory()
+        vnum.fill_(-1)
+        status.fill_(-1)
+        pipe.run_host_bev(host_pts, host_sizes, vnum, status, host_dense)
+        assert vnum.tolist() == want_num and status.tolist() == [0] * F
+        # groups 0..5 ran on slots 0,1,0,1,0,1: slot 0 ends with frames 8,9 and slot 1 with the partial group (frame 10)
+        assert torch.equal(host_dense[0, 0], want_dense[8].cpu()) and torch.equal(host_dense[0, 1], want_dense[9].cpu())
+        assert torch.equal(host_dense[1, 0], want_dense[10].cpu())
+        assert torch.equal(pipe.dense(0)[0], want_dense[8]) and torch.equal(pipe.dense(1)[0], want_dense[10])
+        vnum.fill_(-1)
+        pipe.run_host(host_pts, host_sizes, vnum, status)
+        assert vnum.tolist() == want_num and status.tolist() == [0] * F
+        assert torch.equal(pipe.dense(0)[1], want_dense[9]) and torch.equal(pipe.dense(1)[0], want_dense[10])
+    pipe.close()
+    bb.close()
+
+
 @pytest.mark.parametrize("dtype", [0, 1])
 def test_sparse2dense_plugin_entry(gpu, oracle, dtype):
     import torch
