@@ -15,7 +15,10 @@
 // One persistent CTA per SM; every role has warps of its own and walks the same sequence of groups:
 //   warps 0-3    epilogue (warp w reads tensor-memory lanes 32w .. 32w+31). The accumulators are double
 //                buffered (2 sets x 4 tiles x Cout columns), so the epilogue of one group runs while the
-//                other roles are already working on the next group.
+//                other roles are already working on the next group. A thread holds one row; the rows go
+//                through a small staging area of the warp, so that a store instruction writes whole 32- or
+//                64-byte runs of 8 or 16 rows instead of one 16-byte piece of 32 rows (those piecemeal
+//                stores alone were an eighth of the kernel's time).
 //   warps 4-7    MMA issuers; issuer t owns tile t of every group. The warp works out the group's schedule
 //                once (lane g for stage g) and walks it together; one elected lane issues the tcgen05.mma and
 //                commit instructions (each costs its thread on the order of a hundred cycles, so four share).
@@ -25,7 +28,7 @@
 //   warps 10..   gather. The A ring has one 16 KB slot per gather warp: item q (the q-th (tile, stage) pair
 //                of the CTA's life) lives in slot q % NSLOT and is filled by warp q % NSLOT alone with
 //                sixteen-byte cp.async copies that publish the slot themselves (mbarrier arrival of the
-//                copies). With 10-11 slots in flight the latency chain of one slot (issue, landing, MMA,
+//                copies). With ten slots in flight the latency chain of one slot (issue, landing, MMA,
 //                commit) is covered and no barrier is shared between gather warps.
 // Every barrier has one waiting role that sees each of its phases in order (a parity wait is only safe
 // then): a_full exists per (issuer, slot); index block j is always read by gather warp j % NSLOT.
@@ -59,12 +62,12 @@ constexpr int A_BYTES = TILE_M * ROW_BYTES;  // 16 KB
 constexpr int KVOL_MAX = 27;
 constexpr long long WAIT_LIMIT_CYCLES = 200000000LL;   // about a tenth of a second; real waits are microseconds
 
-// Gather slots (= gather warps): as many as fit beside the weight ring and the index blocks.
+// Gather slots (= gather warps): as many as fit beside the weight ring, the index blocks and the epilogue's staging area.
 // The index ring is deeper than the A ring (index rows come from DRAM, several microseconds away under load):
 // block j = q % NIDX, with NIDX a multiple of NSLOT so that block j is always read by gather warp j % NSLOT.
 template <int CIN>
 struct Ring {
-    static constexpr int NSLOT = CIN == 64 ? 11 : 10;
+    static constexpr int NSLOT = 10;
     static constexpr int NIDX = (CIN == 16 ? 2 : 3) * NSLOT;
     static constexpr int THREADS = (FIRST_GATHER_WARP + NSLOT) * 32;
 };
@@ -231,10 +234,17 @@ struct SharedCtl {
     uint32_t idx_uses[NIDX_MAX];             // bulk copies issued into index block j so far (for the abort path)
 };
 
+// Epilogue staging: every epilogue warp owns room for its 32 rows of one column block (up to 32 channels), so that
+// the rows leave for global memory as whole 32- or 64-byte runs instead of one 16-byte piece per row and store.
+template <int COUT>
+__host__ __device__ constexpr int stage_row_bytes() { return (COUT < 32 ? COUT : 32) * 2; }
+template <int COUT>
+__host__ __device__ constexpr int stage_bytes() { return EPI_WARPS * 32 * stage_row_bytes<COUT>(); }
+
 template <int CIN, int COUT>
 constexpr int umma_smem_bytes() {
     return 1024 /*alignment slack*/ + Ring<CIN>::NSLOT * A_BYTES + B_STAGES * COUT * ROW_BYTES +
-           Ring<CIN>::NIDX * (64 / CIN) * TILE_M * 4 + 2 * COUT * 4 + (int)sizeof(SharedCtl);
+           Ring<CIN>::NIDX * (64 / CIN) * TILE_M * 4 + stage_bytes<COUT>() + 2 * COUT * 4 + (int)sizeof(SharedCtl);
 }
 
 // Offsets g*KG .. g*KG+KG-1 of a tile's 27-bit offset mask.
@@ -303,7 +313,8 @@ conv_umma_kernel(const __half* __restrict__ in, __half* __restrict__ out, const 
     uint8_t* sA = smem;
     uint8_t* sB = sA + NSLOT * A_BYTES;
     int32_t* s_idx = reinterpret_cast<int32_t*>(sB + B_STAGES * B_BYTES);
-    float* s_scale = reinterpret_cast<float*>(s_idx + NIDX * IDX_WORDS);
+    uint8_t* s_stage = reinterpret_cast<uint8_t*>(s_idx + NIDX * IDX_WORDS);
+    float* s_scale = reinterpret_cast<float*>(s_stage + stage_bytes<COUT>());
     float* s_shift = s_scale + COUT;
     SharedCtl* ctl = reinterpret_cast<SharedCtl*>(s_shift + COUT);
 
@@ -574,13 +585,16 @@ conv_umma_kernel(const __half* __restrict__ in, __half* __restrict__ out, const 
             }
             // Column blocks of CB channels keep the register footprint small.
             constexpr int CB = COUT < 32 ? COUT : 32;
+            constexpr int RB = stage_row_bytes<COUT>();   // bytes of a row's column block
+            constexpr int CPR = RB / 16;                  // 16-byte chunks per row and block: 4 or 2
+            uint8_t* stage = s_stage + warp * (32 * RB);
+            auto stage_swz = [](int r) { return RB == 64 ? (r >> 1) & 3 : (r >> 2) & 1; };
 #pragma unroll 1
             for (int t2 = 0; t2 < cnt; ++t2) {
                 const int row = row0 + t2 * TILE_M + tid;
                 const uint32_t m_t2 = t2 == 0 ? m[0] : (t2 == 1 ? m[1] : (t2 == 2 ? m[2] : m[3]));
                 const bool have = any && got && m_t2;
                 const bool store = got && row < n;
-                __half* dst = out + ((size_t)b * max_voxels + row) * COUT;
                 __half* d = nullptr;
                 if (dense && store) {
                     // fused BEV scatter (sparse2Dense.cu:201-206): channel c*D + z, pixel (y, x)
@@ -603,7 +617,8 @@ conv_umma_kernel(const __half* __restrict__ in, __half* __restrict__ out, const 
 #pragma unroll
                         for (int j = 0; j < CB; ++j) acc[j] = 0.f;
                     }
-                    if (!store) continue;
+                    // Every lane packs its row's block into the warp's staging area (16-byte chunks XOR-swizzled by
+                    // row so that neither the writes nor the reads below meet in a bank) ...
 #pragma unroll
                     for (int c0 = 0; c0 < CB; c0 += 8) {
                         uint4 pk;
@@ -622,7 +637,7 @@ conv_umma_kernel(const __half* __restrict__ in, __half* __restrict__ out, const 
                             }
                             h[j] = __floats2half2_rn(v0, v1);
                         }
-                        *reinterpret_cast<uint4*>(dst + cb + c0) = pk;
+                        *reinterpret_cast<uint4*>(stage + lane * RB + (((c0 >> 3) ^ stage_swz(lane)) << 4)) = pk;
                         if (d) {
 #pragma unroll
                             for (int j = 0; j < 4; ++j) {
@@ -631,6 +646,20 @@ conv_umma_kernel(const __half* __restrict__ in, __half* __restrict__ out, const 
                             }
                         }
                     }
+                    __syncwarp();
+                    // ... and the warp copies the block out with CPR lanes per row: each store instruction writes
+                    // 32 / CPR rows as whole runs of RB bytes.
+                    if (got) {
+#pragma unroll
+                        for (int i = 0; i < CPR; ++i) {
+                            const int rr = lane / CPR + i * (32 / CPR), cc = lane % CPR;
+                            const uint4 v = *reinterpret_cast<const uint4*>(stage + rr * RB + ((cc ^ stage_swz(rr)) << 4));
+                            const int grow = row0 + t2 * TILE_M + warp * 32 + rr;
+                            if (grow < n)
+                                *reinterpret_cast<uint4*>(out + ((size_t)b * max_voxels + grow) * COUT + cb + cc * 8) = v;
+                        }
+                    }
+                    __syncwarp();
                 }
             }
             if (any && got) {
