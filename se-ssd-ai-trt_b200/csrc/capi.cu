@@ -395,6 +395,10 @@ int sessd_conv_weights_create(const sessd_conv_params* p, const float* weights, 
             e = cudaMemset(w->impl.shift, 0, p->out_channel * 4);
         if (e != cudaSuccess) return fail(e, "cudaMemcpy(shift)");
     }
+    for (int c = 0; c < 64; ++c) {
+        w->impl.host_scale[c] = (scale && c < p->out_channel) ? scale[c] : 1.f;
+        w->impl.host_shift[c] = (scale && shift && c < p->out_channel) ? shift[c] : 0.f;
+    }
     if (dtype == SESSD_F16 && conv_umma_supported(p->in_channel, p->out_channel)) {
         rc = conv_umma_pack_weights(weights, g.kvol, p->in_channel, p->out_channel, &w->impl.umma_w);
         if (rc) {
@@ -495,6 +499,8 @@ static int conv_enqueue_common(const sessd_conv_params* p, const sessd_conv_weig
     c.dtype = w->impl.dtype;
     c.status = ws.status;
     c.debug_withhold_weights = w->impl.debug_withhold;
+    c.scale_host = w->impl.host_scale;
+    c.shift_host = w->impl.host_shift;
     rc = choose_conv(c, stream);
     if (rc) return rc;
     // Rows past the active count are zero in the reference (outputs are memset, submConv3dlayer.cu:594).
@@ -762,6 +768,8 @@ static int backbone_enqueue_impl(const sessd_backbone* bb, int batch, int max_po
         c.dtype = bb->dtype;
         c.status = w.status;
         c.debug_withhold_weights = L.w->impl.debug_withhold;
+        c.scale_host = L.w->impl.host_scale;
+        c.shift_host = L.w->impl.host_shift;
         if (bb->has_s2d && i + 1 == bb->layers.size()) {
             // The padded plane is (top + H + bottom) x (left + W + right); starting the scatter (top, left)
             // into it folds the reference's ZeroPad2dPlugin (zeroPad2d.cu:192-198) into this epilogue.

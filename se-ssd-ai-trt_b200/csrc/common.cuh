@@ -283,6 +283,8 @@ struct ConvLaunch {
     int D, H, W;
     int32_t* status;       // device status word (tensor-core path reports wait timeouts there)
     int debug_withhold_weights;   // tests only: the tensor-core kernel's weight streamer stays silent (waits run out)
+    const float* scale_host;      // [Cout <= 64] host copies of scale / shift (ones / zeros without batch norm), or null
+    const float* shift_host;
 };
 int launch_conv_simt(const ConvLaunch& c, cudaStream_t stream);
 bool conv_simt_supported(int cin, int cout);
@@ -323,6 +325,9 @@ struct sessd_conv_weights_impl {
     float* shift;   // device or null
     int relu, dtype, kvol, cin, cout;
     int debug_withhold;   // tests of the time-out path: the tensor-core kernel's weight streamer stays silent
+    // host copies of scale and shift (ones and zeros without batch norm) for kernels that take them as launch
+    // parameters; filled for out_channel <= 64
+    float host_scale[64], host_shift[64];
 };
 
 }  // namespace sessd

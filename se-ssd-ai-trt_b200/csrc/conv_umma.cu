@@ -38,6 +38,7 @@
 // work, waits for its own copies and MMAs, frees its tensor memory and returns.
 #include <atomic>
 #include <cstdlib>
+#include <cstring>
 #include <string>
 #include <vector>
 
@@ -135,13 +136,15 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
 __device__ __forceinline__ void cp_async_16(uint32_t dst, const void* src, uint32_t src_bytes) {
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
 }
-// 16-byte copy that writes zeros instead when index < 0 (the source address is then not touched).
-__device__ __forceinline__ void cp_async_16_or_zero(uint32_t dst, const void* src, int index) {
+// 16-byte copy that writes zeros instead when index < 0 (the source address is then not touched), and
+// nothing at all when `was_zero` is set as well: the destination still holds the zeros an earlier copy wrote.
+__device__ __forceinline__ void cp_async_16_or_zero_once(uint32_t dst, const void* src, int index, uint32_t was_zero) {
     asm volatile(
-        "{\n\t.reg .pred p;\n\t"
+        "{\n\t.reg .pred p, q;\n\t"
         "setp.lt.s32 p, %2, 0;\n\t"
-        "cp.async.cg.shared.global [%0], [%1], 16, p;\n\t}" ::"r"(dst),
-        "l"(src), "r"(index)
+        "setp.ne.and.b32 q, %3, 0, p;\n\t"
+        "@!q cp.async.cg.shared.global [%0], [%1], 16, p;\n\t}" ::"r"(dst),
+        "l"(src), "r"(index), "r"(was_zero)
         : "memory");
 }
 // Arrival on `bar` that fires when all cp.async copies this thread has issued so far have landed
@@ -208,6 +211,17 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
         : "r"(taddr)
         : "memory");
 }
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,"
+        "%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+          "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+          "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr)
+        : "memory");
+}
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
 struct SharedCtl {
@@ -244,7 +258,7 @@ __host__ __device__ constexpr int stage_bytes() { return EPI_WARPS * 32 * stage_
 template <int CIN, int COUT>
 constexpr int umma_smem_bytes() {
     return 1024 /*alignment slack*/ + Ring<CIN>::NSLOT * A_BYTES + B_STAGES * COUT * ROW_BYTES +
-           Ring<CIN>::NIDX * (64 / CIN) * TILE_M * 4 + stage_bytes<COUT>() + 2 * COUT * 4 + (int)sizeof(SharedCtl);
+           Ring<CIN>::NIDX * (64 / CIN) * TILE_M * 4 + stage_bytes<COUT>() + (int)sizeof(SharedCtl);
 }
 
 // Offsets g*KG .. g*KG+KG-1 of a tile's 27-bit offset mask.
@@ -286,14 +300,34 @@ __device__ __forceinline__ bool next_item(const uint32_t (&m)[TILES], int nstage
     return true;
 }
 
+// Folded batch-norm scale and shift of the layer as launch parameters: the epilogue's multiply-adds then take them
+// straight from the constant bank (its column loops are unrolled, so every index is a constant), where the
+// earlier shared-memory copies cost two loads per channel pair and row on the pipe the gather copies keep busy.
+struct EpiConst {
+    float scale[64];
+    float shift[64];
+};
+
+// Lane g holds `bits`, the tiles with work under stage g. Returns the number of (tile, stage) items of the stages
+// before g and, in blocks_before, the number of those stages that have any work. Five warp votes: a vote answers
+// in a few cycles, while a shuffle scan (five to ten shuffles, each a trip through the shared-memory pipe that the
+// gather copies keep busy) cost every role some thousand cycles at each group boundary.
+__device__ __forceinline__ int items_before_stage(uint32_t bits, int lane, int* blocks_before = nullptr) {
+    const uint32_t lt = (1u << lane) - 1u;
+    int items = 0;
+#pragma unroll
+    for (int t = 0; t < TILES; ++t) items += __popc(__ballot_sync(0xFFFFFFFFu, (bits >> t) & 1u) & lt);
+    if (blocks_before) *blocks_before = __popc(__ballot_sync(0xFFFFFFFFu, bits != 0u) & lt);
+    return items;
+}
 
 template <int CIN, int COUT>
 __global__ void __launch_bounds__(Ring<CIN>::THREADS, 1)
 conv_umma_kernel(const __half* __restrict__ in, __half* __restrict__ out, const int32_t* __restrict__ nbr,
                  const uint32_t* __restrict__ tile_mask, const int32_t* __restrict__ out_num,
-                 const uint8_t* __restrict__ wtiles, const float* __restrict__ scale, const float* __restrict__ shift,
-                 int relu, int batch, int max_voxels, int kvol, __half* __restrict__ dense,
-                 const int4* __restrict__ out_coors, int D, int H, int W, int32_t* status, int withhold_weights) {
+                 const uint8_t* __restrict__ wtiles, const __grid_constant__ EpiConst epi, int relu, int batch,
+                 int max_voxels, int kvol, __half* __restrict__ dense, const int4* __restrict__ out_coors, int D, int H,
+                 int W, int32_t* status, int withhold_weights) {
     // withhold_weights (tests of the time-out path only): the weight streamer stays silent, so the MMA issuers'
     // bounded wait for the first weight block runs out and every CTA with work leaves through the abort path.
     constexpr int KG = 64 / CIN;            // kernel offsets sharing one 128-byte A row
@@ -314,9 +348,7 @@ conv_umma_kernel(const __half* __restrict__ in, __half* __restrict__ out, const 
     uint8_t* sB = sA + NSLOT * A_BYTES;
     int32_t* s_idx = reinterpret_cast<int32_t*>(sB + B_STAGES * B_BYTES);
     uint8_t* s_stage = reinterpret_cast<uint8_t*>(s_idx + NIDX * IDX_WORDS);
-    float* s_scale = reinterpret_cast<float*>(s_stage + stage_bytes<COUT>());
-    float* s_shift = s_scale + COUT;
-    SharedCtl* ctl = reinterpret_cast<SharedCtl*>(s_shift + COUT);
+    SharedCtl* ctl = reinterpret_cast<SharedCtl*>(s_stage + stage_bytes<COUT>());
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int nstages = (kvol + KG - 1) / KG;
@@ -346,10 +378,6 @@ conv_umma_kernel(const __half* __restrict__ in, __half* __restrict__ out, const 
         ctl->abort_where = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    for (int c = tid; c < COUT; c += THREADS) {
-        s_scale[c] = scale ? scale[c] : 1.f;
-        s_shift[c] = (scale && shift) ? shift[c] : 0.f;
-    }
     const int tiles_per_frame = (max_voxels + TILE_M - 1) / TILE_M;
     if (warp == EPI_WARPS) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&ctl->tmem_base)),
@@ -367,6 +395,7 @@ conv_umma_kernel(const __half* __restrict__ in, __half* __restrict__ out, const 
     uint32_t a_it = 0, b_it = 0, acc_it = 0;  // items, weight blocks and accumulator sets used so far; every role advances them identically
     uint32_t full_phase = 0;                  // MMA issuers: bit s = parity of the next phase of their a_full[t][s]
     uint32_t b_issued = 0;                    // weight streamer: blocks whose bulk copy has been started
+    uint32_t zero_rows = 0;                   // gather warps: bit p = this lane's chunk of row p of its slot holds zeros
 
     // Balanced split: the occupied 128-row tiles of all frames, laid end to end, are cut into gridDim.x
     // contiguous ranges of equal work (row counts and tile masks are read from the device, so no host round
@@ -508,14 +537,7 @@ conv_umma_kernel(const __half* __restrict__ in, __half* __restrict__ out, const 
             uint8_t* list = ctl->stage_list[s];
             {
                 const uint32_t bits = lane < nstages ? active_tiles<KG>(m, lane) : 0u;
-                const int cnt_l = __popc(bits);
-                int incl = cnt_l;
-#pragma unroll
-                for (int d = 1; d < 32; d <<= 1) {
-                    const int v = __shfl_up_sync(0xFFFFFFFFu, incl, d);
-                    if (lane >= d) incl += v;
-                }
-                int at = incl - cnt_l;
+                int at = items_before_stage(bits, lane);
 #pragma unroll
                 for (int tt = 0; tt < TILES; ++tt)
                     if ((bits >> tt) & 1u) list[at++] = (uint8_t)((lane << 2) | tt);
@@ -555,11 +577,19 @@ conv_umma_kernel(const __half* __restrict__ in, __half* __restrict__ out, const 
                 const bool plain = g * KG + KG <= kvol && row0 + (t + 1) * TILE_M <= n;   // uniform over the warp
                 const __half* lane_base = in_b + csub;
                 if (plain) {
+                    // More than half of an item's rows are missing neighbours, and a third are missing in two
+                    // consecutive uses of the slot: their zeros are still there, so the copy is left out (the
+                    // shared-memory write of a zero row costs the same as that of a real one).
+                    uint32_t zero_now = 0;
 #pragma unroll
-                    for (int p = 0; p < 32; ++p)
-                        cp_async_16_or_zero(a_base + p * ROW_BYTES + ((c ^ (p & 7)) << 4),
-                                            lane_base + (ptrdiff_t)vv[p] * CIN, vv[p]);
+                    for (int p = 0; p < 32; ++p) {
+                        cp_async_16_or_zero_once(a_base + p * ROW_BYTES + ((c ^ (p & 7)) << 4),
+                                                 lane_base + (ptrdiff_t)vv[p] * CIN, vv[p], zero_rows & (1u << p));
+                        zero_now |= ((uint32_t)vv[p] >> 31) << p;
+                    }
+                    zero_rows = zero_now;
                 } else {
+                    zero_rows = 0;   // (the general path writes every row)
 #pragma unroll
                     for (int p = 0; p < 32; ++p) {
                         const int id = (k_ok && p < rows_left) ? vv[p] : -1;
@@ -601,16 +631,21 @@ conv_umma_kernel(const __half* __restrict__ in, __half* __restrict__ out, const 
                     const int4 c4 = __ldg(&out_coors[(size_t)b * max_voxels + row]);
                     d = dense + (size_t)b * COUT * D * H * W + ((size_t)c4.y * H + c4.z) * W + c4.w;
                 }
-#pragma unroll 1
+#pragma unroll
                 for (int cb = 0; cb < COUT; cb += CB) {
                     float acc[CB];
                     if (have) {
+                        const uint32_t taddr = tmem + ((uint32_t)(warp * 32) << 16) + set * SET_COLS + t2 * COUT + cb;
+                        if constexpr (CB == 32) {
+                            uint32_t r32[32];
+                            tmem_ld32(taddr, r32);
 #pragma unroll
-                        for (int c0 = 0; c0 < CB; c0 += 16) {
+                            for (int j = 0; j < 32; ++j) acc[j] = __uint_as_float(r32[j]);
+                        } else {
                             uint32_t r16[16];
-                            tmem_ld16(tmem + ((uint32_t)(warp * 32) << 16) + set * SET_COLS + t2 * COUT + cb + c0, r16);
+                            tmem_ld16(taddr, r16);
 #pragma unroll
-                            for (int j = 0; j < 16; ++j) acc[c0 + j] = __uint_as_float(r16[j]);
+                            for (int j = 0; j < 16; ++j) acc[j] = __uint_as_float(r16[j]);
                         }
                         tmem_ld_wait();
                     } else {
@@ -625,12 +660,9 @@ conv_umma_kernel(const __half* __restrict__ in, __half* __restrict__ out, const 
                         __half2* h = reinterpret_cast<__half2*>(&pk);
 #pragma unroll
                         for (int j = 0; j < 4; ++j) {
-                            // scale and shift of channels ch, ch+1 as two 8-byte shared-memory reads
-                            const int ch = cb + c0 + 2 * j;
-                            const float2 sc = *reinterpret_cast<const float2*>(&s_scale[ch]);
-                            const float2 sh = *reinterpret_cast<const float2*>(&s_shift[ch]);
-                            float v0 = fmaf(acc[c0 + 2 * j], sc.x, sh.x);
-                            float v1 = fmaf(acc[c0 + 2 * j + 1], sc.y, sh.y);
+                            const int ch = cb + c0 + 2 * j;   // a constant after unrolling
+                            float v0 = fmaf(acc[c0 + 2 * j], epi.scale[ch], epi.shift[ch]);
+                            float v1 = fmaf(acc[c0 + 2 * j + 1], epi.scale[ch + 1], epi.shift[ch + 1]);
                             if (relu) {
                                 v0 = v0 > 0.f ? v0 : 0.f;
                                 v1 = v1 > 0.f ? v1 : 0.f;
@@ -682,15 +714,10 @@ conv_umma_kernel(const __half* __restrict__ in, __half* __restrict__ out, const 
                 uint32_t info = 0;
                 {
                     const uint32_t bits = lane < nstages ? active_tiles<KG>(m, lane) : 0u;
-                    const int act = __popc(bits), blk = bits ? 1 : 0;
-                    int acts = act, blks = blk;   // inclusive scans over the stages
-#pragma unroll
-                    for (int d = 1; d < 32; d <<= 1) {
-                        const int va = __shfl_up_sync(0xFFFFFFFFu, acts, d), vb = __shfl_up_sync(0xFFFFFFFFu, blks, d);
-                        if (lane >= d) acts += va, blks += vb;
-                    }
-                    const uint32_t pos = a_it + (uint32_t)(acts - act) + (uint32_t)__popc(bits & ((1u << t) - 1u));
-                    const uint32_t my_b = b_it + (uint32_t)(blks - blk);
+                    int blocks_before = 0;
+                    const int items_before = items_before_stage(bits, lane, &blocks_before);
+                    const uint32_t pos = a_it + (uint32_t)items_before + (uint32_t)__popc(bits & ((1u << t) - 1u));
+                    const uint32_t my_b = b_it + (uint32_t)blocks_before;
                     info = (bits ? 1u : 0u) | (((bits >> t) & 1u) << 1) | ((my_b % B_STAGES) << 2) |
                            (((my_b / B_STAGES) & 1u) << 4) | ((pos % NSLOT) << 5) | (pos << 9);
                 }
@@ -748,14 +775,7 @@ conv_umma_kernel(const __half* __restrict__ in, __half* __restrict__ out, const 
                 uint8_t* list = ctl->idx_list;
                 {
                     const uint32_t bits = lane < nstages ? active_tiles<KG>(m, lane) : 0u;
-                    const int cnt_l = __popc(bits);
-                    int incl = cnt_l;
-#pragma unroll
-                    for (int d = 1; d < 32; d <<= 1) {
-                        const int v = __shfl_up_sync(0xFFFFFFFFu, incl, d);
-                        if (lane >= d) incl += v;
-                    }
-                    int at = incl - cnt_l;
+                    int at = items_before_stage(bits, lane);
 #pragma unroll
                     for (int tt = 0; tt < TILES; ++tt)
                         if ((bits >> tt) & 1u) list[at++] = (uint8_t)((lane << 2) | tt);
@@ -899,9 +919,13 @@ int launch_one(const ConvLaunch& c, cudaStream_t stream) {
         SESSD_CUDA(cudaFuncSetAttribute(conv_umma_kernel<CIN, COUT>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
         configured.fetch_or(bit, std::memory_order_release);
     }
+    if (!c.scale_host || !c.shift_host) return SESSD_ERR_PARAM;
+    EpiConst epi;
+    memcpy(epi.scale, c.scale_host, sizeof epi.scale);
+    memcpy(epi.shift, c.shift_host, sizeof epi.shift);
     SESSD_LAUNCH_NAMED(name.c_str(), (conv_umma_kernel<CIN, COUT>), persistent_grid(1), Ring<CIN>::THREADS, smem, stream,
                        static_cast<const __half*>(c.in), static_cast<__half*>(c.out), c.nbr, c.tile_mask, c.out_num,
-                       static_cast<const uint8_t*>(c.umma_weights), c.scale, c.shift, c.relu, c.batch, c.max_voxels,
+                       static_cast<const uint8_t*>(c.umma_weights), epi, c.relu, c.batch, c.max_voxels,
                        c.kvol, static_cast<__half*>(c.dense), reinterpret_cast<const int4*>(c.out_coors), c.D, c.H, c.W,
                        c.status, c.debug_withhold_weights);
     return SESSD_OK;
