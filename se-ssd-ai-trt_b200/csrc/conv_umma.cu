@@ -61,6 +61,9 @@ constexpr int B_STAGES = 3;                  // weight ring: a group needs up to
 constexpr int ROW_BYTES = 128;               // 64 halves per A/B row
 constexpr int A_BYTES = TILE_M * ROW_BYTES;  // 16 KB
 constexpr int KVOL_MAX = 27;
+// Words from one offset's 128 indices to the next offset's inside an index block: 16 bytes more than the indices
+// take, so that lanes reading different offsets of a stage (32- and 16-channel inputs) use different banks too.
+constexpr int TAP_WORDS = TILE_M + 4;
 constexpr long long WAIT_LIMIT_CYCLES = 200000000LL;   // about a tenth of a second; real waits are microseconds
 
 // Gather slots (= gather warps): as many as fit beside the weight ring, the index blocks and the epilogue's staging area.
@@ -258,7 +261,7 @@ __host__ __device__ constexpr int stage_bytes() { return EPI_WARPS * 32 * stage_
 template <int CIN, int COUT>
 constexpr int umma_smem_bytes() {
     return 1024 /*alignment slack*/ + Ring<CIN>::NSLOT * A_BYTES + B_STAGES * COUT * ROW_BYTES +
-           Ring<CIN>::NIDX * (64 / CIN) * TILE_M * 4 + stage_bytes<COUT>() + (int)sizeof(SharedCtl);
+           Ring<CIN>::NIDX * (64 / CIN) * TAP_WORDS * 4 + stage_bytes<COUT>() + (int)sizeof(SharedCtl);
 }
 
 // Offsets g*KG .. g*KG+KG-1 of a tile's 27-bit offset mask.
@@ -336,7 +339,7 @@ conv_umma_kernel(const __half* __restrict__ in, __half* __restrict__ out, const 
     constexpr int NSLOT = Ring<CIN>::NSLOT;
     constexpr int NIDX = Ring<CIN>::NIDX;
     constexpr int THREADS = Ring<CIN>::THREADS;
-    constexpr int IDX_WORDS = KG * TILE_M;  // one index block: KG offsets x 128 rows
+    constexpr int IDX_WORDS = KG * TAP_WORDS;  // one index block: KG offsets x 128 rows
     constexpr int IDX_BATCH = 16;           // items the index warp handles side by side (must stay below NIDX)
     constexpr int SET_COLS = TILES * COUT;  // accumulator columns of one set
     constexpr int TMEM_COLS = 2 * SET_COLS < 32 ? 32 : 2 * SET_COLS;
@@ -525,11 +528,14 @@ conv_umma_kernel(const __half* __restrict__ in, __half* __restrict__ out, const 
             // ---------------- gather producers ----------------
             // Gather warp s fills slot s with every NSLOT-th item and issues all of its copies: while one warp
             // sits in the latency of its barrier hand-offs the others keep the copy pipe busy.
-            // Lane = (row group j, 16-byte chunk c): the eight lanes j*8..j*8+7 copy rows 32j..32j+31 of the
-            // item, one row per step, chunk c of the row landing at chunk c ^ (row & 7) (128-byte swizzle).
+            // Lane = (row group j, 16-byte chunk c): the eight lanes j*8..j*8+7 copy, in step p, chunk c of row
+            // 32 (p / 8) + 8 j + p % 8 of the item to chunk c ^ (row & 7) of the slot's row (128-byte swizzle).
+            // With the rows of a group in runs of eight, the four groups' 16-byte index reads of one instruction
+            // lie 32 bytes apart (different banks: one pass), where runs of 32 rows put them 128 bytes apart
+            // (the same banks: four passes).
             const int s = warp - FIRST_GATHER_WARP;
             const int c = lane & 7;                // 16-byte chunk of the 128-byte row
-            const int jrow = (lane >> 3) * 32;     // first row of this lane group
+            const int jrow = (lane >> 3) * 8;      // first row of this lane group's first run of eight
             const int koff = c / CPO;              // offset of the stage's group this chunk belongs to
             const int csub = (c % CPO) * 8;        // first channel of the chunk
             const __half* in_b = in + (size_t)b * max_voxels * CIN;
@@ -544,7 +550,7 @@ conv_umma_kernel(const __half* __restrict__ in, __half* __restrict__ out, const 
                 __syncwarp();
             }
             const int first = (s + NSLOT - (int)(a_it % NSLOT)) % NSLOT;
-            const uint32_t idx_lane = smem_u32(&s_idx[koff * TILE_M + jrow]);
+            const uint32_t idx_lane = smem_u32(&s_idx[koff * TAP_WORDS + jrow]);
             const uint32_t a_base = smem_u32(sA + s * A_BYTES) + jrow * ROW_BYTES;
             for (int e = first; e < n_a; e += NSLOT) {
                 const uint32_t q = a_it + (uint32_t)e;
@@ -564,12 +570,12 @@ conv_umma_kernel(const __half* __restrict__ in, __half* __restrict__ out, const 
                     int4 v;
                     asm volatile("ld.shared.v4.s32 {%0,%1,%2,%3}, [%4];"
                                  : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
-                                 : "r"(idx_base + 16 * w4));
+                                 : "r"(idx_base + 128 * (w4 >> 1) + 16 * (w4 & 1)));   // rows 32 (w4 / 2) + 8 j + 4 (w4 % 2) ..
                     vv[4 * w4] = v.x, vv[4 * w4 + 1] = v.y, vv[4 * w4 + 2] = v.z, vv[4 * w4 + 3] = v.w;
                 }
                 if (!mbar_wait(smem_u32(&ctl->a_empty[s]), use ^ 1u, abort_flag, 2 | (int)(q << 4))) break;
                 const bool k_ok = g * KG + koff < kvol;
-                const int rows_left = n - (row0 + t * TILE_M + jrow);   // rows of this lane group inside the frame
+                const int rows_left = n - (row0 + t * TILE_M + jrow);   // step p's row lies inside the frame when 32 (p / 8) + p % 8 < rows_left
                 // Every instruction of this loop is on the critical path of the item, so the common case - all
                 // offsets of the stage exist and the whole tile lies inside the frame - takes three instructions
                 // per row: a predicate from the sign of the index, the address, and a copy that writes zeros when
@@ -583,7 +589,7 @@ conv_umma_kernel(const __half* __restrict__ in, __half* __restrict__ out, const 
                     uint32_t zero_now = 0;
 #pragma unroll
                     for (int p = 0; p < 32; ++p) {
-                        cp_async_16_or_zero_once(a_base + p * ROW_BYTES + ((c ^ (p & 7)) << 4),
+                        cp_async_16_or_zero_once(a_base + (32 * (p >> 3) + (p & 7)) * ROW_BYTES + ((c ^ (p & 7)) << 4),
                                                  lane_base + (ptrdiff_t)vv[p] * CIN, vv[p], zero_rows & (1u << p));
                         zero_now |= ((uint32_t)vv[p] >> 31) << p;
                     }
@@ -592,9 +598,10 @@ conv_umma_kernel(const __half* __restrict__ in, __half* __restrict__ out, const 
                     zero_rows = 0;   // (the general path writes every row)
 #pragma unroll
                     for (int p = 0; p < 32; ++p) {
-                        const int id = (k_ok && p < rows_left) ? vv[p] : -1;
+                        const int id = (k_ok && 32 * (p >> 3) + (p & 7) < rows_left) ? vv[p] : -1;
                         const __half* src = in_b + (size_t)(id < 0 ? 0 : id) * CIN + csub;
-                        cp_async_16(a_base + p * ROW_BYTES + ((c ^ (p & 7)) << 4), src, id < 0 ? 0u : 16u);
+                        cp_async_16(a_base + (32 * (p >> 3) + (p & 7)) * ROW_BYTES + ((c ^ (p & 7)) << 4), src,
+                                    id < 0 ? 0u : 16u);
                     }
                 }
                 // The index block may be refilled now: every index has been consumed by a copy above (the arrival
@@ -803,7 +810,7 @@ conv_umma_kernel(const __half* __restrict__ in, __half* __restrict__ out, const 
                             ctl->idx_uses[j] = q / NIDX + 1u;
                             mbar_arrive_expect_tx(bar, (uint32_t)(nk * rows * 4));
                             for (int jj = 0; jj < nk; ++jj)
-                                bulk_load(smem_u32(&s_idx[j * IDX_WORDS + jj * TILE_M]),
+                                bulk_load(smem_u32(&s_idx[j * IDX_WORDS + jj * TAP_WORDS]),
                                           nbr_b + (size_t)(g * KG + jj) * max_voxels + row, (uint32_t)(rows * 4), bar);
                         }
                     }
@@ -828,7 +835,7 @@ conv_umma_kernel(const __half* __restrict__ in, __half* __restrict__ out, const 
                             const bool in_range = k < kvol && row < max_voxels;
                             const int32_t* src = nbr_b + (in_range ? (size_t)k * max_voxels + row : 0);
                             asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;" ::"r"(
-                                             smem_u32(&s_idx[j * IDX_WORDS + jj * TILE_M + r])),
+                                             smem_u32(&s_idx[j * IDX_WORDS + jj * TAP_WORDS + r])),
                                          "l"(src), "r"(in_range ? 4u : 0u)
                                          : "memory");
                         }
