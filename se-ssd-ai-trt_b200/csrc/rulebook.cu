@@ -308,48 +308,77 @@ __device__ __forceinline__ unsigned long long rec_bits(const uint4& r) {
     return (unsigned long long)r.x | ((unsigned long long)r.y << 32);
 }
 
-// Marks the candidate outputs of every input row. Thread = (input row i, candidate e), where
-// e = (cz * span_max_y + cy) * span_max_x + cx walks the row's candidate box from its upper corner downward:
-// the reference's enumeration (sparseConv3dlayer.cu:339-383). A bit that is already set is not set again,
-// so most threads finish with one L2 read.
+// Marks the candidate outputs of every input row: the reference's enumeration (sparseConv3dlayer.cu:339-383),
+// one thread per input row. Per axis the row has up to three candidate output positions (one or two for the
+// stride-2 layers); the x candidates of one (z, y) pair are neighbouring bits, mostly of one 64-bit word, so
+// they are tested and set together, and all words are read before any is updated (the reads are independent;
+// most of them find their bits already set by a neighbouring row and nothing is written).
 __global__ void __launch_bounds__(kThreads)
 mark_outputs_kernel(const int4* __restrict__ in_coors, const int32_t* __restrict__ in_num, int batch, int max_voxels,
                     ConvGeom g, BitGrid out) {
-    const int64_t per_frame = (int64_t)max_voxels * g.ncand;
-    const int chunks = (int)((per_frame + kThreads - 1) / kThreads);
+    constexpr int MAXS = 3;   // span_max never exceeds the kernel size (<= 3)
+    const int chunks = (max_voxels + kThreads - 1) / kThreads;
     const int items = batch * chunks;
     for (int it = blockIdx.x; it < items; it += gridDim.x) {
         const int b = it / chunks;
-        const int t = (it - b * chunks) * kThreads + threadIdx.x;
+        const int i0 = (it - b * chunks) * kThreads;
         int n = in_num[b];
         n = n > max_voxels ? max_voxels : n;
-        if ((it - b * chunks) * kThreads >= n * g.ncand) continue;   // uniform over the block
-        if (t >= n * g.ncand) continue;
-        const int i = g.cand_shift >= 0 ? (t >> g.cand_shift) : t / g.ncand;
-        const int e = t - i * g.ncand;
-        int cz, cy, cx, rest;
-        split_small(e, g.span_max[2], &rest, &cx);
-        split_small(rest, g.span_max[1], &cz, &cy);
+        if (i0 >= n) continue;   // uniform over the block
+        const int i = i0 + threadIdx.x;
+        if (i >= n) continue;
         const int4 c4 = __ldg(&in_coors[(size_t)b * max_voxels + i]);
         const int c[3] = {c4.y, c4.z, c4.w};
-        const int cj[3] = {cz, cy, cx};
-        int o[3];
-        bool ok = true;
+        // candidate positions per axis, upper corner downward; pos[j][e] < 0 marks an unusable candidate
+        int pos[3][MAXS];
+        bool in_ok = true;
 #pragma unroll
         for (int j = 0; j < 3; ++j) {
             // C integer division, as in the reference (sparseConv3dlayer.cu:339-348); dilation is 1
             const int lo = div_trunc(c[j] - (g.K[j] - 1) - 1 + g.S[j] + g.P[j], g.S[j]);
             const int hi = div_trunc(c[j] + g.P[j], g.S[j]);
-            o[j] = hi - cj[j];
-            const int k = c[j] - o[j] * g.S[j] + g.P[j];   // the offset this pair would get (:366)
-            ok = ok && cj[j] <= hi - lo && o[j] >= 0 && o[j] < g.out_shape[j] && k >= 0 && k < g.K[j] &&
-                 c[j] >= 0 && c[j] < g.in_shape[j];
+            in_ok = in_ok && c[j] >= 0 && c[j] < g.in_shape[j];
+#pragma unroll
+            for (int e = 0; e < MAXS; ++e) {
+                const int o = hi - e;
+                const int k = c[j] - o * g.S[j] + g.P[j];   // the offset this pair would get (:366)
+                const bool ok = e < g.span_max[j] && e <= hi - lo && o >= 0 && o < g.out_shape[j] && k >= 0 && k < g.K[j];
+                pos[j][e] = ok ? o : -1;
+            }
         }
-        if (!ok) continue;
-        unsigned long long* word = reinterpret_cast<unsigned long long*>(
-            out.rec + (size_t)b * out.words + ((size_t)o[0] * out.Y + o[1]) * out.xw + (o[2] >> 6));
-        const unsigned long long bit = 1ull << (o[2] & 63);
-        if (!(*reinterpret_cast<volatile unsigned long long*>(word) & bit)) atomicOr(word, bit);
+        if (!in_ok) continue;
+        // the x candidates as bits of at most two neighbouring words
+        int w0 = -1;
+        unsigned long long bits0 = 0ull, bits1 = 0ull;
+#pragma unroll
+        for (int e = 0; e < MAXS; ++e) {
+            const int ox = pos[2][e];
+            if (ox < 0) continue;
+            if (w0 < 0) w0 = ox >> 6;            // candidates descend, so the first valid one has the highest word
+            if ((ox >> 6) == w0) bits0 |= 1ull << (ox & 63);
+            else bits1 |= 1ull << (ox & 63);     // the word below (spans are at most three cells)
+        }
+        if (w0 < 0) continue;
+        unsigned long long* base = reinterpret_cast<unsigned long long*>(out.rec + (size_t)b * out.words);
+        unsigned long long cur0[MAXS * MAXS], cur1[MAXS * MAXS];
+        size_t rec[MAXS * MAXS];
+#pragma unroll
+        for (int ez = 0; ez < MAXS; ++ez)
+#pragma unroll
+            for (int ey = 0; ey < MAXS; ++ey) {
+                const int q = ez * MAXS + ey;
+                const bool ok = pos[0][ez] >= 0 && pos[1][ey] >= 0;
+                rec[q] = ok ? ((size_t)pos[0][ez] * out.Y + pos[1][ey]) * out.xw + w0 : (size_t)-1;
+                // a record is 16 bytes: its bits are the first 8
+                cur0[q] = ok ? *reinterpret_cast<volatile unsigned long long*>(base + 2 * rec[q]) : ~0ull;
+                cur1[q] = (ok && bits1) ? *reinterpret_cast<volatile unsigned long long*>(base + 2 * (rec[q] - 1)) : ~0ull;
+            }
+#pragma unroll
+        for (int q = 0; q < MAXS * MAXS; ++q) {
+            if (rec[q] == (size_t)-1) continue;
+            if ((cur0[q] & bits0) != bits0) atomicOr(base + 2 * rec[q], bits0);
+            if (bits1 && (cur1[q] & bits1) != bits1) atomicOr(base + 2 * (rec[q] - 1), bits1);
+        }
     }
 }
 
