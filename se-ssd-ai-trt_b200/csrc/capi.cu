@@ -686,23 +686,29 @@ static int backbone_enqueue_impl(const sessd_backbone* bb, int batch, int max_po
     // keep_status (pipelines): word 0 is left alone, so that it collects the conditions of every group of a run
     SESSD_CUDA(cudaMemsetAsync(w.status + (keep_status ? 1 : 0), 0, (kStatusInts - (keep_status ? 1 : 0)) * sizeof(int32_t),
                                stream));
-    int rc = launch_fill_ones(w.ones_base, w.ones_bytes, stream);
-    if (rc) return rc;
-    rc = launch_fill_zero(w.zero_base, w.zero_bytes, stream);
-    if (rc) return rc;
+    // one launch resets everything the call needs: the voxeliser's table and the bucket table (0xFF), the grids and
+    // tile masks (0), and the BEV map (0; by cudaMemsetAsync when its size is not a multiple of 16 bytes)
+    FillRanges fills{};
+    fills.ptr[0] = static_cast<uint4*>(w.ones_base), fills.n16[0] = w.ones_bytes / 16, fills.ones[0] = 1;
+    fills.ptr[1] = static_cast<uint4*>(w.zero_base), fills.n16[1] = w.zero_bytes / 16, fills.ones[1] = 0;
+    fills.ptr[2] = static_cast<uint4*>(static_cast<void*>(w.vox.table_base)), fills.n16[2] = w.vox.table_bytes / 16,
+    fills.ones[2] = 1;
+    const bool table_in_fill = w.vox.table_bytes % 16 == 0 && reinterpret_cast<uintptr_t>(w.vox.table_base) % 16 == 0;
+    if (!table_in_fill) fills.n16[2] = 0;
     if (bb->has_s2d) {
         const size_t bytes = (size_t)batch * bb->s2d.feature_map_channel * bb->s2d.feature_map_size_z *
                              (bb->s2d.feature_map_size_y + bb->pad.top + bb->pad.bottom) *
                              (bb->s2d.feature_map_size_x + bb->pad.left + bb->pad.right) * esize(bb->dtype);
-        if (bytes % 16 == 0)
-            rc = launch_fill_zero(dense, bytes, stream);
+        if (bytes % 16 == 0 && reinterpret_cast<uintptr_t>(dense) % 16 == 0)
+            fills.ptr[3] = static_cast<uint4*>(dense), fills.n16[3] = bytes / 16, fills.ones[3] = 0;
         else
             SESSD_CUDA(cudaMemsetAsync(dense, 0, bytes, stream));
-        if (rc) return rc;
     }
+    int rc = launch_fill_ranges(fills, stream);
+    if (rc) return rc;
     rc = voxelize_run(&bb->vp, batch, max_points, bb->dtype, static_cast<const float*>(points),
                       static_cast<const int32_t*>(points_size), w.voxel_feat, w.coors[0], w.num[0], w.vox,
-                      /*zero_tail=*/false, stream);
+                      /*zero_tail=*/false, stream, table_in_fill);
     if (rc) return rc;
     std::vector<char> nbr_ready(bb->nlevels, 0);
     const void* cur = w.voxel_feat;

@@ -235,6 +235,14 @@ int launch_zero_tail(void* tensor, int row_bytes, const int32_t* voxel_num, int 
                      cudaStream_t stream);
 int launch_fill_zero(void* ptr, size_t bytes, cudaStream_t stream);  // bytes % 16 == 0, ptr 16-byte aligned
 int launch_fill_ones(void* ptr, size_t bytes, cudaStream_t stream);  // every byte 0xFF; same constraints
+// Several fills as one launch: range r is n16[r] 16-byte words at ptr[r] (16-byte aligned), 0xFF bytes when ones[r]
+// is set, else zeros; unused ranges have n16 = 0.
+struct FillRanges {
+    uint4* ptr[4];
+    size_t n16[4];
+    int ones[4];
+};
+int launch_fill_ranges(const FillRanges& f, cudaStream_t stream);
 
 // rulebook.cu
 int conv_geom_from_params(const sessd_conv_params* p, ConvGeom* g);
@@ -316,7 +324,7 @@ struct VoxelWorkspace {
 void voxel_workspace_layout(Bump& bump, const sessd_voxel_params* p, int batch, int max_points, VoxelWorkspace* w);
 int voxelize_run(const sessd_voxel_params* p, int batch, int max_points, int out_dtype, const float* points,
                  const int32_t* points_size, void* voxels, int32_t* coors, int32_t* voxel_num, const VoxelWorkspace& w,
-                 bool zero_tail, cudaStream_t stream);
+                 bool zero_tail, cudaStream_t stream, bool table_is_reset = false);   // table_is_reset: the caller has filled w.table_base
 
 struct sessd_conv_weights_impl {
     void* w;        // device, [kvol][Cin][Cout] in dtype

@@ -174,7 +174,26 @@ __global__ void __launch_bounds__(kThreads) fill_ones_kernel(uint4* __restrict__
         p[i] = make_uint4(kEmpty, kEmpty, kEmpty, kEmpty);
 }
 
+// Up to four ranges filled by one launch (r = range, 16-byte words; value 0 or kEmpty in every word): the resets a
+// call of the fused front end needs (voxel table and bucket table to 0xFF, grids + masks and the BEV map to 0).
+__global__ void __launch_bounds__(kThreads) fill_ranges_kernel(FillRanges f) {
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    const size_t first = blockIdx.x * (size_t)blockDim.x + threadIdx.x;
+#pragma unroll
+    for (int r = 0; r < 4; ++r) {
+        const uint32_t v = f.ones[r] ? kEmpty : 0u;
+        uint4* p = f.ptr[r];
+        const size_t n = f.n16[r];
+        for (size_t i = first; i < n; i += stride) p[i] = make_uint4(v, v, v, v);
+    }
+}
+
 }  // namespace
+
+int launch_fill_ranges(const FillRanges& f, cudaStream_t stream) {
+    SESSD_LAUNCH(fill_ranges_kernel, persistent_grid(8), kThreads, 0, stream, f);
+    return SESSD_OK;
+}
 
 int launch_count_owners(const NumberingArgs& a, const Table& t, cudaStream_t stream) {
     SESSD_LAUNCH(count_owners_kernel, persistent_grid(8), kThreads, 0, stream, a, t);
@@ -232,10 +251,10 @@ void voxel_workspace_layout(Bump& bump, const sessd_voxel_params* p, int batch, 
 
 int voxelize_run(const sessd_voxel_params* p, int batch, int max_points, int out_dtype, const float* points,
                  const int32_t* points_size, void* voxels, int32_t* coors, int32_t* voxel_num, const VoxelWorkspace& w,
-                 bool zero_tail, cudaStream_t stream) {
+                 bool zero_tail, cudaStream_t stream, bool table_is_reset) {
     VoxGeom g{p->x_min, p->x_max, p->y_min, p->y_max, p->z_min, p->z_max, p->voxel_x, p->voxel_y, p->voxel_z,
               p->grid_x, p->grid_y, p->grid_z};
-    int rc = launch_fill_ones(w.table_base, w.table_bytes, stream);
+    int rc = table_is_reset ? SESSD_OK : launch_fill_ones(w.table_base, w.table_bytes, stream);
     if (rc) return rc;
     const float4* pts = reinterpret_cast<const float4*>(points);
     SESSD_LAUNCH(voxel_insert_kernel, persistent_grid(8), kThreads, 0, stream, pts, points_size, batch, max_points, g,
