@@ -59,6 +59,20 @@ def measured_traffic(workload, kernel):
         rec.get("frames_per_launch", 0), rec.get("command", "?"), rec.get("commit", "?"))
     return float(k["dram_bytes_per_frame"]), src
 
+
+def measured_l2_to_sm(workload, kernel):
+    """L2 -> SM bytes per frame of one launch of `kernel` from the same record (the gathers re-read every input row
+    once per kernel offset that reaches it), or None. Captured for one launch of the 1/4-resolution layers."""
+    path = os.path.join(ROOT, "profiles", "dram_traffic.json")
+    try:
+        with open(path) as f:
+            rec = json.load(f)
+    except (OSError, ValueError):
+        return None
+    k = rec.get("workloads", {}).get(workload, {}).get(kernel) or {}
+    v = k.get("l2_to_sm_bytes_per_frame_quarter_resolution_launch")
+    return float(v) if v else None
+
 WORKLOADS = {
     # name: (points per frame, object clusters, frames per GPU per step, max_voxels, frames per launch group)
     "sweep": dict(points=120000, boxes=40, frames=512, max_voxels=200000, batch=16, streams=3,
@@ -624,6 +638,9 @@ def main():
             roof.update(kernel=top, launches=len(idx), avg_launch_ms=ms / len(idx), peak_source=pk["source"],
                         algorithmic_bytes=byts / len(idx), traffic=per_frame * B if per_frame else None,
                         traffic_source=traffic_src)
+            l2sm = measured_l2_to_sm(args.workload, top)
+            if l2sm:
+                roof["l2_to_sm_bytes_quarter_resolution_launch"] = l2sm * B
         else:
             vox_rows = int(bb.layer_view(ws, B, P, -1)[2].sum())
             byts = 16.0 * float(grp_sizes.sum()) + vox_rows * (16 + 8 + 4) + 4 * B
