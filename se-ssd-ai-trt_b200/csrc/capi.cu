@@ -118,7 +118,7 @@ void conv_workspace_layout(Bump& bump, const sessd_conv_params* p, const ConvGeo
     w->zero_bytes = grid_bytes + mask_bytes;
     w->out_bits.rec = reinterpret_cast<uint4*>(zero);
     w->tile_mask = reinterpret_cast<uint32_t*>(zero ? zero + grid_bytes : nullptr);
-    w->nbr = bump.take<int32_t>((size_t)batch * g.kvol * p->max_voxels);
+    w->nbr = bump.take<int32_t>((size_t)batch * nbr_frame_words(g.kvol, p->max_voxels));
 }
 
 bool conv_params_ok(const sessd_conv_params* p, int batch) {
@@ -237,8 +237,9 @@ void backbone_layout(Bump& bump, const sessd_backbone* bb, int batch, int max_po
     for (size_t i = 0; i < bb->layers.size(); ++i)
         if (!bb->layers[i].p.subm) w->mask_layer[i] = masks ? masks + mask_words * mi++ : (mi++, nullptr);
     for (int l = 0; l < bb->nlevels; ++l)
-        if (bb->level_has_subm[l]) w->nbr_subm[l] = bump.take<int32_t>((size_t)batch * 27 * maxV);
-    w->nbr_strided = bump.take<int32_t>((size_t)batch * (bb->kvol_strided_max > 0 ? bb->kvol_strided_max : 1) * maxV);
+        if (bb->level_has_subm[l]) w->nbr_subm[l] = bump.take<int32_t>((size_t)batch * nbr_frame_words(27, maxV));
+    w->nbr_strided =
+        bump.take<int32_t>((size_t)batch * nbr_frame_words(bb->kvol_strided_max > 0 ? bb->kvol_strided_max : 1, maxV));
     w->chunk_counts = bump.take<int32_t>((size_t)batch * chunks_max);
     w->feat.assign(bb->layers.size(), nullptr);
     for (size_t i = 0; i < bb->layers.size(); ++i)

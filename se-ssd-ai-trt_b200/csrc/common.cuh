@@ -136,6 +136,18 @@ inline BitGrid bitgrid_shape(const int shape[3]) {
     return g;
 }
 
+// Neighbour maps are tile-major: [frame][tile of 128 output rows][kernel offset][kNbrRun], entry (k, o) of a frame
+// holding the input row under offset k of output row o, or -1. All offsets of a tile lie side by side, kNbrRun
+// words apart (the 128 entries and 16 bytes of padding), which is also how the tensor-core kernel keeps them in
+// shared memory: the offsets of one of its stages arrive with a single copy, already spaced for its index reads.
+constexpr int kNbrRun = 132;
+__host__ __device__ inline size_t nbr_frame_words(int kvol, int max_voxels) {
+    return (size_t)((max_voxels + 127) / 128) * kvol * kNbrRun;
+}
+__host__ __device__ inline size_t nbr_index(int kvol, int max_voxels, int b, int k, int o) {
+    return (size_t)b * nbr_frame_words(kvol, max_voxels) + ((size_t)(o >> 7) * kvol + k) * kNbrRun + (o & 127);
+}
+
 // Geometry of one sparse convolution (z, y, x order everywhere).
 struct ConvGeom {
     int K[3], S[3], P[3];

@@ -115,7 +115,7 @@ conv_simt_kernel(const T* __restrict__ in, T* __restrict__ out, const int32_t* _
         float acc[CO_T];
 #pragma unroll
         for (int c = 0; c < CO_T; ++c) acc[c] = 0.f;
-        const int32_t* nb = nbr + (size_t)b * kvol * max_voxels + o;
+        const int32_t* nb = nbr + nbr_index(kvol, max_voxels, b, 0, o);
         const T* in_b = in + (size_t)b * max_voxels * CIN;
         // one neighbour: s = sum_ci x[ci] * W[k][ci][:] as a fused chain, then acc += s
         auto add_neighbour = [&](int k, const float (&x)[CIN]) {
@@ -141,7 +141,7 @@ conv_simt_kernel(const T* __restrict__ in, T* __restrict__ out, const int32_t* _
             uint32_t present = 0;
 #pragma unroll
             for (int k = 0; k < KVOL_MAX; ++k) {
-                const int idx = k < kvol ? __ldg(nb + (size_t)k * max_voxels) : -1;
+                const int idx = k < kvol ? __ldg(nb + k * kNbrRun) : -1;
                 s_idx[k][threadIdx.x] = idx;          // read back by this thread only
                 present |= (idx >= 0 ? 1u : 0u) << k;
             }
@@ -161,7 +161,7 @@ conv_simt_kernel(const T* __restrict__ in, T* __restrict__ out, const int32_t* _
             }
         } else {
             for (int k = 0; k < kvol; ++k) {
-                const int idx = __ldg(nb + (size_t)k * max_voxels);
+                const int idx = __ldg(nb + k * kNbrRun);
                 if (idx < 0) continue;
                 float x[CIN];
                 RowLoader<T, CIN>::load(in_b + (size_t)idx * CIN, x);
@@ -209,7 +209,7 @@ conv_generic_kernel(const T* __restrict__ in, T* __restrict__ out, const int32_t
         int n = out_num[b];
         n = n > max_voxels ? max_voxels : n;
         if (o >= n) continue;
-        const int32_t* nb = nbr + (size_t)b * kvol * max_voxels + o;
+        const int32_t* nb = nbr + nbr_index(kvol, max_voxels, b, 0, o);
         const T* in_b = in + (size_t)b * max_voxels * cin;
         T* d = nullptr;
         if (dense) {
@@ -219,7 +219,7 @@ conv_generic_kernel(const T* __restrict__ in, T* __restrict__ out, const int32_t
         for (int co = lane; co < cout; co += 32) {
             float acc = 0.f;
             for (int k = 0; k < kvol; ++k) {
-                const int idx = __ldg(nb + (size_t)k * max_voxels);
+                const int idx = __ldg(nb + k * kNbrRun);
                 if (idx < 0) continue;
                 const T* x = in_b + (size_t)idx * cin;
                 const T* wk = weights + (size_t)k * cin * cout + co;

@@ -63,7 +63,8 @@ constexpr int A_BYTES = TILE_M * ROW_BYTES;  // 16 KB
 constexpr int KVOL_MAX = 27;
 // Words from one offset's 128 indices to the next offset's inside an index block: 16 bytes more than the indices
 // take, so that lanes reading different offsets of a stage (32- and 16-channel inputs) use different banks too.
-constexpr int TAP_WORDS = TILE_M + 4;
+constexpr int TAP_WORDS = kNbrRun;
+static_assert(kNbrRun == TILE_M + 4, "the map's spacing between offsets is the index block's");
 constexpr long long WAIT_LIMIT_CYCLES = 200000000LL;   // about a tenth of a second; real waits are microseconds
 
 // Gather slots (= gather warps): as many as fit beside the weight ring, the index blocks and the epilogue's staging area.
@@ -355,7 +356,6 @@ conv_umma_kernel(const __half* __restrict__ in, __half* __restrict__ out, const 
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int nstages = (kvol + KG - 1) / KG;
-    const bool idx_bulk = (max_voxels & 3) == 0;   // bulk copies need 16-byte aligned map rows
 
     if (tid == 0) {
         for (int s = 0; s < NSLOT; ++s) {
@@ -365,7 +365,7 @@ conv_umma_kernel(const __half* __restrict__ in, __half* __restrict__ out, const 
         }
         for (int j = 0; j < NIDX; ++j) {
             ctl->idx_uses[j] = 0;
-            mbar_init(smem_u32(&ctl->i_full[j]), idx_bulk ? 1 : 32);   // the issuing lane / the lanes of the index warp
+            mbar_init(smem_u32(&ctl->i_full[j]), 1);           // the lane of the index warp that issues the block's copy
             mbar_init(smem_u32(&ctl->i_empty[j]), 32);         // the lanes of the gather warp
         }
         for (int s = 0; s < B_STAGES; ++s) {
@@ -772,13 +772,13 @@ conv_umma_kernel(const __half* __restrict__ in, __half* __restrict__ out, const 
         } else if (warp == INDEX_WARP) {
             // ---------------- neighbour-index loader ----------------
             // Copies, for every item in consumption order, the KG x 128 neighbour indices into the next block of
-            // the index ring, two to three slot cycles ahead of the gather warp that will use them. A (tile,
-            // offset) row of the map is 512 contiguous bytes, so an item is KG bulk copies that report to the
-            // block's barrier by byte count; the lanes of the warp work on IDX_BATCH consecutive items at once
-            // (one dependent chain of wait, expect and copy per lane instead of one per item). Indices of rows
-            // past the frame's row count or of offsets past kvol are not loaded; the gather warps ignore them.
-            const int32_t* nbr_b = nbr + (size_t)b * kvol * max_voxels;
-            if (idx_bulk) {
+            // the index ring, two to three slot cycles ahead of the gather warp that will use them. The map is
+            // tile-major and spaces a tile's offsets like the index block does, so an item is one bulk copy that
+            // reports to the block's barrier by byte count; the lanes of the warp work on IDX_BATCH consecutive
+            // items at once (one dependent chain of wait, expect and copy per lane instead of one per item). The
+            // gather warps ignore the indices of rows past the frame's row count (stale) and of offsets past kvol
+            // (not loaded).
+            {
                 uint8_t* list = ctl->idx_list;
                 {
                     const uint32_t bits = lane < nstages ? active_tiles<KG>(m, lane) : 0u;
@@ -801,47 +801,20 @@ conv_umma_kernel(const __half* __restrict__ in, __half* __restrict__ out, const 
                         const int g = code >> 2, t = code & 3;
                         live = mbar_wait(smem_u32(&ctl->i_empty[j]), ((q / NIDX) & 1u) ^ 1u, abort_flag, 7 | (int)(q << 4));
                         if (live) {
-                            const int row = row0 + t * TILE_M;
-                            int rows = max_voxels - row;
-                            rows = rows > TILE_M ? TILE_M : rows;
+                            // the map is tile-major with the block's own spacing between offsets: the stage's
+                            // offsets of this tile are one contiguous run
                             int nk = kvol - g * KG;
                             nk = nk > KG ? KG : nk;
                             const uint32_t bar = smem_u32(&ctl->i_full[j]);
                             ctl->idx_uses[j] = q / NIDX + 1u;
-                            mbar_arrive_expect_tx(bar, (uint32_t)(nk * rows * 4));
-                            for (int jj = 0; jj < nk; ++jj)
-                                bulk_load(smem_u32(&s_idx[j * IDX_WORDS + jj * TAP_WORDS]),
-                                          nbr_b + (size_t)(g * KG + jj) * max_voxels + row, (uint32_t)(rows * 4), bar);
+                            mbar_arrive_expect_tx(bar, (uint32_t)(nk * TAP_WORDS * 4));
+                            bulk_load(smem_u32(&s_idx[j * IDX_WORDS]),
+                                      nbr + nbr_index(kvol, max_voxels, b, g * KG, row0 + t * TILE_M),
+                                      (uint32_t)(nk * TAP_WORDS * 4), bar);
                         }
                     }
                     live = __all_sync(0xFFFFFFFFu, live);   // also the batch boundary: no lane starts the next batch early
                     if (!live) break;
-                }
-            } else {
-                // map rows that are not 16-byte aligned (max_voxels not a multiple of 4): 4-byte copies, item by item
-                uint32_t q = a_it;
-                int g = -1, t = 0;
-                uint32_t rem = 0;
-                while (next_item<KG>(m, nstages, g, rem, t)) {
-                    const uint32_t j = q % NIDX;
-                    if (!mbar_wait(smem_u32(&ctl->i_empty[j]), ((q / NIDX) & 1u) ^ 1u, abort_flag, 7 | (int)(q << 4))) break;
-#pragma unroll
-                    for (int jj = 0; jj < KG; ++jj) {
-                        const int k = g * KG + jj;
-#pragma unroll
-                        for (int w4 = 0; w4 < TILE_M / 32; ++w4) {
-                            const int r = w4 * 32 + lane;
-                            const int row = row0 + t * TILE_M + r;
-                            const bool in_range = k < kvol && row < max_voxels;
-                            const int32_t* src = nbr_b + (in_range ? (size_t)k * max_voxels + row : 0);
-                            asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;" ::"r"(
-                                             smem_u32(&s_idx[j * IDX_WORDS + jj * TAP_WORDS + r])),
-                                         "l"(src), "r"(in_range ? 4u : 0u)
-                                         : "memory");
-                        }
-                    }
-                    cp_async_arrive_noinc(smem_u32(&ctl->i_full[j]));
-                    ++q;
                 }
             }
         } else {
@@ -877,7 +850,7 @@ conv_umma_kernel(const __half* __restrict__ in, __half* __restrict__ out, const 
         // its last bulk copies.
         if (warp >= FIRST_GATHER_WARP || warp == INDEX_WARP) asm volatile("cp.async.wait_all;" ::: "memory");
         if (warp >= EPI_WARPS && warp < WEIGHT_WARP && leader) umma_commit(smem_u32(&ctl->mma_drain));
-        if (warp == INDEX_WARP && idx_bulk) {
+        if (warp == INDEX_WARP) {
             for (int j = lane; j < NIDX; j += 32) {
                 const uint32_t uses = ctl->idx_uses[j];
                 if (!uses) continue;

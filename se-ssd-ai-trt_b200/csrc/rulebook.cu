@@ -82,7 +82,7 @@ nbr_build_kernel(const int4* __restrict__ out_coors, const int32_t* __restrict__
             const int slot = table_find(in_table.keys + (size_t)b * in_table.cap, in_table.cap, in_table.shift, key);
             if (slot >= 0) row = in_table.vals[(size_t)b * in_table.cap + slot];
         }
-        nbr[((size_t)b * g.kvol + k) * max_voxels + o] = row;
+        nbr[nbr_index(g.kvol, max_voxels, b, k, o)] = row;
     }
 }
 
@@ -114,13 +114,13 @@ rulebook_export_kernel(const int32_t* __restrict__ nbr, const int32_t* __restric
     const int k = blockIdx.x;
     int n = out_num[frame];
     n = n > max_voxels ? max_voxels : n;
-    const int32_t* col = nbr + ((size_t)frame * kvol + k) * max_voxels;
+    const int32_t* col = nbr + nbr_index(kvol, max_voxels, frame, k, 0);   // entry o of the column: col[(o >> 7) * kvol * kNbrRun + (o & 127)]
     int32_t* pin = pairs + ((size_t)k * 2 + 0) * max_voxels;
     int32_t* pout = pairs + ((size_t)k * 2 + 1) * max_voxels;
     int base = 0;
     for (int o0 = 0; o0 < n; o0 += kThreads) {
         const int o = o0 + threadIdx.x;
-        const int v = o < n ? col[o] : -1;
+        const int v = o < n ? col[(size_t)(o >> 7) * kvol * kNbrRun + (o & 127)] : -1;
         int total;
         const int pos = base + block_exclusive_scan(v >= 0 ? 1 : 0, &total);
         if (v >= 0) {
@@ -146,7 +146,7 @@ count_pairs_kernel(const int32_t* __restrict__ nbr, const int32_t* __restrict__ 
         const int o = (r - k * chunks) * kThreads + threadIdx.x;
         int n = out_num[b];
         n = n > max_voxels ? max_voxels : n;
-        if (o < n && nbr[((size_t)b * kvol + k) * max_voxels + o] >= 0) ++local;
+        if (o < n && nbr[nbr_index(kvol, max_voxels, b, k, o)] >= 0) ++local;
     }
     const int sum = block_sum(local);
     if (threadIdx.x == 0 && sum) atomicAdd(total, (unsigned long long)sum);
@@ -257,7 +257,7 @@ nbr_build_subm_kernel(const int4* __restrict__ coors, const int32_t* __restrict_
         const int x = c.w;
         const bool x_ok = live && x >= 0 && x < X;
         const uint32_t* base = t.data + (size_t)b * t.cap * 8;
-        int32_t* out = nbr + (size_t)b * 27 * max_voxels + o;
+        int32_t* out = nbr + nbr_index(27, max_voxels, b, 0, o);
         uint32_t bits = 0;
 #pragma unroll
         for (int kz = 0; kz < 3; ++kz) {
@@ -292,7 +292,7 @@ nbr_build_subm_kernel(const int4* __restrict__ coors, const int32_t* __restrict_
 #pragma unroll
                 for (int d = 0; d < 3; ++d) {
                     const int k = (kz * 3 + ky) * 3 + d;
-                    if (live) out[(size_t)k * max_voxels] = res[d];
+                    if (live) out[k * kNbrRun] = res[d];
                     if (__ballot_sync(0xFFFFFFFFu, res[d] >= 0)) bits |= 1u << k;
                 }
             }
@@ -505,7 +505,7 @@ map_rows_kernel(const int4* __restrict__ out_coors, const int32_t* __restrict__ 
         int4 c = make_int4(0, 0, 0, 0);
         if (live) c = __ldg(&out_coors[(size_t)b * max_voxels + o]);
         const int bz = c.y * g.S[0] - g.P[0], by = c.z * g.S[1] - g.P[1], bx = c.w * g.S[2] - g.P[2];
-        int32_t* out = nbr + (size_t)b * g.kvol * max_voxels + o;
+        int32_t* out = nbr + nbr_index(g.kvol, max_voxels, b, 0, o);
         uint32_t bits = 0;
 #pragma unroll
         for (int kz = 0; kz < 3; ++kz) {
@@ -530,7 +530,7 @@ map_rows_kernel(const int4* __restrict__ out_coors, const int32_t* __restrict__ 
                     const int x = bx + kx;
                     const int row = on ? in.finish(pb[ky], x) : -1;
                     const int k = (kz * K1 + ky) * K2 + kx;
-                    if (live) out[(size_t)k * max_voxels] = row;
+                    if (live) out[k * kNbrRun] = row;
                     if (__ballot_sync(0xFFFFFFFFu, row >= 0)) bits |= 1u << k;
                 }
             }
@@ -540,24 +540,21 @@ map_rows_kernel(const int4* __restrict__ out_coors, const int32_t* __restrict__ 
     }
 }
 
-// Fills nbr[b][k][0 .. out_num[b]) with -1 (one int4 per thread where aligned).
+// Fills the map entries of the tiles that hold rows 0 .. out_num[b] with -1, one int4 per thread (a tile's block of
+// kvol x kNbrRun words is contiguous and 16-byte aligned; the padding words are written too).
 __global__ void __launch_bounds__(kThreads)
 nbr_clear_kernel(int32_t* __restrict__ nbr, const int32_t* __restrict__ out_num, int batch, int max_voxels, int kvol) {
-    const int chunks = (max_voxels + kThreads * 4 - 1) / (kThreads * 4);
-    const int items = batch * kvol * chunks;
+    const size_t frame_words = nbr_frame_words(kvol, max_voxels);
+    const int chunks = (int)((frame_words / 4 + kThreads - 1) / kThreads);
+    const int items = batch * chunks;
     for (int it = blockIdx.x; it < items; it += gridDim.x) {
-        const int bk = it / chunks;
-        const int b = bk / kvol;
-        const int o = ((it - bk * chunks) * kThreads + threadIdx.x) * 4;
+        const int b = it / chunks;
         int n = out_num[b];
         n = n > max_voxels ? max_voxels : n;
-        if (o >= n) continue;
-        int32_t* p = nbr + (size_t)bk * max_voxels + o;
-        if ((max_voxels & 3) == 0) {
-            *reinterpret_cast<int4*>(p) = make_int4(-1, -1, -1, -1);   // may run up to 3 rows past n: inside the row block
-        } else {
-            for (int q = 0; q < 4 && o + q < max_voxels; ++q) p[q] = -1;
-        }
+        const size_t used_words = (size_t)((n + 127) / 128) * kvol * kNbrRun;   // a multiple of 4
+        const size_t w = ((size_t)(it - b * chunks) * kThreads + threadIdx.x) * 4;
+        if (w >= used_words) continue;
+        *reinterpret_cast<int4*>(nbr + (size_t)b * frame_words + w) = make_int4(-1, -1, -1, -1);
     }
 }
 
@@ -606,7 +603,7 @@ scatter_rows_kernel(const int4* __restrict__ in_coors, const int32_t* __restrict
         out.probe(b, o[0], o[1], o[2], 1, true, &p);
         const int id = out.finish(p, o[2]);
         if (id < 0) continue;   // output dropped by the max_voxels cap
-        nbr[((size_t)b * g.kvol + k) * max_voxels + id] = i;
+        nbr[nbr_index(g.kvol, max_voxels, b, k, id)] = i;
         uint32_t* m = &tile_mask[(size_t)b * tiles_per_frame + (id >> 7)];
         if (!((*reinterpret_cast<volatile uint32_t*>(m) >> k) & 1u)) atomicOr(m, 1u << k);
     }
@@ -628,7 +625,7 @@ tile_mask_kernel(const int32_t* __restrict__ nbr, const int32_t* __restrict__ ou
         bool any = false;
         for (int q = 0; q < 4; ++q) {
             const int o = tile * 128 + q * 32 + lane;
-            if (o < n && nbr[((size_t)b * kvol + k) * max_voxels + o] >= 0) any = true;
+            if (o < n && nbr[nbr_index(kvol, max_voxels, b, k, o)] >= 0) any = true;
         }
         if (__ballot_sync(0xFFFFFFFFu, any) && lane == 0) atomicOr(&tile_mask[(size_t)b * tiles_per_frame + tile], 1u << k);
     }
