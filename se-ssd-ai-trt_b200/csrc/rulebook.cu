@@ -481,6 +481,26 @@ struct BitsIndex {
         const int id = (int)r.z + __popcll(bits & ((1ull << bit) - 1ull));
         return id < max_rows ? id : -1;
     }
+    // The rows of the cells x0 .. x0 + count - 1 (count <= 3) of a probed line at once: the cells are neighbouring
+    // bits of a window that may straddle two records, and rows are numbered along the line, so the row of a set
+    // cell is the row of the window's first cell plus the set cells before it.
+    __device__ __forceinline__ void finish_line(const Probe& p, int x0, int count, int (&rows)[3]) const {
+        const int lo = x0 < 0 ? 0 : x0;
+        const int sh = lo & 63;
+        const unsigned long long a = rec_bits(p.a), b = p.two ? rec_bits(p.b) : 0ull;
+        const unsigned long long window = sh ? (a >> sh) | (b << (64 - sh)) : a;
+        const int base = (int)p.a.z + __popcll(a & ((1ull << sh) - 1ull));
+#pragma unroll
+        for (int e = 0; e < 3; ++e) {
+            const int x = x0 + e, pos = x - lo;
+            int row = -1;
+            if (e < count && x >= 0 && x < g.X && ((window >> pos) & 1ull)) {
+                const int id = base + __popcll(window & ((1ull << pos) - 1ull));
+                row = id < max_rows ? id : -1;
+            }
+            rows[e] = row;
+        }
+    }
 };
 
 // Neighbour map of a layer whose input level has an occupancy grid: one thread per output row walks the
@@ -524,11 +544,12 @@ map_rows_kernel(const int4* __restrict__ out_coors, const int32_t* __restrict__ 
                 if (ky >= K1) break;
                 const int y = by + ky;
                 const bool on = z_ok && y >= 0 && y < g.in_shape[1];
+                int rows3[3] = {-1, -1, -1};
+                if (on) in.finish_line(pb[ky], bx, K2, rows3);
 #pragma unroll
                 for (int kx = 0; kx < 3; ++kx) {
                     if (kx >= K2) break;
-                    const int x = bx + kx;
-                    const int row = on ? in.finish(pb[ky], x) : -1;
+                    const int row = rows3[kx];
                     const int k = (kz * K1 + ky) * K2 + kx;
                     if (live) out[k * kNbrRun] = row;
                     if (__ballot_sync(0xFFFFFFFFu, row >= 0)) bits |= 1u << k;
