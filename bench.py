@@ -75,7 +75,7 @@ def measured_l2_to_sm(workload, kernel):
 
 WORKLOADS = {
     # name: (points per frame, object clusters, frames per GPU per step, max_voxels, frames per launch group)
-    "sweep": dict(points=120000, boxes=40, frames=512, max_voxels=200000, batch=16, streams=3,
+    "sweep": dict(points=120000, boxes=40, frames=512, max_voxels=200000, batch=32, streams=2,
                   desc="throughput sweep: 512 frames x 120,000 points per GPU"),
     "single": dict(points=20000, boxes=15, frames=2048, max_voxels=60000, batch=32,
                    desc="20,000-point frames (single-frame backbone case), 2048 per GPU"),
