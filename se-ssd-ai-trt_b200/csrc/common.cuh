@@ -287,7 +287,7 @@ int launch_tile_mask(const int32_t* nbr, const int32_t* out_num, int batch, int 
 struct ConvLaunch {
     const void* in;        // [B][max_voxels][Cin]
     void* out;             // [B][max_voxels][Cout]
-    const int32_t* nbr;    // [B][kvol][max_voxels]
+    const int32_t* nbr;    // neighbour map, tile-major (nbr_index)
     const int32_t* out_num;// [B]
     const uint32_t* tile_mask; // [B][ceil(max_voxels/128)]: bit k set when offset k has a neighbour in the tile
     const void* weights;   // [kvol][Cin][Cout] in the feature dtype

@@ -6,6 +6,8 @@
 // output-stationary form: nbr[b][k][o] = input row that feeds output row o through kernel offset k,
 // or -1. Pair (k, i, o) of the reference exists exactly when nbr[b][k][o] == i, because
 // k = in - out*stride + pad per axis (submConv3dlayer.cu:328-329) and input rows are unique.
+// nbr[b][k][o] names the entry; in memory the map is tile-major (nbr_index in common.cuh: the offsets of a
+// 128-row tile side by side), so that the tensor-core kernel fetches a tile's offsets with one copy.
 //
 // Where the rows of a frame come from decides how a coordinate is turned back into its row:
 //   - the voxeliser's rows (full resolution, 92 M cells, 80 K of them active) sit in an x-grouped
